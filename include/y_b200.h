@@ -1,0 +1,181 @@
+/*
+ * liby_b200 - C ABI of the B200 (sm_100a) quantised-inference GEMM path.
+ *
+ * Plain pointers and sizes only. Every device pointer is a CUDA device
+ * address of the current device; `stream` is a cudaStream_t passed as void*
+ * (NULL = the default stream). Functions return 0 on success or a negative
+ * Y_B200_ERR_* code; y_b200_last_error() gives the message for the calling
+ * thread. No entry point falls back to the CPU.
+ *
+ * Each block names the reference interface it replaces (path inside the
+ * reference project : line).
+ */
+#ifndef Y_B200_H
+#define Y_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define Y_B200_API __attribute__((visibility("default")))
+#else
+#define Y_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- errors --------------------------------------------------------------- */
+#define Y_B200_OK 0
+#define Y_B200_ERR_INVALID (-1)     /* null pointer, bad enum, bad size        */
+#define Y_B200_ERR_SHAPE (-2)       /* shape precondition violated              */
+#define Y_B200_ERR_ALIGN (-3)       /* pointer or stride alignment              */
+#define Y_B200_ERR_CUDA (-4)        /* a CUDA call failed                       */
+#define Y_B200_ERR_WORKSPACE (-5)   /* workspace missing or too small           */
+#define Y_B200_ERR_DEVICE (-6)      /* device reported a bounded-wait timeout   */
+#define Y_B200_ERR_UNSUPPORTED (-7) /* not an sm_100 device, unknown kernel ... */
+
+#define Y_B200_DEV_WAIT_TIMEOUT 1u
+
+Y_B200_API const char* y_b200_last_error(void);
+Y_B200_API const char* y_b200_version(void);
+/* Reads and clears the device status word that kernels with bounded waits
+ * write when a wait runs out. Returns 0 when clean, else Y_B200_ERR_DEVICE
+ * with details in y_b200_last_error(). Synchronises `stream`. */
+Y_B200_API int y_b200_device_status(void* stream);
+
+/* ---- element kinds ---------------------------------------------------------- */
+enum { Y_B200_F32 = 0, Y_B200_F16 = 1, Y_B200_BF16 = 2, Y_B200_E4M3 = 3 };
+enum { Y_B200_EPI_NONE = 0, Y_B200_EPI_BIAS = 1, Y_B200_EPI_BIAS_RELU = 2, Y_B200_EPI_SWIGLU = 3 };
+
+/* ---- FP8 quantisation -------------------------------------------------------
+ * Replaces the quantise+stage loops fused into the reference's FP8 GEMM
+ * (src/ptx_emitter.rs:2595-2658 emit_fp8_quantize_pair / emit_fp8_pack_quad,
+ * :2693-3053 stage_a/_b) and the host-side amax
+ * (tests/test_fp8_gemm_correctness.py:99-100): q = e4m3_rn_satfinite(x * (1/scale)),
+ * scale = max(amax/448, 1e-12), element i in byte i. */
+
+/* amax_out: one device float; overwritten with max|x|. */
+Y_B200_API int y_b200_amax(const void* x, int x_kind, size_t n, float* amax_out, void* stream);
+/* scale_out[0] = max(amax[0]/448, 1e-12) (device to device). */
+Y_B200_API int y_b200_scale_from_amax(const float* amax, float* scale_out, void* stream);
+/* Static scale: q = e4m3(x * (1/scale[0])); scale is a device float. */
+Y_B200_API int y_b200_quantize_fp8(const void* x, int x_kind, size_t n, const float* scale, void* q,
+                        void* stream);
+/* x is [rows, cols] row-major, q is [cols, rows] row-major (used to store the
+ * reference's row-major B [K, N] as K-major [N, K] for the tensor cores). */
+Y_B200_API int y_b200_quantize_fp8_transpose(const void* x, int x_kind, size_t rows, size_t cols,
+                                  const float* scale, void* q, void* stream);
+/* Dynamic per-tensor: amax pass, then quantise; scale_out (device float)
+ * receives the scale. transpose != 0 writes q as [cols, rows]. */
+Y_B200_API int y_b200_quantize_fp8_dynamic(const void* x, int x_kind, size_t rows, size_t cols,
+                                int transpose, void* q, float* scale_out, void* stream);
+
+/* ---- RMSNorm -> FP8 prologue -----------------------------------------------
+ * Replaces rmsnorm_residual_<H> (src/ptx_emitter.rs:5773-6015) for the
+ * column-parallel GEMM's A operand: no residual, runtime eps, output
+ * quantised to e4m3 with a fresh per-tensor scale. hidden % 8 == 0.
+ * workspace: y_b200_rmsnorm_workspace_bytes(rows) bytes of device memory. */
+Y_B200_API size_t y_b200_rmsnorm_workspace_bytes(size_t rows);
+Y_B200_API int y_b200_rmsnorm_quantize_fp8(const void* x_f16, const void* gamma_f16, size_t rows,
+                                size_t hidden, float eps, void* q, float* scale_out,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- FP8 GEMM ---------------------------------------------------------------
+ * Replaces gemm_fp8_<tag> (src/ptx_emitter.rs:3282-3580, entry
+ * tests/gemm_fp8_256.ptx:5-11) and y_fp8_tensor_core_gemm_kernel
+ * (tests/y_tensor_core_gemm.cu:4152-4159) with its fused epilogues
+ * (src/ptx_emitter.rs:3530-3577 scale, :4729-4814 bias+ReLU,
+ * :5481-5565 SwiGLU).
+ *   C = epilogue((sa*sb) * (Aq @ Bq)), f32 accumulation in tensor memory.
+ * a: [M, K] e4m3 row-major. bt: [N, K] e4m3 row-major (B stored K-major).
+ * K % 16 == 0; M, N >= 1. Scales: when scale_a_dev / scale_b_dev are non-null
+ * they are read on the device (no host sync), else the by-value floats are used.
+ * EPI_SWIGLU: the N columns are gate|up interleaved (2j gate, 2j+1 up); c is
+ * [M, N/2] bf16 and amax_out (device float, must be zeroed by the caller or
+ * by y_b200_gemm_fp8_swiglu_requant) receives max|c|. */
+typedef struct y_b200_gemm_fp8_args {
+    const void* a;
+    const void* bt;
+    void* c;
+    int m, n, k;
+    float scale_a, scale_b;
+    const float* scale_a_dev;
+    const float* scale_b_dev;
+    const void* bias;  /* [N], bias_kind F16 or F32; NULL for EPI_NONE/SWIGLU */
+    int bias_kind;
+    int epilogue;      /* Y_B200_EPI_*  */
+    int out_kind;      /* Y_B200_F32 / F16 / BF16 */
+    float* amax_out;   /* EPI_SWIGLU only */
+    int cta_n;         /* 0 = pick from the tile table; else 64, 128 or 256 */
+    int max_ctas;      /* 0 = one persistent CTA per SM */
+} y_b200_gemm_fp8_args;
+
+Y_B200_API int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* args, void* stream);
+
+/* Launch geometry the library would use for this problem (the reference
+ * embeds it in PTX comments, src/ptx_emitter.rs:3337, :4323-4331). */
+typedef struct y_b200_launch_info {
+    unsigned grid[3], block[3], cluster[3];
+    unsigned dyn_smem_bytes;
+    size_t workspace_bytes;
+    int cta_m, cta_n, cta_k, stages;
+} y_b200_launch_info;
+Y_B200_API int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b200_launch_info* out);
+
+/* Drop-in for the reference entry gemm_fp8_<tag>(A, B, scale_a, scale_b, C):
+ * A [M, K] f32, B [K, N] f32 row-major, C [M, N] f32; operands are quantised
+ * on the device with the given scales, then multiplied. workspace holds the
+ * e4m3 copies: y_b200_gemm_fp8_f32_workspace_bytes(m, n, k) bytes. */
+Y_B200_API size_t y_b200_gemm_fp8_f32_workspace_bytes(int m, int n, int k);
+Y_B200_API int y_b200_gemm_fp8_f32(const float* a, const float* b, float scale_a, float scale_b, float* c,
+                        int m, int n, int k, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
+/* Fused SwiGLU GEMM with FP8 re-quantisation (replaces gemm_f16_swiglu_<tag>,
+ * src/ptx_emitter.rs:5064-5565, with FP8 operands and interleaved gate|up):
+ * h = bf16(silu(g) * u) -> fresh per-tensor scale -> q = e4m3(h / scale).
+ * q is [M, N/2] e4m3, scale_out a device float.
+ * workspace: y_b200_swiglu_workspace_bytes(m, n) bytes (the bf16 h tensor
+ * and the amax word). */
+Y_B200_API size_t y_b200_swiglu_workspace_bytes(int m, int n);
+Y_B200_API int y_b200_gemm_fp8_swiglu_requant(const y_b200_gemm_fp8_args* args, void* q, float* scale_out,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- INT4 weight-only decode GEMM -------------------------------------------
+ * The reference has no INT4 kernel (src/ptx_emitter.rs:7321-7330 is a dead
+ * stub); its decode entries gemm_f16_decode_m<M> (tests/gemm_f16_decode_m1.ptx:6-9)
+ * stream F16 weights. Format defined here: symmetric, group 128 along K,
+ * s = f16(amax_g/7), q = clamp(rne(w/s), -8, 7), two's-complement nibbles,
+ * element k = 8*kw + j in nibble j of qweight[kw, n]; scales [K/128, N] f16.
+ * K % 128 == 0, N % 16 == 0. */
+Y_B200_API int y_b200_int4_quantize(const void* w_f16, size_t k, size_t n, uint32_t* qweight,
+                         void* scales_f16, void* stream);
+/* Bytes of the streaming layout the decode kernel reads (weights and scales
+ * interleaved per 16-column x 128-row block). */
+Y_B200_API size_t y_b200_int4_stream_bytes(size_t k, size_t n);
+Y_B200_API int y_b200_int4_repack(const uint32_t* qweight, const void* scales_f16, size_t k, size_t n,
+                       void* wstream, void* stream);
+/* out[M, N] f16 = x[M, K] f16 @ dequant(W); f32 accumulation. 1 <= M <= 32. */
+Y_B200_API int y_b200_gemm_int4_decode(const void* x_f16, const void* wstream, void* out_f16, int m, int n,
+                            int k, void* stream);
+
+/* ---- input generator ---------------------------------------------------------
+ * random_f16_bits (src/cuda_runtime.rs:657-682): element i = f(i + index0, seed),
+ * a normal binary16 with exponent in 12..14. Written on the device. */
+Y_B200_API int y_b200_fill_random_f16(void* out_f16, size_t n, uint64_t index0, uint64_t seed, void* stream);
+
+/* ---- c_api.rs symbols (src/c_api.rs:27-212) -----------------------------------
+ * Strings returned by these are owned by the library; free with y_free_string. */
+Y_B200_API char* y_compile_to_ptx(const char* source, const char* target_sm, char** error_out);
+Y_B200_API char* y_autotune_search_space_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8);
+Y_B200_API char* y_autotune_select_config_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8);
+Y_B200_API int32_t y_interpret_kernel(const char* source, char** error_out);
+Y_B200_API uint32_t y_block_cdiv(uint32_t a, uint32_t b);
+Y_B200_API void y_free_string(char* s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,104 @@
+"""INT4 weight-only path on the GPU: quantise/pack and repack are bit-exact against
+the oracle; the decode GEMM meets the GEMM acceptance criteria."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import assert_gemm_close, dev, f16_dev, host_bits, to_f64
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def q(cuda):
+    from y_b200 import quant
+    return quant
+
+
+@pytest.mark.parametrize("k,n", [(128, 16), (256, 32), (1024, 176), (4096, 1376)])
+def test_quantise_and_repack_bit_exact(q, k, n):
+    w = oracle.fill_normal_f16(k * n, oracle.SEED_B + 3, 1.0 / 16.0).reshape(k, n)
+    if k >= 256:
+        w[128:256, 5] = 0  # an all-zero group: scale 0, codes 0
+    qw, sc = q.int4_quantize(f16_dev(w))
+    rq, rs = oracle.int4_quantize(w)
+    assert np.array_equal(qw.cpu().numpy().view(np.uint32), rq)
+    assert np.array_equal(host_bits(sc), rs)
+    stream = q.int4_repack(qw, sc)
+    assert np.array_equal(stream.cpu().numpy(), oracle.int4_repack(rq, rs))
+
+
+@pytest.mark.parametrize("m", [1, 2, 4, 7, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("k,n", [(256, 32), (1024, 2368), (4096, 1376)])
+def test_decode_gemm_matches_oracle(q, m, k, n):
+    w = oracle.fill_normal_f16(k * n, oracle.SEED_B + 3, 1.0 / np.sqrt(k)).reshape(k, n)
+    x = oracle.fill_normal_f16(m * k, oracle.SEED_A + 3).reshape(m, k)
+    rq, rs = oracle.int4_quantize(w)
+    stream = dev(oracle.int4_repack(rq, rs))
+    out = q.gemm_int4_decode(f16_dev(x), stream, n)
+    q.device_status()
+    ref = oracle.gemm_int4_decode(x, rq, rs)
+    assert_gemm_close(to_f64(host_bits(out), oracle.OUT_F16), to_f64(ref, oracle.OUT_F16), f"M={m}")
+
+
+def test_decode_exact_integers_and_determinism(q):
+    # integer activations and unit scales: every partial sum is exact, so the
+    # result must equal the integer matmul bit for bit
+    m, k, n = 8, 1152, 208   # 9 groups: exercises the partial last ring slot
+    rng = np.random.default_rng(9)
+    qv = rng.integers(-8, 8, size=(k, n)).astype(np.int32)
+    xv = rng.integers(-4, 5, size=(m, k)).astype(np.float32)
+    nib = (qv & 0xF).astype(np.uint32).reshape(k // 8, 8, n)
+    qw = np.zeros((k // 8, n), np.uint32)
+    for j in range(8):
+        qw |= nib[:, j, :] << np.uint32(4 * j)
+    sc = np.full((k // 128, n), np.float16(1.0)).view(np.uint16)
+    stream = dev(oracle.int4_repack(qw, sc))
+    xd = torch.from_numpy(xv).cuda().to(torch.float16)
+    out = q.gemm_int4_decode(xd, stream, n)
+    q.device_status()
+    ref = xv.astype(np.float64) @ qv.astype(np.float64)
+    assert np.array_equal(out.float().cpu().numpy().astype(np.float64), ref.astype(np.float16).astype(np.float64))
+    for _ in range(20):
+        assert torch.equal(q.gemm_int4_decode(xd, stream, n), out)
+
+
+def test_decode_config_shape_full(q, golden_dir):
+    # K=4096, N=11008 (the decode config), every M of the config
+    k, n = 4096, 11008
+    w = (torch.randn(k, n, device="cuda") / 64).to(torch.float16)
+    qw, sc = q.int4_quantize(w)
+    stream = q.int4_repack(qw, sc)
+    qw_h, sc_h = qw.cpu().numpy().view(np.uint32), host_bits(sc)
+    # pack -> unpack round trip on the device data
+    nib = np.stack([(qw_h >> (4 * j)) & 0xF for j in range(8)], axis=1).reshape(k, n).astype(np.int32)
+    qint = np.where(nib >= 8, nib - 16, nib)
+    wd = qint * np.repeat(sc_h.view(np.float16).astype(np.float32), 128, axis=0)
+    assert np.abs(wd - w.float().cpu().numpy()).max() <= np.abs(w.float().cpu().numpy()).max() / 7 * 0.51 + 1e-6
+    for m in (1, 4, 8, 32):
+        x = torch.randn(m, k, device="cuda", dtype=torch.float16)
+        out = q.gemm_int4_decode(x, stream, n)
+        q.device_status()
+        ref = oracle.gemm_int4_decode(host_bits(x), qw_h, sc_h)
+        assert_gemm_close(to_f64(host_bits(out), oracle.OUT_F16), to_f64(ref, oracle.OUT_F16), f"M={m}")
+    g = np.load(os.path.join(golden_dir, "path_small.npz"))
+    M4, N4, K4 = g["int4_shape"]
+    xw = oracle.fill_normal_f16(M4 * K4, oracle.SEED_A + 3).reshape(M4, K4)
+    out = q.gemm_int4_decode(f16_dev(xw), dev(g["int4_stream"]), int(N4))
+    assert_gemm_close(to_f64(host_bits(out), oracle.OUT_F16), to_f64(g["int4_out"], oracle.OUT_F16))
+    out2 = q.int4_weight_only_gemm(f16_dev(xw), dev(g["int4_qweight"]), f16_dev(g["int4_scales"]))
+    assert torch.equal(out, out2)
+
+
+def test_decode_preconditions(q):
+    from y_b200._lib import YB200Error, ERR_SHAPE
+    x = torch.zeros(33, 128, dtype=torch.float16, device="cuda")
+    s = torch.zeros(1056, dtype=torch.uint8, device="cuda")
+    with pytest.raises(YB200Error) as e:
+        q.gemm_int4_decode(x, s, 16)
+    assert e.value.code == ERR_SHAPE
+    with pytest.raises(YB200Error):
+        q.gemm_int4_decode(x[:4, :100].contiguous(), s, 16)

@@ -1,0 +1,114 @@
+"""ctypes binding of liby_b200.so (the C ABI declared in include/y_b200.h).
+
+The library is the product; this module only loads it and declares the
+argument types. There is no fallback: if the shared library is missing the
+import fails with instructions to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liby_b200.so")
+
+OK = 0
+ERR_INVALID, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE, ERR_UNSUPPORTED = (
+    -1, -2, -3, -4, -5, -6, -7)
+F32, F16, BF16, E4M3 = 0, 1, 2, 3
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_SWIGLU = 0, 1, 2, 3
+
+
+class YB200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"liby_b200 error {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+class GemmFp8Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("bt", C.c_void_p), ("c", C.c_void_p),
+        ("m", C.c_int), ("n", C.c_int), ("k", C.c_int),
+        ("scale_a", C.c_float), ("scale_b", C.c_float),
+        ("scale_a_dev", C.c_void_p), ("scale_b_dev", C.c_void_p),
+        ("bias", C.c_void_p), ("bias_kind", C.c_int),
+        ("epilogue", C.c_int), ("out_kind", C.c_int),
+        ("amax_out", C.c_void_p),
+        ("cta_n", C.c_int), ("max_ctas", C.c_int),
+    ]
+
+
+class LaunchInfo(C.Structure):
+    _fields_ = [
+        ("grid", C.c_uint * 3), ("block", C.c_uint * 3), ("cluster", C.c_uint * 3),
+        ("dyn_smem_bytes", C.c_uint), ("workspace_bytes", C.c_size_t),
+        ("cta_m", C.c_int), ("cta_n", C.c_int), ("cta_k", C.c_int), ("stages", C.c_int),
+    ]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m y_b200.build` (needs nvcc); "
+            "this package has no CPU or PyTorch fallback")
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+_vp, _sz, _i, _f, _u32, _u64 = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_uint32, C.c_uint64
+
+# name -> (restype, argtypes); every symbol include/y_b200.h declares.
+SIGNATURES = {
+    "y_b200_last_error": (C.c_char_p, []),
+    "y_b200_version": (C.c_char_p, []),
+    "y_b200_device_status": (_i, [_vp]),
+    "y_b200_amax": (_i, [_vp, _i, _sz, _vp, _vp]),
+    "y_b200_scale_from_amax": (_i, [_vp, _vp, _vp]),
+    "y_b200_quantize_fp8": (_i, [_vp, _i, _sz, _vp, _vp, _vp]),
+    "y_b200_quantize_fp8_transpose": (_i, [_vp, _i, _sz, _sz, _vp, _vp, _vp]),
+    "y_b200_quantize_fp8_dynamic": (_i, [_vp, _i, _sz, _sz, _i, _vp, _vp, _vp]),
+    "y_b200_rmsnorm_workspace_bytes": (_sz, [_sz]),
+    "y_b200_rmsnorm_quantize_fp8": (_i, [_vp, _vp, _sz, _sz, _f, _vp, _vp, _vp, _sz, _vp]),
+    "y_b200_gemm_fp8": (_i, [C.POINTER(GemmFp8Args), _vp]),
+    "y_b200_gemm_fp8_launch_info": (_i, [_i, _i, _i, _i, C.POINTER(LaunchInfo)]),
+    "y_b200_gemm_fp8_f32_workspace_bytes": (_sz, [_i, _i, _i]),
+    "y_b200_gemm_fp8_f32": (_i, [_vp, _vp, _f, _f, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "y_b200_swiglu_workspace_bytes": (_sz, [_i, _i]),
+    "y_b200_gemm_fp8_swiglu_requant": (_i, [C.POINTER(GemmFp8Args), _vp, _vp, _vp, _sz, _vp]),
+    "y_b200_int4_quantize": (_i, [_vp, _sz, _sz, _vp, _vp, _vp]),
+    "y_b200_int4_stream_bytes": (_sz, [_sz, _sz]),
+    "y_b200_int4_repack": (_i, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    "y_b200_gemm_int4_decode": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "y_b200_fill_random_f16": (_i, [_vp, _sz, _u64, _u64, _vp]),
+    "y_compile_to_ptx": (_vp, [C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
+    "y_autotune_search_space_json": (_vp, [_u32, _u32, _u32, _i]),
+    "y_autotune_select_config_json": (_vp, [_u32, _u32, _u32, _i]),
+    "y_interpret_kernel": (C.c_int32, [C.c_char_p, C.POINTER(_vp)]),
+    "y_block_cdiv": (_u32, [_u32, _u32]),
+    "y_free_string": (None, [_vp]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.y_b200_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise YB200Error(rc, last_error())
+
+
+def take_string(ptr) -> str | None:
+    """Copies a library-owned C string and frees it with y_free_string."""
+    if not ptr:
+        return None
+    s = C.string_at(ptr).decode("utf-8", "replace")
+    lib.y_free_string(ptr)
+    return s

@@ -1,0 +1,333 @@
+// The reference's C-ABI symbols (src/c_api.rs:27-212) on top of the B200
+// kernels. `y_compile_to_ptx` keeps its name and contract (source text in,
+// heap string out, error text through *error_out), but what it returns for a
+// recognised `@tile` kernel is a launch descriptor for the prebuilt sm_100a
+// kernel family rather than PTX: the kernels here are compiled ahead of time.
+// The descriptor keeps the reference's machine-readable comment lines
+// (src/ptx_emitter.rs:3337, :4323-4331) so launchers that scrape them keep
+// working, and y_ctx_load_module accepts it as the "image".
+#include <ctype.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "autotuner.cuh"
+#include "common.cuh"
+#include "frontend.h"
+
+namespace yb {
+
+namespace {
+
+char* dup_string(const std::string& s) {
+    char* p = static_cast<char*>(malloc(s.size() + 1));
+    if (p) memcpy(p, s.c_str(), s.size() + 1);
+    return p;
+}
+
+void put_error(char** error_out, const std::string& msg) {
+    if (error_out) *error_out = dup_string(msg);
+}
+
+struct Cursor {
+    const std::string& s;
+    size_t i;
+    void skip_ws_and_comments() {
+        for (;;) {
+            while (i < s.size() && isspace((unsigned char)s[i])) ++i;
+            if (i + 1 < s.size() && s[i] == '/' && s[i + 1] == '/') {
+                while (i < s.size() && s[i] != '\n') ++i;
+                continue;
+            }
+            if (i + 1 < s.size() && s[i] == '/' && s[i + 1] == '*') {
+                size_t e = s.find("*/", i + 2);
+                i = e == std::string::npos ? s.size() : e + 2;
+                continue;
+            }
+            return;
+        }
+    }
+    bool eat(char ch) {
+        skip_ws_and_comments();
+        if (i < s.size() && s[i] == ch) { ++i; return true; }
+        return false;
+    }
+    bool eat_word(const char* w) {
+        skip_ws_and_comments();
+        size_t n = strlen(w);
+        if (s.compare(i, n, w) == 0 && (i + n >= s.size() || !(isalnum((unsigned char)s[i + n]) || s[i + n] == '_'))) {
+            i += n;
+            return true;
+        }
+        return false;
+    }
+    std::string ident() {
+        skip_ws_and_comments();
+        size_t b = i;
+        while (i < s.size() && (isalnum((unsigned char)s[i]) || s[i] == '_')) ++i;
+        return s.substr(b, i - b);
+    }
+    bool positive_int(long long* out) {
+        skip_ws_and_comments();
+        size_t b = i;
+        while (i < s.size() && isdigit((unsigned char)s[i])) ++i;
+        if (b == i || i - b > 12) return false;
+        *out = atoll(s.substr(b, i - b).c_str());
+        return *out > 0;
+    }
+};
+
+}  // namespace
+
+// Parses every `[@tile(M, N, K)] kernel name(params) { ... }` in the source.
+// Grammar subset of src/parser.rs:135-154; everything else in the file is
+// skipped (the reference fixtures also hold an empty `fn main() {}`).
+bool parse_kernels(const std::string& src, std::vector<KernelDecl>* out, std::string* err) {
+    Cursor c{src, 0};
+    while (true) {
+        c.skip_ws_and_comments();
+        if (c.i >= src.size()) break;
+        KernelDecl k;
+        size_t save = c.i;
+        if (c.eat('@')) {
+            std::string attr = c.ident();
+            if (attr == "tile") {
+                long long v[3];
+                if (!c.eat('(') || !c.positive_int(&v[0]) || !c.eat(',') || !c.positive_int(&v[1])) {
+                    *err = "Parser Error: @tile expects (M, N, K) positive integer literals";
+                    return false;
+                }
+                if (!c.eat(',') || !c.positive_int(&v[2])) {
+                    *err = "TypeChecker Error: Kernel-level @tile(M, N, K) requires K (the third argument) - it must be a positive integer literal.";
+                    return false;
+                }
+                if (!c.eat(')')) { *err = "Parser Error: expected ')' after @tile arguments"; return false; }
+                k.has_tile = true;
+                k.m = v[0]; k.n = v[1]; k.k = v[2];
+            } else {
+                // another attribute: skip an optional parenthesised list
+                if (c.eat('(')) { int depth = 1; while (c.i < src.size() && depth) { if (src[c.i] == '(') ++depth; if (src[c.i] == ')') --depth; ++c.i; } }
+                continue;
+            }
+        }
+        if (c.eat_word("kernel")) {
+            k.name = c.ident();
+            if (k.name.empty() || !c.eat('(')) { *err = "Parser Error: expected kernel name and '('"; return false; }
+            while (!c.eat(')')) {
+                ParamDecl p;
+                p.name = c.ident();
+                if (p.name.empty() || !c.eat(':')) { *err = "Parser Error: expected `name: Type` in the parameter list of `" + k.name + "`"; return false; }
+                std::string base = c.ident();
+                if (c.eat('<')) {
+                    p.is_global = base == "GlobalMemory";
+                    p.elem = c.ident();
+                    if (!c.eat('>')) { *err = "Parser Error: expected '>' in the type of `" + p.name + "`"; return false; }
+                    if (!p.is_global) p.elem = base + "<" + p.elem + ">";
+                } else {
+                    p.elem = base;
+                }
+                k.params.push_back(p);
+                c.eat(',');
+                if (c.i >= src.size()) { *err = "Parser Error: unterminated parameter list"; return false; }
+            }
+            if (!c.eat('{')) { *err = "Parser Error: expected '{' after the parameter list of `" + k.name + "`"; return false; }
+            int depth = 1;
+            while (c.i < src.size() && depth) { if (src[c.i] == '{') ++depth; if (src[c.i] == '}') --depth; ++c.i; }
+            if (depth) { *err = "Parser Error: unterminated body of `" + k.name + "`"; return false; }
+            out->push_back(k);
+            continue;
+        }
+        if (k.has_tile) { *err = "Parser Error: @tile must be followed by a kernel declaration"; return false; }
+        // Not a kernel: skip one token / balanced block.
+        c.i = save;
+        if (src[c.i] == '{') { int depth = 1; ++c.i; while (c.i < src.size() && depth) { if (src[c.i] == '{') ++depth; if (src[c.i] == '}') --depth; ++c.i; } }
+        else if (isalnum((unsigned char)src[c.i]) || src[c.i] == '_') c.ident();
+        else ++c.i;
+    }
+    return true;
+}
+
+// Shape dispatch by parameter list, the rules of src/type_checker.rs:892-1009
+// (and src/ptx_emitter.rs:555-575): 5 params = FP8 GEMM, 3 = F16 GEMM,
+// 4 with F32 third = bias+ReLU, 4 with F16 third = SwiGLU; 5 F16 buffers
+// without @tile and a `rmsnorm_residual_` name = fused add+RMSNorm.
+KernelFamily classify_kernel(const KernelDecl& k, std::string* err) {
+    auto gm = [&](size_t i, const char* elem) {
+        return i < k.params.size() && k.params[i].is_global && k.params[i].elem == elem;
+    };
+    auto scalar = [&](size_t i, const char* elem) {
+        return i < k.params.size() && !k.params[i].is_global && k.params[i].elem == elem;
+    };
+    if (!k.has_tile) {
+        if (k.params.size() == 5 && k.name.rfind("rmsnorm_residual_", 0) == 0 && gm(0, "F16") &&
+            gm(1, "F16") && gm(2, "F16") && gm(3, "F16") && gm(4, "F16"))
+            return KernelFamily::RmsnormResidual;
+        return KernelFamily::None;
+    }
+    const size_t np = k.params.size();
+    if (np == 5) {
+        if (gm(0, "F32") && gm(1, "F32") && scalar(2, "F32") && scalar(3, "F32") && gm(4, "F32"))
+            return KernelFamily::GemmFp8;
+        *err = "TypeChecker Error: Kernel-level @tile(M, N, K) on `" + k.name +
+               "` with 5 parameters requires (A, B: GlobalMemory<F32>, scale_a, scale_b: F32, C: GlobalMemory<F32>) for a fused FP8 (e4m3) GEMM.";
+        return KernelFamily::Invalid;
+    }
+    if (np == 3 && gm(0, "F16") && gm(1, "F16") && gm(2, "F32")) return KernelFamily::GemmF16;
+    if (np == 4 && gm(0, "F16") && gm(1, "F16") && gm(2, "F32") && gm(3, "F32")) return KernelFamily::GemmF16BiasRelu;
+    if (np == 4 && gm(0, "F16") && gm(1, "F16") && gm(2, "F16") && gm(3, "F32")) return KernelFamily::GemmF16Swiglu;
+    char buf[64];
+    snprintf(buf, sizeof buf, "%zu", np);
+    *err = "TypeChecker Error: Kernel-level @tile(M, N, K) on `" + k.name +
+           "` requires 3 parameters (A, B: GlobalMemory<F16>, C: GlobalMemory<F32>) for a plain GEMM, 4 (A, B: GlobalMemory<F16>, Bias, C: GlobalMemory<F32>) for a fused GEMM+Bias+ReLU epilogue, or 4 (X, W_gate, W_up: GlobalMemory<F16>, Out: GlobalMemory<F32>) for a fused Linear+SwiGLU epilogue, in that order. Found " +
+           buf + " parameter(s).";
+    return KernelFamily::Invalid;
+}
+
+const char* family_name(KernelFamily f) {
+    switch (f) {
+        case KernelFamily::GemmFp8: return "gemm_fp8";
+        case KernelFamily::GemmF16: return "gemm_f16";
+        case KernelFamily::GemmF16BiasRelu: return "gemm_f16_bias_relu";
+        case KernelFamily::GemmF16Swiglu: return "gemm_f16_swiglu";
+        case KernelFamily::RmsnormResidual: return "rmsnorm_residual";
+        default: return "none";
+    }
+}
+
+// One descriptor block per recognised kernel.
+std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::string& target_sm) {
+    char buf[1024];
+    std::string out;
+    snprintf(buf, sizeof buf, "// [Y B200 KERNEL] entry=%s family=%s target=%s\n", k.name.c_str(),
+             family_name(fam), target_sm.c_str());
+    out += buf;
+    if (fam == KernelFamily::GemmFp8) {
+        if (k.k % 64 != 0) return std::string();  // caller reports the K precondition
+        Candidate c = autotune((uint32_t)k.m, (uint32_t)k.n, (uint32_t)k.k, Precision::Fp8,
+                               "NVIDIA B200", 148);
+        const long long tiles = ((k.m + c.cta_m - 1) / c.cta_m) * ((k.n + c.cta_n - 1) / c.cta_n);
+        const long long grid = tiles < 148 ? tiles : 148;
+        const unsigned smem = c.num_stages * (128u * 128u + c.cta_n * 128u) + (2 * c.num_stages + 4) * 8 + 16 + 1024;
+        snprintf(buf, sizeof buf,
+                 "// [Y FP8 TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %ux%ux%u | %ux%u warps | "
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 e4m3 x e4m3 -> f32 (TMEM)\n"
+                 "// Operands are quantised to e4m3 by separate HBM-bound kernels; epilogue dequants by scale_a*scale_b.\n"
+                 "// Launch grid required: (%lld, 1, 1) CTAs, block (192,1,1); persistent over %lld tiles, %u stages.\n"
+                 "// Dynamic shared memory required: %u bytes.\n"
+                 "// Workspace required: %zu bytes.\n",
+                 k.m, k.n, k.k, c.cta_m, c.cta_n, c.cta_k, c.warps_m, c.warps_n, grid, tiles,
+                 c.num_stages, smem,
+                 y_b200_gemm_fp8_f32_workspace_bytes((int)k.m, (int)k.n, (int)k.k));
+        out += buf;
+    } else if (fam == KernelFamily::RmsnormResidual) {
+        out += "// [Y RMSNORM] one 256-thread CTA per row; 128-bit loads; fixed-order reduction\n";
+    } else {
+        const uint32_t cta_k = 64;
+        snprintf(buf, sizeof buf,
+                 "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA 128x256x%u | 4x1 warps | "
+                 "tcgen05.mma.cta_group::1.kind::f16 f16 x f16 -> f32 (TMEM)\n",
+                 k.m, k.n, k.k, cta_k);
+        out += buf;
+    }
+    return out;
+}
+
+}  // namespace yb
+
+using namespace yb;
+
+extern "C" char* y_compile_to_ptx(const char* source, const char* target_sm, char** error_out) {
+    if (error_out) *error_out = nullptr;
+    if (!source) { put_error(error_out, "Source pointer is null"); return nullptr; }
+    std::string sm = target_sm ? target_sm : "";
+    if (sm.empty() || sm == "auto") sm = "sm_100a";
+    std::vector<KernelDecl> kernels;
+    std::string err;
+    if (!parse_kernels(source, &kernels, &err)) { put_error(error_out, err); return nullptr; }
+    std::string out = "// liby_b200 launch descriptor (prebuilt " + sm + " kernels; no PTX is generated)\n";
+    for (const KernelDecl& k : kernels) {
+        KernelFamily fam = classify_kernel(k, &err);
+        if (fam == KernelFamily::Invalid) { put_error(error_out, err); return nullptr; }
+        if (fam == KernelFamily::None) {
+            out += "// [Y B200 KERNEL] entry=" + k.name + " family=none (generic kernels are outside this library)\n";
+            continue;
+        }
+        if (fam == KernelFamily::GemmFp8 && k.k % 64 != 0) {
+            // src/ptx_emitter.rs:3297-3304 asserts the same at emit time.
+            put_error(error_out, "FP8 GEMM `" + k.name + "` requires K to be a multiple of 64");
+            return nullptr;
+        }
+        if ((fam == KernelFamily::GemmF16 || fam == KernelFamily::GemmF16BiasRelu) && k.k % 8 != 0) {
+            put_error(error_out, "F16 GEMM `" + k.name + "` requires K to be a multiple of 8");
+            return nullptr;
+        }
+        if (fam == KernelFamily::GemmF16Swiglu && (k.m % 128 || k.n % 128 || k.k % 32)) {
+            put_error(error_out, "SwiGLU GEMM `" + k.name + "` requires M, N multiples of 128 and K a multiple of 32");
+            return nullptr;
+        }
+        out += describe_kernel(k, fam, sm);
+    }
+    return dup_string(out);
+}
+
+static std::string candidate_json(const Candidate& c, int with_fp8, bool is_fp8) {
+    char buf[256];
+    if (with_fp8)
+        snprintf(buf, sizeof buf,
+                 "{\"cta_m\":%u,\"cta_n\":%u,\"cta_k\":%u,\"warps_m\":%u,\"warps_n\":%u,\"num_stages\":%u,\"num_warps\":%u,\"is_fp8\":%s}",
+                 c.cta_m, c.cta_n, c.cta_k, c.warps_m, c.warps_n, c.num_stages, c.num_warps,
+                 is_fp8 ? "true" : "false");
+    else
+        snprintf(buf, sizeof buf,
+                 "{\"cta_m\":%u,\"cta_n\":%u,\"cta_k\":%u,\"warps_m\":%u,\"warps_n\":%u,\"num_stages\":%u,\"num_warps\":%u}",
+                 c.cta_m, c.cta_n, c.cta_k, c.warps_m, c.warps_n, c.num_stages, c.num_warps);
+    return buf;
+}
+
+// is_fp8 == 0 selects the 16-bit namespace; decode shapes (M <= 32) there are
+// served by the INT4 weight-streaming kernel.
+static Precision precision_for(uint32_t m, int is_fp8) {
+    if (is_fp8) return Precision::Fp8;
+    return m <= 32 ? Precision::Int4 : Precision::F16;
+}
+
+extern "C" char* y_autotune_search_space_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8) {
+    std::string out = "[";
+    bool first = true;
+    for (const Candidate& c : generate_candidates(m, n, k, precision_for(m, is_fp8))) {
+        if (!first) out += ",";
+        first = false;
+        out += candidate_json(c, 1, is_fp8 != 0);
+    }
+    out += "]";
+    return dup_string(out);
+}
+
+extern "C" char* y_autotune_select_config_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8) {
+    // The reference resolves against a default hardware profile here
+    // (src/c_api.rs:183-185), not the GPU that happens to be present.
+    Candidate c = autotune(m, n, k, precision_for(m, is_fp8), "NVIDIA B200", 148);
+    return dup_string(candidate_json(c, 0, false));
+}
+
+extern "C" int32_t y_interpret_kernel(const char* source, char** error_out) {
+    if (error_out) *error_out = nullptr;
+    if (!source) { put_error(error_out, "Source pointer is null"); return -1; }
+    // The reference parses, type-checks and emits CPU source text that it then
+    // discards (src/c_api.rs:133-172); nothing is executed. This library has no
+    // CPU path at all, so the call only validates the source.
+    std::vector<KernelDecl> kernels;
+    std::string err;
+    if (!parse_kernels(source, &kernels, &err)) { put_error(error_out, err); return -1; }
+    return 0;
+}
+
+extern "C" uint32_t y_block_cdiv(uint32_t a, uint32_t b) {
+    if (b == 0) return 0;
+    return (uint32_t)(((uint64_t)a + b - 1) / b);
+}
+
+extern "C" void y_free_string(char* s) { free(s); }

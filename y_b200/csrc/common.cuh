@@ -1,0 +1,258 @@
+// Shared device helpers for the sm_100a kernels: error plumbing, bounded
+// mbarrier waits, TMA and tcgen05 PTX wrappers, small conversion helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/y_b200.h"
+
+namespace yb {
+
+// ---- host-side error plumbing ---------------------------------------------
+// Every extern "C" entry returns 0 or a negative Y_B200_ERR_* code and leaves
+// a message retrievable through y_b200_last_error() (thread local).
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+
+#define YB_CUDA(call)                                         \
+    do {                                                      \
+        int _rc = ::yb::check_cuda((call), #call);            \
+        if (_rc != 0) return _rc;                             \
+    } while (0)
+
+int sm_count();  // multiprocessors of the current device (cached per device)
+
+// ---- device status word ------------------------------------------------------
+// Kernels that wait on mbarriers never spin without a limit: a wait that runs
+// out records where it gave up in this word and the kernel unwinds. The host
+// reads it with y_b200_device_status().
+struct DeviceStatus {
+    unsigned int code;   // 0 = ok, else Y_B200_DEV_* reason
+    unsigned int where;  // role / barrier index that gave up
+    unsigned int block;  // blockIdx.x of the reporting CTA
+    unsigned int extra;
+};
+DeviceStatus* device_status_ptr();  // per-device, allocated on first use
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// ---- mbarrier ---------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Cycle budget of one wait (about two seconds at 2 GHz). Far above any legal
+// wait inside these kernels, far below the watchdog of a shared machine.
+constexpr long long kWaitCycles = 4000000000LL;
+
+// Bounded wait. Returns false when the budget ran out or when another role of
+// this CTA already raised `abort_flag` (a word in shared memory).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0x3ffu) == 0) {
+            if (*abort_flag != 0) return false;
+            if (clock64() - t0 > kWaitCycles) return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void report_timeout(DeviceStatus* st, volatile uint32_t* abort_flag,
+                                               unsigned int where, unsigned int extra) {
+    *abort_flag = 1u;
+    if (st != nullptr && atomicCAS(&st->code, 0u, (unsigned int)Y_B200_DEV_WAIT_TIMEOUT) == 0u) {
+        st->where = where;
+        st->block = blockIdx.x;
+        st->extra = extra;
+    }
+}
+
+// ---- TMA ----------------------------------------------------------------------
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+
+// 2-D tiled load into this CTA's shared memory; completion is counted in bytes
+// on `bar`. x is the innermost coordinate (elements); x * elemsize must be a
+// multiple of 16. No multicast.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar,
+                                            int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// 1-D bulk copy global -> shared; both addresses and the size are multiples of 16.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(dst),
+        "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+// ---- tcgen05 / TMEM --------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// The mbarrier gets one arrival once every tcgen05.mma this thread issued so
+// far has finished (implies fence::before_thread_sync).
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; `accumulate` == 0 overwrites D.
+__device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives
+// lane (base_lane + t), registers r[0..31] are columns col .. col+31.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are one
+// 128-byte swizzle span wide (the layout a SWIZZLE_128B tensor-map box lands
+// in): 8-row groups 1024 bytes apart, descriptor version 1, 128-byte swizzle.
+// The tile base must be 1024-byte aligned; advancing along K inside the span
+// adds the byte offset to the start address.
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);  // start address, 16-byte units
+    d |= (uint64_t)0 << 16;                        // leading byte offset: unused here
+    d |= (uint64_t)(1024u >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                        // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor for kind::f8f6f4 / kind::f16, dense, f32 accumulate,
+// both operands K-major. a_fmt/b_fmt: f8f6f4 0 = e4m3, 1 = e5m2; f16 kind
+// 0 = f16, 1 = bf16.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t a_fmt,
+                                                  uint32_t b_fmt) {
+    return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ---- small conversion helpers -------------------------------------------------
+// Two f32 -> two e4m3 codes (round to nearest even, saturate to +-448):
+// `lo` lands in bits 0..7, `hi` in bits 8..15.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t)r;
+}
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+    return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+
+// scale = max(amax / 448, 1e-12), inv = 1 / scale; both correctly rounded.
+__device__ __forceinline__ float scale_from_amax(float amax) {
+    return fmaxf(__fdiv_rn(amax, 448.0f), 1e-12f);
+}
+__device__ __forceinline__ float inv_scale(float scale) { return __fdiv_rn(1.0f, scale); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
+    return __reduce_max_sync(0xffffffffu, v);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace yb

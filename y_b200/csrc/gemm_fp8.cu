@@ -1,0 +1,579 @@
+// Large-M FP8 (e4m3 x e4m3 -> f32) GEMM for sm_100a: tcgen05.mma kind::f8f6f4
+// with the accumulator in tensor memory, operands staged by TMA into a
+// multi-stage shared-memory ring, and the scale / bias / ReLU / SwiGLU
+// epilogues applied while draining tensor memory.
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
+//   warps 2..5  epilogue; warp w drains TMEM lanes 32*(w%4) .. +31
+// The accumulator is double-buffered in TMEM (2 x CTA_N columns) so the
+// epilogue of tile i overlaps the main loop of tile i+1. Tiles are visited in
+// grouped-raster order (8 M-tiles per group, column-first) so the CTAs running
+// at the same time share A and B panels through L2.
+//
+// Operand layout: A [M, K] and Bt [N, K] are both K-major e4m3. A k-block is
+// 128 bytes of K, i.e. exactly one 128-byte swizzle span: a TMA box of
+// {128 bytes, rows} with SWIZZLE_128B lands in shared memory in the layout the
+// UMMA descriptor (K-major, 128-byte swizzle, 8-row groups 1024 bytes apart)
+// expects. Out-of-range rows and K are zero-filled by TMA, so any M, N >= 1 and
+// any K % 16 == 0 work; the epilogue masks the ragged edge. No multicast.
+//
+// Every mbarrier wait is bounded; a wait that runs out raises the device
+// status word and the CTA unwinds through the common teardown.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace yb {
+
+int quantize_with_host_scale(const void* x, int kind, size_t rows, size_t cols, bool transpose,
+                             float scale, float* scale_slot, void* q, cudaStream_t st);
+int quantize_from_amax(const void* x, int kind, size_t n, const float* amax, void* q,
+                       float* scale_out, cudaStream_t st);
+
+namespace {
+
+constexpr int kCtaM = 128;
+constexpr int kCtaK = 128;  // bytes of K per stage = one swizzle span
+constexpr int kUmmaK = 32;  // K per tcgen05.mma for 8-bit operands
+constexpr int kGemmThreads = 192;
+constexpr int kSwizzleGroup = 8;  // M-tiles per raster group
+
+struct GemmParams {
+    void* c;
+    int m, n, k;
+    float scale_a, scale_b;
+    const float* scale_a_dev;
+    const float* scale_b_dev;
+    const void* bias;
+    int bias_kind;
+    unsigned int* amax_out;
+    DeviceStatus* status;
+    int m_tiles, n_tiles;
+};
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int a_bytes = kCtaM * kCtaK;
+    static constexpr int b_bytes = BN * kCtaK;
+    static constexpr int stage_bytes = a_bytes + b_bytes;
+    static constexpr int stages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int tmem_cols = 2 * BN;  // 128, 256 or 512: powers of two >= 32
+    static constexpr int bar_bytes = (2 * stages + 4) * 8 + 16;
+    // +1024 so the ring can be aligned to the swizzle-atom size at run time.
+    static constexpr int smem_bytes = stages * stage_bytes + bar_bytes + 1024;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& tm, int& tn) {
+    const int per_group = n_tiles * kSwizzleGroup;
+    const int gid = tile / per_group, off = tile % per_group;
+    const int first_m = gid * kSwizzleGroup;
+    const int gsz = min(kSwizzleGroup, m_tiles - first_m);
+    tm = first_m + off % gsz;
+    tn = off / gsz;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    // silu(g) = g / (1 + exp(-g)), exp through ex2 like the reference epilogue.
+    const float e = exp2f(-g * 1.4426950408889634f);
+    return __fdividef(g, 1.0f + e) * u;
+}
+
+template <int OUT>
+struct OutT;
+template <>
+struct OutT<Y_B200_F32> { using type = float; };
+template <>
+struct OutT<Y_B200_F16> { using type = __half; };
+template <>
+struct OutT<Y_B200_BF16> { using type = __nv_bfloat16; };
+
+template <int OUT>
+__device__ __forceinline__ void store_scalar(void* c, size_t idx, float v) {
+    if (OUT == Y_B200_F32) static_cast<float*>(c)[idx] = v;
+    else if (OUT == Y_B200_F16) static_cast<__half*>(c)[idx] = __float2half_rn(v);
+    else static_cast<__nv_bfloat16*>(c)[idx] = __float2bfloat16_rn(v);
+}
+
+// Stores `count` (16 or 32, all in range) consecutive values of one row with
+// 16-byte stores; `dst` is 16-byte aligned.
+template <int OUT, int COUNT>
+__device__ __forceinline__ void store_vec(void* dst, const float* v) {
+    if (OUT == Y_B200_F32) {
+        float4* d = static_cast<float4*>(dst);
+#pragma unroll
+        for (int i = 0; i < COUNT / 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+        uint4* d = static_cast<uint4*>(dst);
+#pragma unroll
+        for (int i = 0; i < COUNT / 8; ++i) {
+            uint4 o;
+            if (OUT == Y_B200_F16) {
+                o.x = pack_f16x2(v[8 * i], v[8 * i + 1]);
+                o.y = pack_f16x2(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_f16x2(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_f16x2(v[8 * i + 6], v[8 * i + 7]);
+            } else {
+                o.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
+                o.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+            }
+            d[i] = o;
+        }
+    }
+}
+
+template <int BN, int EPI, int OUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    using Cfg = GemmCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // The swizzle pattern is a function of the shared-memory address, so the
+    // ring must start on a 1024-byte boundary.
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t ring0 = (raw_addr + 1023u) & ~1023u;
+    uint8_t* ring_ptr = smem_raw + (ring0 - raw_addr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + Cfg::stages * Cfg::stage_bytes);
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 8 * Cfg::stages;
+    const uint32_t tfull0 = empty0 + 8 * Cfg::stages;   // 2 barriers: accumulator ready
+    const uint32_t tempty0 = tfull0 + 16;               // 2 barriers: accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::stages + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int num_kb = (p.k + kCtaK - 1) / kCtaK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull0 + 8 * a, 1);
+            mbar_init(tempty0 + 8 * a, 128);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) {
+                        report_timeout(p.status, abort_flag, 0x10u, (unsigned)kb);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = ring0 + stage * Cfg::stage_bytes;
+                    mbar_expect_tx(full0 + 8 * stage, Cfg::stage_bytes);
+                    tma_load_2d(dst, &tmap_a, full0 + 8 * stage, kb * kCtaK, tm * kCtaM);
+                    tma_load_2d(dst + Cfg::a_bytes, &tmap_b, full0 + 8 * stage, kb * kCtaK, tn * BN);
+                    if (++stage == Cfg::stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc(kCtaM, BN, 0u, 0u);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t as = it & 1, aphase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * as, aphase ^ 1u, abort_flag)) {
+                    report_timeout(p.status, abort_flag, 0x20u, (unsigned)it);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) {
+                        report_timeout(p.status, abort_flag, 0x21u, (unsigned)kb);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = ring0 + stage * Cfg::stage_bytes;
+                    const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + Cfg::a_bytes);
+#pragma unroll
+                    for (int k = 0; k < kCtaK / kUmmaK; ++k) {
+                        // +32 bytes of K inside the swizzle span = +2 in 16-byte units.
+                        umma_f8f6f4(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
+                                    b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
+                                    (uint32_t)((kb | k) != 0));
+                    }
+                    tc_commit(empty0 + 8 * stage);  // frees the stage once the MMAs have read it
+                    if (++stage == Cfg::stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(tfull0 + 8 * as);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may touch
+        const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
+                            (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
+        constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
+        const int n_out = p.n / out_div;
+        constexpr int esize = OUT == Y_B200_F32 ? 4 : 2;
+        const bool rows_aligned = ((size_t)n_out * esize) % 16 == 0 &&
+                                  (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0;
+        uint32_t amax_bits = 0;
+        bool dead = false;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            int tm, tn;
+            tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+            const uint32_t as = it & 1, aphase = (it >> 1) & 1;
+            if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
+                report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
+                dead = true;
+            }
+            if (dead) break;
+            tc_fence_after();
+            const int row = tm * kCtaM + quarter * 32 + lane;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                const int col0 = tn * BN + ch * 32;
+                if (col0 >= p.n) break;  // uniform across the warp
+                uint32_t r[32];
+                tmem_ld_32x32(t_addr + ch * 32, r);
+                tc_wait_ld();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * scale;
+
+                if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        float b = 0.0f;
+                        if (col < p.n)
+                            b = p.bias_kind == Y_B200_F16
+                                    ? __half2float(__ldg(static_cast<const __half*>(p.bias) + col))
+                                    : __ldg(static_cast<const float*>(p.bias) + col);
+                        v[j] += b;
+                        if (EPI == Y_B200_EPI_BIAS_RELU) v[j] = fmaxf(v[j], 0.0f);
+                    }
+                }
+
+                if (EPI == Y_B200_EPI_SWIGLU) {
+                    // columns 2j (gate) and 2j+1 (up) -> output column col0/2 + j
+                    float h[16];
+                    uint32_t packed[8];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) h[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        packed[j] = pack_bf16x2(h[2 * j], h[2 * j + 1]);
+                        // amax over the bf16-rounded values, as f32 bit patterns
+                        amax_bits = max(amax_bits, (packed[j] << 16) & 0x7fffffffu);
+                        amax_bits = max(amax_bits, packed[j] & 0x7fff0000u);
+                    }
+                    if (row < p.m) {
+                        const int ocol0 = col0 / 2;
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + (size_t)row * n_out + ocol0;
+                        if (rows_aligned && col0 + 32 <= p.n) {
+                            uint4* d = reinterpret_cast<uint4*>(dst);
+                            d[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            d[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (ocol0 + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
+                        }
+                    }
+                } else if (row < p.m) {
+                    if (rows_aligned && col0 + 32 <= p.n) {
+                        store_vec<OUT, 32>(static_cast<char*>(p.c) + ((size_t)row * p.n + col0) * esize, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < p.n) store_scalar<OUT>(p.c, (size_t)row * p.n + col0 + j, v[j]);
+                    }
+                }
+            }
+            // This thread's TMEM reads are complete (wait::ld above): hand the
+            // accumulator buffer back to the MMA warp.
+            tc_fence_before();
+            mbar_arrive(tempty0 + 8 * as);
+        }
+        if (EPI == Y_B200_EPI_SWIGLU && p.amax_out != nullptr) {
+            // Rows beyond M and columns beyond N were zero-filled, so they add
+            // nothing to the maximum.
+            amax_bits = warp_max_u32(amax_bits);
+            if (lane == 0 && amax_bits != 0u) atomicMax(p.amax_out, amax_bits);
+        }
+    }
+
+    // ------------------------------ teardown -------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::tmem_cols);
+    }
+}
+
+// ---- host side -----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// K-major e4m3 matrix [rows, k]; box = 128 bytes of K x box_rows rows.
+int make_operand_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(Y_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k};
+    cuuint32_t box[2] = {(cuuint32_t)kCtaK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(Y_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
+    return 0;
+}
+
+int pick_cta_n(int m, int n) {
+    // Tile table for B200 (148 SMs): the widest tile keeps shared-memory traffic
+    // per MMA lowest; narrower tiles only when the grid would leave most SMs idle.
+    const int m_tiles = (m + kCtaM - 1) / kCtaM;
+    const int sms = sm_count();
+    if ((long long)m_tiles * ((n + 255) / 256) >= sms || n >= 4096) return 256;
+    if ((long long)m_tiles * ((n + 127) / 128) >= sms / 2 || n > 512) return 128;
+    return 64;
+}
+
+template <int BN, int EPI, int OUT>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+               cudaStream_t st) {
+    using Cfg = GemmCfg<BN>;
+    static bool configured[64] = {};
+    int dev = 0;
+    YB_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        YB_CUDA(cudaFuncSetAttribute(gemm_fp8_kernel<BN, EPI, OUT>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes));
+        configured[dev] = true;
+    }
+    gemm_fp8_kernel<BN, EPI, OUT><<<grid, kGemmThreads, Cfg::smem_bytes, st>>>(ta, tb, p);
+    return check_cuda(cudaGetLastError(), "gemm_fp8_kernel launch");
+}
+
+template <int BN, int EPI>
+int launch_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_kind,
+               int grid, cudaStream_t st) {
+    switch (out_kind) {
+        case Y_B200_F32: return launch_one<BN, EPI, Y_B200_F32>(ta, tb, p, grid, st);
+        case Y_B200_F16: return launch_one<BN, EPI, Y_B200_F16>(ta, tb, p, grid, st);
+        case Y_B200_BF16: return launch_one<BN, EPI, Y_B200_BF16>(ta, tb, p, grid, st);
+    }
+    return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad out_kind %d", out_kind);
+}
+
+template <int BN>
+int launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int epi,
+               int out_kind, int grid, cudaStream_t st) {
+    switch (epi) {
+        case Y_B200_EPI_NONE: return launch_out<BN, Y_B200_EPI_NONE>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS: return launch_out<BN, Y_B200_EPI_BIAS>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_RELU: return launch_out<BN, Y_B200_EPI_BIAS_RELU>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_SWIGLU:
+            if (out_kind != Y_B200_BF16)
+                return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: the SwiGLU epilogue writes bf16");
+            return launch_one<BN, Y_B200_EPI_SWIGLU, Y_B200_BF16>(ta, tb, p, grid, st);
+    }
+    return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad epilogue %d", epi);
+}
+
+int validate(const y_b200_gemm_fp8_args* a) {
+    if (!a) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: null argument block");
+    if (!a->a || !a->bt || !a->c) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: null operand pointer");
+    if (a->m < 1 || a->n < 1 || a->k < 1)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: M, N, K must be positive (M=%d N=%d K=%d)", a->m, a->n, a->k);
+    if (a->k % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: K=%d must be a multiple of 16 (operand rows are 16-byte aligned for TMA)", a->k);
+    if ((reinterpret_cast<uintptr_t>(a->a) & 15u) || (reinterpret_cast<uintptr_t>(a->bt) & 15u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_fp8: a and bt must be 16-byte aligned");
+    if (a->epilogue == Y_B200_EPI_BIAS || a->epilogue == Y_B200_EPI_BIAS_RELU) {
+        if (!a->bias) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bias epilogue without a bias pointer");
+        if (a->bias_kind != Y_B200_F16 && a->bias_kind != Y_B200_F32)
+            return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bias_kind must be F16 or F32");
+    }
+    if (a->epilogue == Y_B200_EPI_SWIGLU && a->n % 2 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: SwiGLU needs an even N (gate|up pairs), got %d", a->n);
+    if (a->cta_n != 0 && a->cta_n != 64 && a->cta_n != 128 && a->cta_n != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: cta_n must be 0, 64, 128 or 256");
+    return 0;
+}
+
+int smem_for(int bn) {
+    return bn == 256 ? GemmCfg<256>::smem_bytes : (bn == 128 ? GemmCfg<128>::smem_bytes : GemmCfg<64>::smem_bytes);
+}
+int stages_for(int bn) {
+    return bn == 256 ? GemmCfg<256>::stages : (bn == 128 ? GemmCfg<128>::stages : GemmCfg<64>::stages);
+}
+
+}  // namespace
+}  // namespace yb
+
+using namespace yb;
+
+extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
+    int rc = validate(a);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int bn = a->cta_n ? a->cta_n : pick_cta_n(a->m, a->n);
+    CUtensorMap ta, tb;
+    if ((rc = make_operand_map(&ta, a->a, a->m, a->k, kCtaM))) return rc;
+    if ((rc = make_operand_map(&tb, a->bt, a->n, a->k, bn))) return rc;
+    GemmParams p;
+    p.c = a->c;
+    p.m = a->m; p.n = a->n; p.k = a->k;
+    p.scale_a = a->scale_a; p.scale_b = a->scale_b;
+    p.scale_a_dev = a->scale_a_dev; p.scale_b_dev = a->scale_b_dev;
+    p.bias = a->bias; p.bias_kind = a->bias_kind;
+    p.amax_out = reinterpret_cast<unsigned int*>(a->amax_out);
+    p.status = device_status_ptr();
+    p.m_tiles = (a->m + kCtaM - 1) / kCtaM;
+    p.n_tiles = (a->n + bn - 1) / bn;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles > 0x7fffffffLL) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: too many tiles");
+    int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    switch (bn) {
+        case 256: return launch_epi<256>(ta, tb, p, a->epilogue, a->out_kind, grid, st);
+        case 128: return launch_epi<128>(ta, tb, p, a->epilogue, a->out_kind, grid, st);
+        default: return launch_epi<64>(ta, tb, p, a->epilogue, a->out_kind, grid, st);
+    }
+}
+
+extern "C" int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b200_launch_info* out) {
+    if (!out) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_launch_info: null output");
+    if (m < 1 || n < 1 || k < 1 || k % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8_launch_info: bad shape M=%d N=%d K=%d", m, n, k);
+    if (cta_n != 0 && cta_n != 64 && cta_n != 128 && cta_n != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_launch_info: cta_n must be 0, 64, 128 or 256");
+    const int bn = cta_n ? cta_n : pick_cta_n(m, n);
+    const long long tiles = (long long)((m + kCtaM - 1) / kCtaM) * ((n + bn - 1) / bn);
+    const int sms = sm_count();
+    out->grid[0] = (unsigned)(tiles < sms ? tiles : sms);
+    out->grid[1] = out->grid[2] = 1;
+    out->block[0] = kGemmThreads;
+    out->block[1] = out->block[2] = 1;
+    out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
+    out->dyn_smem_bytes = (unsigned)smem_for(bn);
+    out->workspace_bytes = 0;
+    out->cta_m = kCtaM; out->cta_n = bn; out->cta_k = kCtaK; out->stages = stages_for(bn);
+    return 0;
+}
+
+extern "C" size_t y_b200_gemm_fp8_f32_workspace_bytes(int m, int n, int k) {
+    if (m < 1 || n < 1 || k < 1) return 0;
+    // e4m3 A, e4m3 Bt (each rounded up to 256 bytes) and two scale slots.
+    const size_t a = ((size_t)m * k + 255) & ~(size_t)255, b = ((size_t)n * k + 255) & ~(size_t)255;
+    return a + b + 256;
+}
+
+extern "C" int y_b200_gemm_fp8_f32(const float* a, const float* b, float scale_a, float scale_b,
+                                   float* c, int m, int n, int k, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+    if (!a || !b || !c) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_f32: null pointer");
+    if (m < 1 || n < 1 || k < 1 || k % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8_f32: need M, N >= 1 and K %% 16 == 0 (M=%d N=%d K=%d)", m, n, k);
+    if (!(scale_a > 0.0f) || !(scale_b > 0.0f))
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_f32: scales must be positive");
+    const size_t need = y_b200_gemm_fp8_f32_workspace_bytes(m, n, k);
+    if (!workspace || workspace_bytes < need)
+        return fail(Y_B200_ERR_WORKSPACE, "y_b200_gemm_fp8_f32: workspace needs %zu bytes", need);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || (reinterpret_cast<uintptr_t>(a) & 15u) ||
+        (reinterpret_cast<uintptr_t>(b) & 15u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_fp8_f32: a, b need 16-byte and workspace 256-byte alignment");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    char* ws = static_cast<char*>(workspace);
+    const size_t a_bytes = ((size_t)m * k + 255) & ~(size_t)255, b_bytes = ((size_t)n * k + 255) & ~(size_t)255;
+    void* aq = ws;
+    void* bq = ws + a_bytes;
+    float* slots = reinterpret_cast<float*>(ws + a_bytes + b_bytes);
+    int rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, slots, aq, st);
+    if (rc) return rc;
+    rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, slots + 1, bq, st);
+    if (rc) return rc;
+    y_b200_gemm_fp8_args g = {};
+    g.a = aq; g.bt = bq; g.c = c;
+    g.m = m; g.n = n; g.k = k;
+    g.scale_a = scale_a; g.scale_b = scale_b;
+    g.epilogue = Y_B200_EPI_NONE;
+    g.out_kind = Y_B200_F32;
+    return y_b200_gemm_fp8(&g, stream);
+}
+
+extern "C" size_t y_b200_swiglu_workspace_bytes(int m, int n) {
+    if (m < 1 || n < 2) return 0;
+    return 256 + (size_t)m * (size_t)(n / 2) * 2;
+}
+
+extern "C" int y_b200_gemm_fp8_swiglu_requant(const y_b200_gemm_fp8_args* args, void* q,
+                                              float* scale_out, void* workspace,
+                                              size_t workspace_bytes, void* stream) {
+    if (!args || !q || !scale_out) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_swiglu_requant: null pointer");
+    const size_t need = y_b200_swiglu_workspace_bytes(args->m, args->n);
+    if (need == 0) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8_swiglu_requant: bad shape");
+    if (!workspace || workspace_bytes < need)
+        return fail(Y_B200_ERR_WORKSPACE, "y_b200_gemm_fp8_swiglu_requant: workspace needs %zu bytes", need);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || (reinterpret_cast<uintptr_t>(q) & 15u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_fp8_swiglu_requant: workspace needs 256-byte, q 16-byte alignment");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    float* amax = static_cast<float*>(workspace);
+    void* h = static_cast<char*>(workspace) + 256;
+    YB_CUDA(cudaMemsetAsync(amax, 0, sizeof(float), st));
+    y_b200_gemm_fp8_args g = *args;
+    g.c = h;
+    g.epilogue = Y_B200_EPI_SWIGLU;
+    g.out_kind = Y_B200_BF16;
+    g.amax_out = amax;
+    int rc = y_b200_gemm_fp8(&g, stream);
+    if (rc) return rc;
+    return quantize_from_amax(h, Y_B200_BF16, (size_t)args->m * (size_t)(args->n / 2), amax, q,
+                              scale_out, st);
+}

@@ -1,0 +1,372 @@
+// INT4 weight-only path: group quantise/pack, repack into the streaming layout,
+// and the small-M decode GEMM.
+//
+// The decode GEMM is HBM-bound weight streaming (K*N/2 bytes of weights read
+// exactly once), so it is built around keeping every SM's share of the stream
+// in flight from the first cycle: the streaming layout makes each CTA's share
+// one contiguous byte range, a producer warp issues it as 1-D bulk copies into
+// a shared-memory ring (up to ~165 KB outstanding per SM), and eight consumer
+// warps dequantise in registers and feed mma.sync.m16n8k16 (f16 x f16 -> f32)
+// with the weights as the 16-row operand and the M <= 32 tokens as the 8-wide
+// operand. The group scale multiplies each group's f32 partial sum, so the
+// integer weights enter the MMA exactly. K is split across the warps of a
+// CTA and reduced in shared memory in a fixed order: no atomics, results
+// overwrite the output and are run-to-run identical.
+#include "common.cuh"
+
+namespace yb {
+namespace {
+
+// ---- quantise -----------------------------------------------------------------
+// grid (N/2/128, K/128); thread = 2 adjacent columns of one 128-row group.
+__global__ void __launch_bounds__(128)
+    int4_quantize_kernel(const __half* __restrict__ w, size_t K, size_t N,
+                         uint32_t* __restrict__ qweight, __half* __restrict__ scales) {
+    const size_t n = 2 * ((size_t)blockIdx.x * 128 + threadIdx.x);
+    if (n >= N) return;
+    const size_t g = blockIdx.y;
+    const __half* base = w + g * 128 * N + n;
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int k = 0; k < 128; ++k) {
+        float2 f = __half22float2(*reinterpret_cast<const __half2*>(base + (size_t)k * N));
+        a0 = fmaxf(a0, fabsf(f.x));
+        a1 = fmaxf(a1, fabsf(f.y));
+    }
+    const __half h0 = __float2half_rn(__fdiv_rn(a0, 7.0f));
+    const __half h1 = __float2half_rn(__fdiv_rn(a1, 7.0f));
+    *reinterpret_cast<__half2*>(scales + g * N + n) = __halves2half2(h0, h1);
+    const float s0 = __half2float(h0), s1 = __half2float(h1);
+    for (int kw = 0; kw < 16; ++kw) {
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float2 f = __half22float2(
+                *reinterpret_cast<const __half2*>(base + (size_t)(kw * 8 + j) * N));
+            int q0 = 0, q1 = 0;
+            if (s0 > 0.0f) q0 = max(-8, min(7, __float2int_rn(__fdiv_rn(f.x, s0))));
+            if (s1 > 0.0f) q1 = max(-8, min(7, __float2int_rn(__fdiv_rn(f.y, s1))));
+            w0 |= ((uint32_t)q0 & 0xfu) << (4 * j);
+            w1 |= ((uint32_t)q1 & 0xfu) << (4 * j);
+        }
+        *reinterpret_cast<uint2*>(qweight + (g * 16 + kw) * N + n) = make_uint2(w0, w1);
+    }
+}
+
+// ---- repack ----------------------------------------------------------------------
+// Streaming layout: one 1056-byte block per (16-column tile, 128-row group),
+// tiles outermost. Bytes [0,1024): half h, lane, 16-byte unit of four words;
+// with gq = lane/4, c = lane%4, word i holds the eight K-consecutive weights
+// k = 128g + 32(2h + i/2) + 8c + (0..7) of column 16*tile + gq + 8(i%2),
+// offset-binary (q+8), logical element j at nibble {0,4,1,5,2,6,3,7}[j].
+// Bytes [1024,1056): the tile's 16 f16 group scales.
+constexpr int kBlkBytes = 1056;
+constexpr int kBlkWords = kBlkBytes / 4;  // 264
+
+__global__ void __launch_bounds__(256)
+    int4_repack_kernel(const uint32_t* __restrict__ qweight, const uint16_t* __restrict__ scales,
+                       size_t ngroups, size_t N, size_t total_words,
+                       uint32_t* __restrict__ stream) {
+    for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total_words;
+         idx += (size_t)gridDim.x * 256) {
+        const size_t blk = idx / kBlkWords;
+        const int wi = (int)(idx % kBlkWords);
+        const size_t t = blk / ngroups, g = blk % ngroups;
+        uint32_t outw;
+        if (wi < 256) {
+            const int h = wi / 128, lane = (wi % 128) / 4, i = wi % 4;
+            const int gq = lane / 4, c = lane % 4;
+            const size_t kw = g * 16 + (size_t)(4 * (2 * h + i / 2) + c);
+            const size_t col = t * 16 + (size_t)(gq + 8 * (i % 2));
+            const uint32_t src = qweight[kw * N + col] ^ 0x88888888u;
+            // nibble positions 0,4,1,5,2,6,3,7 for logical elements 0..7
+            outw = (src & 0xfu) | ((src >> 4) & 0xfu) << 16 | ((src >> 8) & 0xfu) << 4 |
+                   ((src >> 12) & 0xfu) << 20 | ((src >> 16) & 0xfu) << 8 |
+                   ((src >> 20) & 0xfu) << 24 | ((src >> 24) & 0xfu) << 12 |
+                   ((src >> 28) & 0xfu) << 28;
+        } else {
+            const int sp = wi - 256;  // scale pair 0..7
+            const uint16_t* s = scales + g * N + t * 16 + 2 * sp;
+            outw = (uint32_t)s[0] | ((uint32_t)s[1] << 16);
+        }
+        stream[idx] = outw;
+    }
+}
+
+// ---- decode GEMM ------------------------------------------------------------------
+constexpr int kConsumerWarps = 8;
+constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
+constexpr int kUnitGroups = 8;                         // one group per consumer warp
+constexpr int kUnitBytes = kUnitGroups * kBlkBytes;    // 8448
+constexpr int kRoundTiles = 5;                         // 16-column tiles kept in registers
+
+template <int NT>
+struct DecodeCfg {
+    static constexpr int slots = NT == 4 ? 16 : 20;
+    static constexpr int red_floats = kConsumerWarps * kRoundTiles * NT * 128;
+    static constexpr int ring_bytes = slots * kUnitBytes;
+    static constexpr int smem_bytes = ring_bytes + red_floats * 4 + 2 * slots * 8 + 16;
+};
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// (w & 0x000F000F) | 0x6400 per half = 1024 + u; minus 1032 gives u - 8.
+__device__ __forceinline__ uint32_t deq_lo(uint32_t w) {
+    uint32_t h = (w & 0x000f000fu) | 0x64006400u;
+    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&h), __half2_raw{0x6408, 0x6408});
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+// (w & 0x00F000F0) | 0x6400 per half = 1024 + 16u; times 1/16 minus 72 gives u - 8.
+__device__ __forceinline__ uint32_t deq_hi(uint32_t w) {
+    uint32_t h = (w & 0x00f000f0u) | 0x64006400u;
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&h), __half2_raw{0x2c00, 0x2c00},
+                        __half2_raw{0xd480, 0xd480});
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__device__ __forceinline__ void consumer_bar() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kDecodeThreads, 1)
+    int4_decode_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ wstream,
+                       __half* __restrict__ out, int M, int N, int K, DeviceStatus* status) {
+    using Cfg = DecodeCfg<NT>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;
+    float* red = reinterpret_cast<float*>(smem + Cfg::ring_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::ring_bytes + Cfg::red_floats * 4);
+    volatile uint32_t* abort_flag =
+        reinterpret_cast<volatile uint32_t*>(smem + Cfg::ring_bytes + Cfg::red_floats * 4 +
+                                             2 * Cfg::slots * 8);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + Cfg::slots);
+    const uint32_t ring0 = smem_u32(ring);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::slots; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, kConsumerWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int ngroups = K / 128;
+    const int phases = (ngroups + kUnitGroups - 1) / kUnitGroups;
+    const int T = N / 16;
+    const int t_begin = (int)(((long long)blockIdx.x * T) / gridDim.x);
+    const int t_end = (int)(((long long)(blockIdx.x + 1) * T) / gridDim.x);
+
+    if (warp == kConsumerWarps) {
+        // ---- producer: stream this CTA's contiguous share through the ring ----
+        if (lane == 0) {
+            uint32_t unit = 0;
+            bool ok = true;
+            for (int r0 = t_begin; r0 < t_end && ok; r0 += kRoundTiles) {
+                const int rt = min(kRoundTiles, t_end - r0);
+                for (int p = 0; p < phases && ok; ++p) {
+                    const int ng = min(kUnitGroups, ngroups - p * kUnitGroups);
+                    for (int t = 0; t < rt; ++t, ++unit) {
+                        const uint32_t s = unit % Cfg::slots, ph = (unit / Cfg::slots) & 1u;
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) {
+                            report_timeout(status, abort_flag, 0x100u, unit);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t bytes = (uint32_t)ng * kBlkBytes;
+                        mbar_expect_tx(full0 + 8 * s, bytes);
+                        bulk_load_1d(ring0 + s * kUnitBytes,
+                                     wstream + ((size_t)(r0 + t) * ngroups + (size_t)p * kUnitGroups) *
+                                                   kBlkBytes,
+                                     bytes, full0 + 8 * s);
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- consumers -------------------------------------------------------
+        const int gq = lane >> 2, c = lane & 3;
+        uint32_t unit = 0;
+        bool dead = false;
+        for (int r0 = t_begin; r0 < t_end; r0 += kRoundTiles) {
+            const int rt = min(kRoundTiles, t_end - r0);
+            float acc[kRoundTiles][NT][4];
+#pragma unroll
+            for (int t = 0; t < kRoundTiles; ++t)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[t][j][i] = 0.0f;
+
+            for (int p = 0; p < phases; ++p) {
+                const int g = p * kUnitGroups + warp;
+                const bool valid = g < ngroups;
+                // Activation fragments of this warp's group: token gq + 8j,
+                // k = 128g + 32pp + 8c + (0..7).
+                uint4 xf[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int tok = gq + 8 * j;
+#pragma unroll
+                    for (int pp = 0; pp < 4; ++pp) {
+                        xf[j][pp] = make_uint4(0, 0, 0, 0);
+                        if (valid && tok < M)
+                            xf[j][pp] = __ldg(reinterpret_cast<const uint4*>(
+                                x + (size_t)tok * K + (size_t)g * 128 + pp * 32 + c * 8));
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < kRoundTiles; ++t) {
+                    if (t < rt) {
+                        const uint32_t s = unit % Cfg::slots, ph = (unit / Cfg::slots) & 1u;
+                        if (!dead && !mbar_wait(full0 + 8 * s, ph, abort_flag)) {
+                            report_timeout(status, abort_flag, 0x200u + warp, unit);
+                            dead = true;
+                        }
+                        if (valid && !dead) {
+                            const uint8_t* blk = ring + s * kUnitBytes + warp * kBlkBytes;
+                            const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
+                            const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
+                            const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
+                            const float s_lo = __half2float(sc[gq]);
+                            const float s_hi = __half2float(sc[gq + 8]);
+                            const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
+                            const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
+                            float tmp[NT][4];
+#pragma unroll
+                            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) tmp[j][i] = 0.0f;
+#pragma unroll
+                            for (int pp = 0; pp < 4; ++pp) {
+                                const uint32_t a0 = deq_lo(wA[pp]), a1 = deq_lo(wB[pp]);
+                                const uint32_t a2 = deq_hi(wA[pp]), a3 = deq_hi(wB[pp]);
+                                const uint32_t e0 = deq_lo(wA[pp] >> 8), e1 = deq_lo(wB[pp] >> 8);
+                                const uint32_t e2 = deq_hi(wA[pp] >> 8), e3 = deq_hi(wB[pp] >> 8);
+#pragma unroll
+                                for (int j = 0; j < NT; ++j) {
+                                    mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
+                                    mma_16816(tmp[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < NT; ++j) {
+                                acc[t][j][0] = fmaf(s_lo, tmp[j][0], acc[t][j][0]);
+                                acc[t][j][1] = fmaf(s_lo, tmp[j][1], acc[t][j][1]);
+                                acc[t][j][2] = fmaf(s_hi, tmp[j][2], acc[t][j][2]);
+                                acc[t][j][3] = fmaf(s_hi, tmp[j][3], acc[t][j][3]);
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                        ++unit;
+                    }
+                }
+            }
+
+            // ---- cross-warp reduction in warp order, then store --------------
+            float* mine = red + (size_t)warp * (kRoundTiles * NT * 128);
+#pragma unroll
+            for (int t = 0; t < kRoundTiles; ++t)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+                    *reinterpret_cast<float4*>(mine + (t * NT + j) * 128 + lane * 4) =
+                        make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
+            consumer_bar();
+            const int nout = rt * NT * 128;
+            for (int e = threadIdx.x; e < nout; e += kConsumerWarps * 32) {
+                float v = red[e];
+#pragma unroll
+                for (int w = 1; w < kConsumerWarps; ++w) v += red[w * (kRoundTiles * NT * 128) + e];
+                const int t = e / (NT * 128), j = (e / 128) % NT, l = (e % 128) / 4, i = e % 4;
+                const int col = (r0 + t) * 16 + (l >> 2) + 8 * (i >> 1);
+                const int tok = 8 * j + 2 * (l & 3) + (i & 1);
+                if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
+            }
+            consumer_bar();
+        }
+    }
+}
+
+template <int NT>
+int launch_decode(const void* x, const void* wstream, void* out, int m, int n, int k,
+                  cudaStream_t st) {
+    using Cfg = DecodeCfg<NT>;
+    static bool configured[64] = {};
+    int dev = 0;
+    YB_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        YB_CUDA(cudaFuncSetAttribute(int4_decode_kernel<NT>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes));
+        configured[dev] = true;
+    }
+    const int tiles = n / 16;
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    int4_decode_kernel<NT><<<grid, kDecodeThreads, Cfg::smem_bytes, st>>>(
+        static_cast<const __half*>(x), static_cast<const uint8_t*>(wstream),
+        static_cast<__half*>(out), m, n, k, device_status_ptr());
+    return check_cuda(cudaGetLastError(), "int4_decode_kernel launch");
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace yb
+
+using namespace yb;
+
+extern "C" int y_b200_int4_quantize(const void* w_f16, size_t k, size_t n, uint32_t* qweight,
+                                    void* scales_f16, void* stream) {
+    if (!w_f16 || !qweight || !scales_f16) return fail(Y_B200_ERR_INVALID, "y_b200_int4_quantize: null pointer");
+    if (k == 0 || k % 128 != 0 || n == 0 || n % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_int4_quantize: need K %% 128 == 0 and N %% 16 == 0 (K=%zu N=%zu)", k, n);
+    if (!aligned16(w_f16) || !aligned16(qweight) || !aligned16(scales_f16))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_int4_quantize: pointers must be 16-byte aligned");
+    dim3 grid((unsigned)((n / 2 + 127) / 128), (unsigned)(k / 128));
+    int4_quantize_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(w_f16), k, n, qweight, static_cast<__half*>(scales_f16));
+    return check_cuda(cudaGetLastError(), "int4_quantize_kernel launch");
+}
+
+extern "C" size_t y_b200_int4_stream_bytes(size_t k, size_t n) {
+    return (n / 16) * (k / 128) * (size_t)kBlkBytes;
+}
+
+extern "C" int y_b200_int4_repack(const uint32_t* qweight, const void* scales_f16, size_t k,
+                                  size_t n, void* wstream, void* stream) {
+    if (!qweight || !scales_f16 || !wstream) return fail(Y_B200_ERR_INVALID, "y_b200_int4_repack: null pointer");
+    if (k == 0 || k % 128 != 0 || n == 0 || n % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_int4_repack: need K %% 128 == 0 and N %% 16 == 0 (K=%zu N=%zu)", k, n);
+    if (!aligned16(wstream)) return fail(Y_B200_ERR_ALIGN, "y_b200_int4_repack: wstream must be 16-byte aligned");
+    const size_t words = y_b200_int4_stream_bytes(k, n) / 4;
+    size_t blocks = (words + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    int4_repack_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        qweight, static_cast<const uint16_t*>(scales_f16), k / 128, n, words,
+        static_cast<uint32_t*>(wstream));
+    return check_cuda(cudaGetLastError(), "int4_repack_kernel launch");
+}
+
+extern "C" int y_b200_gemm_int4_decode(const void* x_f16, const void* wstream, void* out_f16, int m,
+                                       int n, int k, void* stream) {
+    if (!x_f16 || !wstream || !out_f16) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_int4_decode: null pointer");
+    if (m < 1 || m > 32) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_int4_decode: M=%d outside 1..32", m);
+    if (k <= 0 || k % 128 != 0 || n <= 0 || n % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_int4_decode: need K %% 128 == 0 and N %% 16 == 0 (K=%d N=%d)", k, n);
+    if (!aligned16(x_f16) || !aligned16(wstream))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_int4_decode: x and wstream must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (m <= 8) return launch_decode<1>(x_f16, wstream, out_f16, m, n, k, st);
+    if (m <= 16) return launch_decode<2>(x_f16, wstream, out_f16, m, n, k, st);
+    return launch_decode<4>(x_f16, wstream, out_f16, m, n, k, st);
+}

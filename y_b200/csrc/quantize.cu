@@ -1,0 +1,455 @@
+// HBM-bound kernels of the FP8 path: abs-max reduce, e4m3 quantise (plain and
+// transposed), RMSNorm -> e4m3 prologue, and the device-side input generator.
+// All global traffic is 128-bit per thread; reductions are warp-shuffle plus
+// one atomic per CTA on the f32 bit pattern (non-negative floats order like
+// unsigned integers, so max needs no floating-point atomics and is exact).
+#include "common.cuh"
+
+namespace yb {
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---- loads of 8 elements as f32 ---------------------------------------------
+template <int KIND>
+struct Elem;
+template <>
+struct Elem<Y_B200_F16> {
+    __device__ static void load8(const void* p, size_t i, float (&v)[8]) {
+        uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __half*>(p) + i);
+        const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 f = __half22float2(h[j]);
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        }
+    }
+    __device__ static float load1(const void* p, size_t i) {
+        return __half2float(static_cast<const __half*>(p)[i]);
+    }
+};
+template <>
+struct Elem<Y_B200_BF16> {
+    __device__ static void load8(const void* p, size_t i, float (&v)[8]) {
+        uint4 u = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + i);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    }
+    __device__ static float load1(const void* p, size_t i) {
+        return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+    }
+};
+template <>
+struct Elem<Y_B200_F32> {
+    __device__ static void load8(const void* p, size_t i, float (&v)[8]) {
+        const float4* q = reinterpret_cast<const float4*>(static_cast<const float*>(p) + i);
+        float4 a = q[0], b = q[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    __device__ static float load1(const void* p, size_t i) {
+        return static_cast<const float*>(p)[i];
+    }
+};
+
+__device__ __forceinline__ void block_atomic_max(float local, unsigned int* out) {
+    __shared__ unsigned int warp_max[kThreads / 32];
+    unsigned int bits = __float_as_uint(local);  // local >= 0
+    bits = warp_max_u32(bits);
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = bits;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        unsigned int v = threadIdx.x < kThreads / 32 ? warp_max[threadIdx.x] : 0u;
+        v = warp_max_u32(v);
+        if (threadIdx.x == 0 && v != 0u) atomicMax(out, v);
+    }
+}
+
+// ---- amax ----------------------------------------------------------------------
+// n8 = number of aligned 8-element vectors; the scalar tail [n8*8, n) is folded
+// in by the first threads of block 0.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) amax_kernel(const void* __restrict__ x, size_t n,
+                                                        unsigned int* __restrict__ out) {
+    const size_t n8 = n / 8;
+    float m = 0.0f;
+    for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n8;
+         v += (size_t)gridDim.x * kThreads) {
+        float f[8];
+        Elem<KIND>::load8(x, v * 8, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[j]));
+    }
+    if (blockIdx.x == 0) {
+        size_t i = n8 * 8 + threadIdx.x;
+        if (i < n) m = fmaxf(m, fabsf(Elem<KIND>::load1(x, i)));
+    }
+    block_atomic_max(m, out);
+}
+
+__global__ void scale_from_amax_kernel(const float* amax, float* scale) {
+    scale[0] = scale_from_amax(amax[0]);
+}
+
+// ---- quantise --------------------------------------------------------------------
+// SCALE_IS_AMAX: `s` points at an amax; the scale is derived on the fly and
+// thread 0 publishes it to scale_out.
+template <int KIND, bool SCALE_IS_AMAX>
+__global__ void __launch_bounds__(kThreads)
+    quantize_kernel(const void* __restrict__ x, size_t n, const float* __restrict__ s,
+                    uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+    const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
+    const float inv = inv_scale(scale);
+    if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
+        scale_out[0] = scale;
+    const size_t n16 = n / 16;
+    for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n16;
+         v += (size_t)gridDim.x * kThreads) {
+        float a[8], b[8];
+        Elem<KIND>::load8(x, v * 16, a);
+        Elem<KIND>::load8(x, v * 16 + 8, b);
+        uint4 o;
+        o.x = cvt_e4m3x4(__fmul_rn(a[0], inv), __fmul_rn(a[1], inv), __fmul_rn(a[2], inv),
+                         __fmul_rn(a[3], inv));
+        o.y = cvt_e4m3x4(__fmul_rn(a[4], inv), __fmul_rn(a[5], inv), __fmul_rn(a[6], inv),
+                         __fmul_rn(a[7], inv));
+        o.z = cvt_e4m3x4(__fmul_rn(b[0], inv), __fmul_rn(b[1], inv), __fmul_rn(b[2], inv),
+                         __fmul_rn(b[3], inv));
+        o.w = cvt_e4m3x4(__fmul_rn(b[4], inv), __fmul_rn(b[5], inv), __fmul_rn(b[6], inv),
+                         __fmul_rn(b[7], inv));
+        *reinterpret_cast<uint4*>(q + v * 16) = o;
+    }
+    if (blockIdx.x == 0) {
+        size_t i = n16 * 16 + threadIdx.x;
+        if (i < n) q[i] = (uint8_t)(cvt_e4m3x2(__fmul_rn(Elem<KIND>::load1(x, i), inv), 0.0f) & 0xff);
+    }
+}
+
+// ---- transposed quantise -----------------------------------------------------------
+// x [rows, cols] -> q [cols, rows]. One CTA moves a 128(row) x 64(col) tile
+// through shared memory so both the reads (along cols) and the writes (along
+// rows) are contiguous. Edges are handled element-wise.
+constexpr int kTR = 128, kTC = 64;
+template <int KIND, bool SCALE_IS_AMAX>
+__global__ void __launch_bounds__(kThreads)
+    quantize_transpose_kernel(const void* __restrict__ x, size_t rows, size_t cols,
+                              const float* __restrict__ s, uint8_t* __restrict__ q,
+                              float* __restrict__ scale_out) {
+    __shared__ __align__(16) uint8_t tile[kTC][kTR + 16];
+    const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
+    const float inv = inv_scale(scale);
+    if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&
+        threadIdx.x == 0)
+        scale_out[0] = scale;
+    const size_t r0 = (size_t)blockIdx.y * kTR, c0 = (size_t)blockIdx.x * kTC;
+    const bool vec_in = (cols % 8 == 0);
+    // 128 rows x 8 column-vectors = 1024 vector slots, 4 per thread.
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        int slot = it * kThreads + threadIdx.x;
+        int r = slot / 8, cv = slot % 8;
+        size_t gr = r0 + r, gc = c0 + (size_t)cv * 8;
+        float f[8];
+        if (gr < rows && vec_in && gc + 8 <= cols) {
+            Elem<KIND>::load8(x, gr * cols + gc, f);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                f[j] = (gr < rows && gc + j < cols) ? Elem<KIND>::load1(x, gr * cols + gc + j) : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            tile[cv * 8 + j][r] = (uint8_t)(cvt_e4m3x2(__fmul_rn(f[j], inv), 0.0f) & 0xff);
+    }
+    __syncthreads();
+    // 64 output rows x 8 sixteen-byte vectors = 512 slots, 2 per thread.
+    const bool vec_out = (rows % 16 == 0);
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        int slot = it * kThreads + threadIdx.x;
+        int c = slot / 8, rv = slot % 8;
+        size_t gc = c0 + c, gr = r0 + (size_t)rv * 16;
+        if (gc >= cols) continue;
+        if (vec_out && gr + 16 <= rows) {
+            *reinterpret_cast<uint4*>(q + gc * rows + gr) =
+                *reinterpret_cast<const uint4*>(&tile[c][rv * 16]);
+        } else {
+            for (int j = 0; j < 16; ++j)
+                if (gr + j < rows) q[gc * rows + gr + j] = tile[c][rv * 16 + j];
+        }
+    }
+}
+
+// ---- RMSNorm -> e4m3 ------------------------------------------------------------------
+// One 256-thread CTA per row. The sum of squares follows a FIXED order so the
+// result can be reproduced bit for bit on a CPU: thread t folds the 8-element
+// vectors t, t+256, ... with fma(x, x, acc); each warp adds its 32 partials by
+// butterfly (xor 16, 8, 4, 2, 1); the eight warp totals are added in warp
+// order; mean = total / hidden; rstd = 1 / sqrt(mean + eps) with correctly
+// rounded division and square root. y = (x * rstd) * gamma.
+__device__ __forceinline__ float rms_row_rstd(const __half* __restrict__ xr, size_t hidden,
+                                              float eps) {
+    __shared__ float warp_tot[8];
+    const size_t nvec = hidden / 8;
+    float acc = 0.0f;
+    for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
+        float f[8];
+        Elem<Y_B200_F16>::load8(xr, v * 8, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = __fmaf_rn(f[j], f[j], acc);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+        acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+    if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    float total = warp_tot[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) total = __fadd_rn(total, warp_tot[w]);
+    const float mean = __fdiv_rn(total, (float)hidden);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+}
+
+__global__ void __launch_bounds__(kThreads)
+    rmsnorm_stats_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma,
+                         size_t hidden, float eps, float* __restrict__ rstd_out,
+                         unsigned int* __restrict__ amax_out) {
+    const __half* xr = x + (size_t)blockIdx.x * hidden;
+    const float rstd = rms_row_rstd(xr, hidden, eps);
+    if (threadIdx.x == 0) rstd_out[blockIdx.x] = rstd;
+    float m = 0.0f;
+    const size_t nvec = hidden / 8;
+    for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
+        float f[8], g[8];
+        Elem<Y_B200_F16>::load8(xr, v * 8, f);
+        Elem<Y_B200_F16>::load8(gamma, v * 8, g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(__fmul_rn(__fmul_rn(f[j], rstd), g[j])));
+    }
+    block_atomic_max(m, amax_out);
+}
+
+__global__ void __launch_bounds__(kThreads)
+    rmsnorm_quantize_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma,
+                            size_t hidden, const float* __restrict__ rstd_in,
+                            const float* __restrict__ amax, uint8_t* __restrict__ q,
+                            float* __restrict__ scale_out) {
+    const float scale = scale_from_amax(amax[0]);
+    const float inv = inv_scale(scale);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out != nullptr) scale_out[0] = scale;
+    const __half* xr = x + (size_t)blockIdx.x * hidden;
+    uint8_t* qr = q + (size_t)blockIdx.x * hidden;
+    const float rstd = rstd_in[blockIdx.x];
+    const size_t nvec = hidden / 8;
+    for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
+        float f[8], g[8];
+        Elem<Y_B200_F16>::load8(xr, v * 8, f);
+        Elem<Y_B200_F16>::load8(gamma, v * 8, g);
+        float y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = __fmul_rn(__fmul_rn(__fmul_rn(f[j], rstd), g[j]), inv);
+        uint2 o;
+        o.x = cvt_e4m3x4(y[0], y[1], y[2], y[3]);
+        o.y = cvt_e4m3x4(y[4], y[5], y[6], y[7]);
+        *reinterpret_cast<uint2*>(qr + v * 8) = o;
+    }
+}
+
+// ---- input generator --------------------------------------------------------------------
+__device__ __forceinline__ uint64_t splitmix64(uint64_t index, uint64_t seed) {
+    uint64_t z = index * 0x9E3779B97F4A7C15ull + seed + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__global__ void fill_random_f16_kernel(uint16_t* out, size_t n, uint64_t index0, uint64_t seed) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        uint64_t z = splitmix64(index0 + i, seed);
+        uint16_t sign = (uint16_t)((z >> 63) & 1u);
+        uint16_t exp = (uint16_t)(12u + (uint16_t)((z >> 40) & 0x3u) % 3u);
+        out[i] = (uint16_t)((sign << 15) | (exp << 10) | (uint16_t)(z & 0x3ffu));
+    }
+}
+
+int grid_for(size_t work_items) {
+    size_t want = (work_items + kThreads - 1) / kThreads;
+    size_t cap = (size_t)sm_count() * 8;
+    if (want < 1) want = 1;
+    return (int)(want < cap ? want : cap);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int kind_ok(int kind) { return kind == Y_B200_F32 || kind == Y_B200_F16 || kind == Y_B200_BF16; }
+
+template <bool IS_AMAX>
+int launch_quantize(const void* x, int kind, size_t n, const float* s, void* q, float* scale_out,
+                    cudaStream_t st) {
+    int grid = grid_for(n / 16 + 1);
+    uint8_t* qq = static_cast<uint8_t*>(q);
+    switch (kind) {
+        case Y_B200_F16:
+            quantize_kernel<Y_B200_F16, IS_AMAX><<<grid, kThreads, 0, st>>>(x, n, s, qq, scale_out);
+            break;
+        case Y_B200_BF16:
+            quantize_kernel<Y_B200_BF16, IS_AMAX><<<grid, kThreads, 0, st>>>(x, n, s, qq, scale_out);
+            break;
+        default:
+            quantize_kernel<Y_B200_F32, IS_AMAX><<<grid, kThreads, 0, st>>>(x, n, s, qq, scale_out);
+            break;
+    }
+    return check_cuda(cudaGetLastError(), "quantize_kernel launch");
+}
+
+template <bool IS_AMAX>
+int launch_quantize_t(const void* x, int kind, size_t rows, size_t cols, const float* s, void* q,
+                      float* scale_out, cudaStream_t st) {
+    dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
+    uint8_t* qq = static_cast<uint8_t*>(q);
+    switch (kind) {
+        case Y_B200_F16:
+            quantize_transpose_kernel<Y_B200_F16, IS_AMAX>
+                <<<grid, kThreads, 0, st>>>(x, rows, cols, s, qq, scale_out);
+            break;
+        case Y_B200_BF16:
+            quantize_transpose_kernel<Y_B200_BF16, IS_AMAX>
+                <<<grid, kThreads, 0, st>>>(x, rows, cols, s, qq, scale_out);
+            break;
+        default:
+            quantize_transpose_kernel<Y_B200_F32, IS_AMAX>
+                <<<grid, kThreads, 0, st>>>(x, rows, cols, s, qq, scale_out);
+            break;
+    }
+    return check_cuda(cudaGetLastError(), "quantize_transpose_kernel launch");
+}
+
+int launch_amax(const void* x, int kind, size_t n, float* amax_out, cudaStream_t st) {
+    YB_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
+    int grid = grid_for(n / 8 + 1);
+    unsigned int* out = reinterpret_cast<unsigned int*>(amax_out);
+    switch (kind) {
+        case Y_B200_F16: amax_kernel<Y_B200_F16><<<grid, kThreads, 0, st>>>(x, n, out); break;
+        case Y_B200_BF16: amax_kernel<Y_B200_BF16><<<grid, kThreads, 0, st>>>(x, n, out); break;
+        default: amax_kernel<Y_B200_F32><<<grid, kThreads, 0, st>>>(x, n, out); break;
+    }
+    return check_cuda(cudaGetLastError(), "amax_kernel launch");
+}
+
+}  // namespace
+
+// Internal entry used by the f32 drop-in GEMM (by-value scale from the host).
+int quantize_with_host_scale(const void* x, int kind, size_t rows, size_t cols, bool transpose,
+                             float scale, float* scale_slot, void* q, cudaStream_t st) {
+    YB_CUDA(cudaMemcpyAsync(scale_slot, &scale, sizeof(float), cudaMemcpyHostToDevice, st));
+    if (transpose) return launch_quantize_t<false>(x, kind, rows, cols, scale_slot, q, nullptr, st);
+    return launch_quantize<false>(x, kind, rows * cols, scale_slot, q, nullptr, st);
+}
+
+// Internal: requantise with the scale derived from an amax word.
+int quantize_from_amax(const void* x, int kind, size_t n, const float* amax, void* q,
+                       float* scale_out, cudaStream_t st) {
+    return launch_quantize<true>(x, kind, n, amax, q, scale_out, st);
+}
+
+}  // namespace yb
+
+using namespace yb;
+
+extern "C" int y_b200_amax(const void* x, int x_kind, size_t n, float* amax_out, void* stream) {
+    if (!x || !amax_out) return fail(Y_B200_ERR_INVALID, "y_b200_amax: null pointer");
+    if (!kind_ok(x_kind)) return fail(Y_B200_ERR_INVALID, "y_b200_amax: bad element kind %d", x_kind);
+    if (!aligned16(x)) return fail(Y_B200_ERR_ALIGN, "y_b200_amax: x must be 16-byte aligned");
+    return launch_amax(x, x_kind, n, amax_out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int y_b200_scale_from_amax(const float* amax, float* scale_out, void* stream) {
+    if (!amax || !scale_out) return fail(Y_B200_ERR_INVALID, "y_b200_scale_from_amax: null pointer");
+    scale_from_amax_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(amax, scale_out);
+    return check_cuda(cudaGetLastError(), "scale_from_amax_kernel launch");
+}
+
+extern "C" int y_b200_quantize_fp8(const void* x, int x_kind, size_t n, const float* scale, void* q,
+                                   void* stream) {
+    if (!x || !scale || !q) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8: null pointer");
+    if (!kind_ok(x_kind)) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8: bad element kind %d", x_kind);
+    if (!aligned16(x) || !aligned16(q))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_quantize_fp8: x and q must be 16-byte aligned");
+    return launch_quantize<false>(x, x_kind, n, scale, q, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int y_b200_quantize_fp8_transpose(const void* x, int x_kind, size_t rows, size_t cols,
+                                             const float* scale, void* q, void* stream) {
+    if (!x || !scale || !q) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8_transpose: null pointer");
+    if (!kind_ok(x_kind)) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8_transpose: bad element kind %d", x_kind);
+    if (rows == 0 || cols == 0) return Y_B200_OK;
+    if (!aligned16(x) || !aligned16(q))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_quantize_fp8_transpose: x and q must be 16-byte aligned");
+    return launch_quantize_t<false>(x, x_kind, rows, cols, scale, q, nullptr,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int y_b200_quantize_fp8_dynamic(const void* x, int x_kind, size_t rows, size_t cols,
+                                           int transpose, void* q, float* scale_out, void* stream) {
+    if (!x || !q || !scale_out) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8_dynamic: null pointer");
+    if (!kind_ok(x_kind)) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8_dynamic: bad element kind %d", x_kind);
+    if (!aligned16(x) || !aligned16(q))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_quantize_fp8_dynamic: x and q must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // scale_out holds the amax while the quantise kernel runs (every CTA reads
+    // it, none writes it); a last one-thread kernel turns it into the scale.
+    int rc = launch_amax(x, x_kind, rows * cols, scale_out, st);
+    if (rc) return rc;
+    if (transpose && rows != 0 && cols != 0)
+        rc = launch_quantize_t<true>(x, x_kind, rows, cols, scale_out, q, nullptr, st);
+    else
+        rc = launch_quantize<true>(x, x_kind, rows * cols, scale_out, q, nullptr, st);
+    if (rc) return rc;
+    scale_from_amax_kernel<<<1, 1, 0, st>>>(scale_out, scale_out);
+    return check_cuda(cudaGetLastError(), "scale_from_amax_kernel launch");
+}
+
+extern "C" size_t y_b200_rmsnorm_workspace_bytes(size_t rows) { return rows * sizeof(float) + 256; }
+
+extern "C" int y_b200_rmsnorm_quantize_fp8(const void* x_f16, const void* gamma_f16, size_t rows,
+                                           size_t hidden, float eps, void* q, float* scale_out,
+                                           void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x_f16 || !gamma_f16 || !q || !scale_out)
+        return fail(Y_B200_ERR_INVALID, "y_b200_rmsnorm_quantize_fp8: null pointer");
+    if (hidden == 0 || hidden % 8 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_rmsnorm_quantize_fp8: hidden=%zu must be a positive multiple of 8", hidden);
+    if (!workspace || workspace_bytes < y_b200_rmsnorm_workspace_bytes(rows))
+        return fail(Y_B200_ERR_WORKSPACE, "y_b200_rmsnorm_quantize_fp8: workspace needs %zu bytes",
+                    y_b200_rmsnorm_workspace_bytes(rows));
+    if (!aligned16(x_f16) || !aligned16(gamma_f16) || !aligned16(q) || !aligned16(workspace))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_rmsnorm_quantize_fp8: pointers must be 16-byte aligned");
+    if (rows == 0) return Y_B200_OK;
+    if (rows > 0x7fffffffu) return fail(Y_B200_ERR_SHAPE, "y_b200_rmsnorm_quantize_fp8: too many rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // workspace: [0,256) amax word, then rows floats of rstd.
+    unsigned int* amax = static_cast<unsigned int*>(workspace);
+    float* rstd = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
+    YB_CUDA(cudaMemsetAsync(amax, 0, sizeof(unsigned int), st));
+    rmsnorm_stats_kernel<<<(unsigned)rows, kThreads, 0, st>>>(
+        static_cast<const __half*>(x_f16), static_cast<const __half*>(gamma_f16), hidden, eps, rstd,
+        amax);
+    YB_CUDA(cudaGetLastError());
+    rmsnorm_quantize_kernel<<<(unsigned)rows, kThreads, 0, st>>>(
+        static_cast<const __half*>(x_f16), static_cast<const __half*>(gamma_f16), hidden, rstd,
+        reinterpret_cast<const float*>(amax), static_cast<uint8_t*>(q), scale_out);
+    return check_cuda(cudaGetLastError(), "rmsnorm_quantize_kernel launch");
+}
+
+extern "C" int y_b200_fill_random_f16(void* out_f16, size_t n, uint64_t index0, uint64_t seed,
+                                      void* stream) {
+    if (!out_f16) return fail(Y_B200_ERR_INVALID, "y_b200_fill_random_f16: null pointer");
+    if (n == 0) return Y_B200_OK;
+    fill_random_f16_kernel<<<grid_for(n), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t*>(out_f16), n, index0, seed);
+    return check_cuda(cudaGetLastError(), "fill_random_f16_kernel launch");
+}
