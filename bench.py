@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Benchmark of the quantised-inference GEMM path on 1..8 B200s.
+
+One "step" is one pass of the hot path over one batch of synthetic input, on
+the column-parallel configuration: X [8192, 8192] f16 -> fused RMSNorm
+(eps 1e-6, gamma ~ U(0.5, 1.5)) -> per-tensor e4m3 quantisation -> FP8 GEMM
+against this GPU's weight shard Bt [8192 (N shard), 8192 (K)] e4m3 -> bf16 C.
+Each GPU keeps its own weight shard (weak scaling along N); the weights are
+quantised once, before the timed region, with one scale agreed across ranks.
+The all-gather of C is measured separately and reported under "gather".
+
+Prints ONE JSON line (rank 0). `--impl reference` times the CPU restatement of
+the same step on the host cores instead (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = K = 8192
+N_SHARD = 8192
+EPS = 1e-6
+METRIC = "fp8_gemm_tflops"
+WORKLOAD = "colpar_fp8_gemm_M8192_K8192_Nshard8192_rmsnorm_fp8_prologue"
+DECODE_K, DECODE_N = 4096, 11008
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                                     timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([s.strip() for s in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._t.join(timeout=10)
+
+    def summary(self):
+        mhz, mx, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def cpu_step_sample(rows: int, seed: int = 1234):
+    """The oracle's restatement of one step on `rows` output rows: RMSNorm statistics
+    and quantisation over the sampled rows (the per-tensor amax is taken over the
+    sample), weight shard quantised beforehand, GEMM + bf16 rounding on the rows."""
+    import numpy as np
+
+    import oracle
+
+    x = oracle.fill_normal_f16(rows * K, seed).reshape(rows, K)
+    g = oracle.fill_uniform_f16(K, seed + 2, 0.5, 1.5)
+    w = oracle.fill_normal_f16(N_SHARD * K, seed + 1).reshape(N_SHARD, K)
+    sb = oracle.scale_from_amax(oracle.amax_f16(w))
+    # weights are prepared outside the timed step, like the GPU arm: quantised, then
+    # decoded once to the f32 values the CPU multiplies with
+    bf = oracle.decode_e4m3(oracle.quantize_fp8_f16(w, sb))
+
+    def step():
+        aq, sa = oracle.rmsnorm_quantize_fp8(x, g, EPS)
+        return oracle.gemm_fp8_decoded(aq, bf, sa, sb, out_kind=oracle.OUT_BF16)
+
+    return step, oracle.num_threads()
+
+
+def run_reference(args):
+    """CPU arm: the oracle port of the step on the host cores, a bounded row sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 64
+    step, cores = cpu_step_sample(rows)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * rows * K * N_SHARD / dt / 1e12
+    sample = f"{rows} of {M} output rows per step (RMSNorm+quantise of those rows, GEMM against the full {N_SHARD}x{K} shard)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over e4m3 (CPU)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def decode_metrics(peaks, iters=200):
+    """INT4 decode GEMM, K=4096, N=11008, M in {1,4,8,32}: HBM-bound weight streaming.
+    Launches are issued by the library's own timing loop (the mirror of the reference's
+    time_launches) over a rotating pool of weight buffers of >= 4x L2 so every launch
+    reads its weights from HBM, not L2."""
+    import torch
+
+    from y_b200 import quant as q
+    from y_b200 import runtime as rt
+    from y_b200._lib import lib
+
+    ctx = rt.CudaContext.new()
+    l2 = ctx.device_attribute(rt.CU_DEVICE_ATTRIBUTE_L2_CACHE_SIZE) or (126 << 20)
+    stream_bytes = lib.y_b200_int4_stream_bytes(DECODE_K, DECODE_N)
+    free = torch.cuda.mem_get_info()[0]
+    nbuf = int(lib.y_autotune_plan_weight_replicas(stream_bytes, 32 * DECODE_K * 2, 32 * DECODE_N * 2, l2, free))
+    w = (torch.randn(DECODE_K, DECODE_N, device="cuda") / 64).to(torch.float16)
+    qw, sc = q.int4_quantize(w)
+    pool = [q.int4_repack(qw, sc) for _ in range(nbuf)]
+    kern = ctx.load_module(None, "y_int4_decode_gemm")
+    out = []
+    for m in (1, 4, 8, 32):
+        x = torch.randn(m, DECODE_K, device="cuda", dtype=torch.float16)
+        o = torch.empty(m, DECODE_N, device="cuda", dtype=torch.float16)
+        sets = [[x.data_ptr(), p.data_ptr(), o.data_ptr(), ("i32", m), ("i32", DECODE_N), ("i32", DECODE_K)]
+                for p in pool]
+        ctx.time_launches(kern, None, None, 0, sets, nbuf)  # warm-up: one pass over the pool
+        best = min(ctx.time_launches(kern, None, None, 0, sets, iters) for _ in range(5))
+        nbytes = stream_bytes + m * DECODE_K * 2 + m * DECODE_N * 2
+        gbs = nbytes / best / 1e3
+        out.append({"m": m, "us": round(best, 3), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                    "bytes": nbytes})
+    q.device_status()
+    kern.free()
+    ctx.close()
+    return {"workload": f"int4_decode_K{DECODE_K}_N{DECODE_N}_g128", "weight_buffers": nbuf,
+            "l2_bytes": l2, "peak_gb_s": peaks["hbm_gbs"], "peak_source": peaks["source"], "by_m": out}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from y_b200 import quant as q
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+
+    # ---- synthetic inputs (seeded; same X on every rank, a different weight shard per rank)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234)
+    x = torch.randn(M, K, device=dev, dtype=torch.float16, generator=gen)
+    gamma = (torch.rand(K, device=dev, generator=gen) + 0.5).to(torch.float16)
+    gen.manual_seed(5678 + rank)
+    w = torch.randn(K, N_SHARD, device=dev, dtype=torch.float16, generator=gen)  # B [K, N] row-major
+    w_amax = q.amax(w)
+    if world > 1:
+        dist.all_reduce(w_amax, op=dist.ReduceOp.MAX)  # one scale for the whole (sharded) B
+    sb = q.scale_from_amax(w_amax)
+    bqt = q.quantize_fp8(w, sb, transpose=True)  # [N_shard, K] e4m3, K-major
+    del w
+    ws = torch.empty(int(q.lib.y_b200_rmsnorm_workspace_bytes(M)), dtype=torch.uint8, device=dev)
+    c = torch.empty(M, N_SHARD, dtype=torch.bfloat16, device=dev)
+    x_host = torch.empty(M, K, dtype=torch.float16).pin_memory()
+    x_host.copy_(x.cpu())
+    c_host = torch.empty(M, N_SHARD, dtype=torch.bfloat16).pin_memory()
+    gathered = torch.empty(world, M, N_SHARD, dtype=torch.bfloat16, device=dev) if world > 1 else None
+
+    gemm_events = []
+
+    def step(x_dev, record=False):
+        aq, sa = q.rmsnorm_quantize_fp8(x_dev, gamma, EPS, workspace=ws)
+        if record:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        q.gemm_fp8_codes(aq, bqt, sa, sb, out_dtype=torch.bfloat16, out=c)
+        if record:
+            e1.record()
+            gemm_events.append((e0, e1))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        barrier()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        step(x)
+    q.device_status()
+
+    # ---- device-resident timed region
+    with ClockSampler(local) as clk:
+        ms = timed(lambda: step(x, record=True), args.steps)
+    clocks = clk.summary()
+    ms_per_step = ms / args.steps
+    flops_step = 2.0 * M * K * N_SHARD * world
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events) / len(gemm_events)
+    gemm_tflops = 2.0 * M * K * N_SHARD / (gemm_ms * 1e-3) / 1e12
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+
+    # ---- end to end through the operator API with host buffers
+    x_dev = torch.empty_like(x)
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        step(x_dev)
+        c_host.copy_(c, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+
+    # ---- the exchange step, reported separately
+    gather = None
+    if world > 1:
+        def gather_step():
+            step(x)
+            dist.all_gather_into_tensor(gathered, c)
+
+        for _ in range(2):
+            gather_step()
+        g_ms = timed(gather_step, args.steps) / args.steps
+        gather = {"ms_per_step_with_gather": g_ms, "tflops_with_gather": flops_step / (g_ms * 1e-3) / 1e12,
+                  "gathered_layout": "[rank, M, N_shard] bf16", "recv_bytes_per_gpu": (world - 1) * M * N_SHARD * 2}
+    q.device_status()
+
+    line = None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "m": M, "k": K, "n_per_gpu": N_SHARD, "n_total": N_SHARD * world,
+                       "parallelism": f"column-parallel N over {world} GPU(s)",
+                       "step": "rmsnorm_stats + rmsnorm_quantize_fp8 + gemm_fp8 (weights pre-quantised)",
+                       "l2": "inputs larger than L2 (X 134 MB + Bt 67 MB + C 134 MB per step)",
+                       "all_gather": "not in value; see gather"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N_SHARD * 2},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_fp8_kernel<256, NONE, BF16>", "achieved": gemm_tflops,
+                         "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
+                         "peak_note": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
+                                      f"nominal dense FP8 is {NOMINAL_FP8_TFLOPS}",
+                         "frac_of_nominal": gemm_tflops / NOMINAL_FP8_TFLOPS, "us_per_launch": gemm_ms * 1e3,
+                         "flops_per_launch": 2.0 * M * K * N_SHARD, "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+        }
+        if gather:
+            line["gather"] = gather
+    if world > 1:
+        dist.barrier()
+    if rank == 0 and world == 1:
+        if not args.no_decode:
+            line["decode"] = decode_metrics(peaks)
+        if not args.no_cpu:
+            rows = args.cpu_rows
+            stepfn, cores = cpu_step_sample(rows)
+            stepfn()
+            t0 = time.perf_counter()
+            reps = 0
+            while time.perf_counter() - t0 < 10.0:
+                stepfn()
+                reps += 1
+            dt = (time.perf_counter() - t0) / reps
+            line["cpu_baseline"] = {
+                "value": 2.0 * rows * K * N_SHARD / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"{rows} of {M} output rows per step, {reps} steps in {dt * reps:.1f} s"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_fp8_kernel launch at the bench
+# shape, from the ncu capture summarised under profiles/ (None until captured).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the INT4 decode section")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-rows", type=int, default=64)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -80,6 +80,9 @@ _rmsq = _sig("orc_rmsnorm_quantize_fp8", None, _u16p, _u16p, C.c_size_t, C.c_siz
              _u8p, _f32p)
 _gemm8 = _sig("orc_gemm_fp8", None, _u8p, _u8p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float,
               C.c_float, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t)
+_dec8 = _sig("orc_decode_e4m3", None, _u8p, C.c_size_t, _f32p)
+_gemm8d = _sig("orc_gemm_fp8_decoded", None, _u8p, _f32p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float,
+               C.c_float, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t)
 _gemm16 = _sig("orc_gemm_f16", None, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p,
                C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_size_t)
 _requant = _sig("orc_requant_bf16_fp8", None, _u16p, C.c_size_t, _u8p, _f32p)
@@ -246,6 +249,23 @@ def gemm_fp8(aq, bqt, scale_a, scale_b, bias=None, epilogue=EPI_NONE, out_kind=O
     _gemm8(_p(aq, _u8p), _p(bqt, _u8p), M, N, K, scale_a, scale_b, bptr, bkind, epilogue,
            out_kind, out.ctypes.data_as(C.c_void_p), row_begin, row_count)
     del keep
+    return out
+
+
+def decode_e4m3(q: np.ndarray) -> np.ndarray:
+    q = _c(q, np.uint8)
+    out = np.empty(q.shape, np.float32)
+    _dec8(_p(q, _u8p), q.size, _p(out, _f32p))
+    return out
+
+
+def gemm_fp8_decoded(aq, bf, scale_a, scale_b, out_kind=OUT_F32) -> np.ndarray:
+    """gemm_fp8 with the weight operand already decoded by `decode_e4m3` ([N, K] f32)."""
+    aq, bf = _c(aq, np.uint8), _c(bf, np.float32)
+    (M, K), (N, _) = aq.shape, bf.shape
+    out = _out_array(M, N, out_kind)
+    _gemm8d(_p(aq, _u8p), _p(bf, _f32p), M, N, K, scale_a, scale_b, None, BIAS_NONE, EPI_NONE, out_kind,
+            out.ctypes.data_as(C.c_void_p), 0, M)
     return out
 
 

@@ -386,30 +386,52 @@ static void epilogue_row(const float* acc, size_t N, float scale, const void* bi
     }
 }
 
-void orc_gemm_fp8(const uint8_t* Aq, const uint8_t* BqT, size_t M, size_t N, size_t K,
-                  float scale_a, float scale_b, const void* bias, int bias_kind, int epilogue,
-                  int out_kind, void* out, size_t row_begin, size_t row_count) {
+void orc_decode_e4m3(const uint8_t* q, size_t n, float* out) {
+    float lut[256];
+    for (int i = 0; i < 256; ++i) lut[i] = orc_e4m3_decode((uint8_t)i);
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) out[i] = lut[q[i]];
+}
+
+/* Same as orc_gemm_fp8 with the weight operand already decoded to f32
+ * (Bf = orc_decode_e4m3(BqT)): lets a caller that reuses one weight matrix
+ * for many calls pay for the decode once. */
+void orc_gemm_fp8_decoded(const uint8_t* Aq, const float* Bf, size_t M, size_t N, size_t K,
+                          float scale_a, float scale_b, const void* bias, int bias_kind,
+                          int epilogue, int out_kind, void* out, size_t row_begin,
+                          size_t row_count) {
     float lut[256];
     for (int i = 0; i < 256; ++i) lut[i] = orc_e4m3_decode((uint8_t)i);
     if (row_begin + row_count > M) row_count = M > row_begin ? M - row_begin : 0;
-    float* Bf = (float*)malloc(N * K * sizeof(float));
-#pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < N * K; ++i) Bf[i] = lut[BqT[i]];
     const float scale = scale_a * scale_b;
-#pragma omp parallel
-    {
-        float* arow = (float*)malloc(K * sizeof(float));
-        float* acc = (float*)malloc(N * sizeof(float));
-#pragma omp for schedule(dynamic, 1)
-        for (size_t r = 0; r < row_count; ++r) {
-            const uint8_t* a = Aq + (row_begin + r) * K;
-            for (size_t k = 0; k < K; ++k) arow[k] = lut[a[k]];
-            for (size_t c = 0; c < N; ++c) acc[c] = dot_f32(arow, Bf + c * K, K);
-            epilogue_row(acc, N, scale, bias, bias_kind, epilogue, out_kind, out, r);
-        }
-        free(arow);
-        free(acc);
+    /* Blocks of 32 rows: the decoded A block stays in cache while each weight
+     * row is streamed once per block instead of once per output row. Every
+     * output is still the same dot_f32 of the same two vectors. */
+    enum { RB = 32 };
+    float* ablk = (float*)malloc((size_t)RB * K * sizeof(float));
+    float* acc = (float*)malloc((size_t)RB * N * sizeof(float));
+    for (size_t r0 = 0; r0 < row_count; r0 += RB) {
+        const size_t nr = row_count - r0 < RB ? row_count - r0 : RB;
+#pragma omp parallel for schedule(static)
+        for (size_t i = 0; i < nr * K; ++i) ablk[i] = lut[Aq[(row_begin + r0) * K + i]];
+#pragma omp parallel for schedule(static)
+        for (size_t c = 0; c < N; ++c)
+            for (size_t r = 0; r < nr; ++r) acc[r * N + c] = dot_f32(ablk + r * K, Bf + c * K, K);
+#pragma omp parallel for schedule(static)
+        for (size_t r = 0; r < nr; ++r)
+            epilogue_row(acc + r * N, N, scale, bias, bias_kind, epilogue, out_kind, out, r0 + r);
     }
+    free(ablk);
+    free(acc);
+}
+
+void orc_gemm_fp8(const uint8_t* Aq, const uint8_t* BqT, size_t M, size_t N, size_t K,
+                  float scale_a, float scale_b, const void* bias, int bias_kind, int epilogue,
+                  int out_kind, void* out, size_t row_begin, size_t row_count) {
+    float* Bf = (float*)malloc(N * K * sizeof(float));
+    orc_decode_e4m3(BqT, N * K, Bf);
+    orc_gemm_fp8_decoded(Aq, Bf, M, N, K, scale_a, scale_b, bias, bias_kind, epilogue, out_kind,
+                         out, row_begin, row_count);
     free(Bf);
 }
 

@@ -87,6 +87,12 @@ void orc_gemm_fp8(const uint8_t* Aq, const uint8_t* BqT, size_t M, size_t N,
                   int bias_kind, int epilogue, int out_kind, void* out,
                   size_t row_begin, size_t row_count);
 
+void orc_decode_e4m3(const uint8_t* q, size_t n, float* out);
+void orc_gemm_fp8_decoded(const uint8_t* Aq, const float* Bf, size_t M, size_t N, size_t K,
+                          float scale_a, float scale_b, const void* bias, int bias_kind,
+                          int epilogue, int out_kind, void* out, size_t row_begin,
+                          size_t row_count);
+
 /* Requantise a bf16 tensor to e4m3 with a fresh per-tensor scale.          */
 void orc_requant_bf16_fp8(const uint16_t* h_bf16, size_t n, uint8_t* q,
                           float* scale_out);

@@ -1,0 +1,145 @@
+"""The C-ABI library loads without a GPU, exports every symbol the headers declare,
+and the host-side entry points (c_api.rs surface, error paths) behave as the
+reference's do. No compute call is made here."""
+import ctypes as C
+import json
+import os
+import re
+
+import pytest
+
+from y_b200 import _lib, runtime
+from y_b200._lib import lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    names = set()
+    for hdr in ("y_b200.h", "y_b200_runtime.h"):
+        text = open(os.path.join(ROOT, "include", hdr)).read()
+        names |= set(re.findall(r"Y_B200_API[^;(]*?\b(y_[a-z0-9_]+)\s*\(", text))
+    return names
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    declared = _declared_symbols()
+    assert len(declared) > 50
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/ but not exported"
+    assert declared == set(_lib.SIGNATURES), "python binding table and headers disagree"
+
+
+def test_block_cdiv_matches_reference_values():
+    # tests/test_rust_triton_parity.rs:62-63 and src/c_api.rs:196-201
+    assert runtime.block_cdiv(10, 3) == 4
+    assert runtime.block_cdiv(100, 32) == 4
+    assert runtime.block_cdiv(5, 0) == 0
+    assert runtime.block_cdiv(0, 7) == 0
+
+
+def test_autotune_json_has_the_reference_keys():
+    # tests/test_rust_triton_parity.rs:65-73
+    space = runtime.autotune_search_space(1024, 1024, 1024, True)
+    assert space and all({"cta_m", "cta_n", "cta_k", "warps_m", "warps_n", "num_stages", "num_warps",
+                          "is_fp8"} <= set(c) for c in space)
+    assert all(c["is_fp8"] is True for c in space)
+    assert all(c["num_stages"] >= 2 and c["num_warps"] >= 4 for c in space)
+    cfg = runtime.autotune_select_config(2048, 2048, 2048, True)
+    assert set(cfg) == {"cta_m", "cta_n", "cta_k", "warps_m", "warps_n", "num_stages", "num_warps"}
+    assert cfg["cta_m"] >= 64 and cfg["num_stages"] >= 2 and cfg["num_warps"] >= 4
+    # decode shapes resolve to the weight-streaming kernel's geometry
+    dec = runtime.autotune_select_config(8, 11008, 4096, False)
+    assert dec["cta_m"] == 8 and dec["cta_n"] == 16
+
+
+FP8_SRC = """
+// FP8 GEMM fixture shape
+@tile(256, 256, 256)
+kernel gemm_fp8_256(A: GlobalMemory<F32>, B: GlobalMemory<F32>, scale_a: F32, scale_b: F32, C: GlobalMemory<F32>) {
+}
+
+fn main() {
+}
+"""
+
+
+def test_compile_returns_a_launch_descriptor_for_tile_kernels():
+    text = runtime.compile_to_ptx(FP8_SRC, "sm_100a")
+    assert "entry=gemm_fp8_256 family=gemm_fp8" in text
+    assert "M=256 N=256 K=256" in text
+    assert "Dynamic shared memory required:" in text and "Launch grid required:" in text
+    out = (C.c_uint32 * 4)()
+    fake = "// [Y TENSOR CORE GEMM] M=1024 N=1024 K=1024 | CTA 64x128x32 | 2x2 warps | x\n" \
+           "// Dynamic shared memory required: 41472 bytes.\n"
+    # src/empirical_autotune.rs:1003-1019
+    assert lib.y_parse_launch_config(fake.encode(), 1024, 1024, out) == 0
+    assert list(out) == [8, 16, 128, 41472]
+    # the synchronous fallback prints no byte count: 0 is the answer (:1021-1030)
+    fake2 = "    // [Y TENSOR CORE GEMM] M=64 N=64 K=32 | CTA 32x32x32 | 2x1 warps | wmma\n"
+    assert lib.y_parse_launch_config(fake2.encode(), 64, 64, out) == 0
+    assert out[3] == 0 and out[2] == 64
+    assert lib.y_parse_launch_config(b".version 8.4\n", 64, 64, out) != 0
+    # the library's own descriptor parses with the same routine
+    assert lib.y_parse_launch_config(text.encode(), 256, 256, out) == 0
+    assert out[3] > 0
+
+
+def test_compile_errors_follow_the_reference_contract():
+    # null source -> error text, not a crash (src/c_api.rs:32-37)
+    err = C.c_void_p()
+    assert lib.y_compile_to_ptx(None, b"sm_100a", C.byref(err)) is None
+    assert _lib.take_string(err.value) == "Source pointer is null"
+    assert lib.y_interpret_kernel(None, C.byref(err)) == -1
+    assert _lib.take_string(err.value) == "Source pointer is null"
+    assert lib.y_interpret_kernel(FP8_SRC.encode(), C.byref(err)) == 0
+    lib.y_free_string(None)  # null is allowed (src/c_api.rs:208-212)
+    # 5-parameter shape with a wrong element type (src/type_checker.rs:944-975)
+    bad = FP8_SRC.replace("A: GlobalMemory<F32>", "A: GlobalMemory<F16>")
+    with pytest.raises(ValueError, match="5 parameters"):
+        runtime.compile_to_ptx(bad)
+    # K % 64 precondition of the FP8 family (src/ptx_emitter.rs:3297-3304)
+    with pytest.raises(ValueError, match="multiple of 64"):
+        runtime.compile_to_ptx(FP8_SRC.replace("@tile(256, 256, 256)", "@tile(256, 256, 96)"))
+    # K is not optional on a kernel-level @tile (src/type_checker.rs:911-916)
+    with pytest.raises(ValueError):
+        runtime.compile_to_ptx(FP8_SRC.replace("@tile(256, 256, 256)", "@tile(256, 256)"))
+    with pytest.raises(ValueError, match="requires 3 parameters"):
+        runtime.compile_to_ptx("@tile(64,64,64)\nkernel k(A: GlobalMemory<F16>, C: GlobalMemory<F32>) {\n}\n")
+
+
+def test_other_reference_shapes_are_classified():
+    for name, params, fam in [
+        ("gemm_f16_decode_m1", "A: GlobalMemory<F16>, B: GlobalMemory<F16>, C: GlobalMemory<F32>", "gemm_f16"),
+        ("gemm_f16_bias_relu_512", "A: GlobalMemory<F16>, B: GlobalMemory<F16>, Bias: GlobalMemory<F32>, "
+                                   "C: GlobalMemory<F32>", "gemm_f16_bias_relu"),
+        ("gemm_f16_swiglu_512", "X: GlobalMemory<F16>, Wgate: GlobalMemory<F16>, Wup: GlobalMemory<F16>, "
+                                "Out: GlobalMemory<F32>", "gemm_f16_swiglu"),
+    ]:
+        text = runtime.compile_to_ptx(f"@tile(512, 512, 512)\nkernel {name}({params}) {{\n}}\n")
+        assert f"entry={name} family={fam}" in text
+    rms = ("kernel rmsnorm_residual_4096(X: GlobalMemory<F16>, Residual: GlobalMemory<F16>, "
+           "Weight: GlobalMemory<F16>, Out: GlobalMemory<F16>, NewResidual: GlobalMemory<F16>) {\n}\n")
+    assert "family=rmsnorm_residual" in runtime.compile_to_ptx(rms)
+    with pytest.raises(ValueError, match="128"):
+        runtime.compile_to_ptx("@tile(100, 128, 64)\nkernel s(X: GlobalMemory<F16>, G: GlobalMemory<F16>, "
+                               "U: GlobalMemory<F16>, O: GlobalMemory<F32>) {\n}\n")
+
+
+def test_argument_errors_are_codes_not_crashes():
+    assert lib.y_b200_amax(None, _lib.F16, 10, None, None) == _lib.ERR_INVALID
+    assert "null" in _lib.last_error()
+    assert lib.y_b200_gemm_fp8(None, None) == _lib.ERR_INVALID
+    assert lib.y_b200_gemm_int4_decode(None, None, None, 1, 16, 128, None) == _lib.ERR_INVALID
+    assert lib.y_b200_int4_stream_bytes(4096, 11008) == 22_544_384 + 704_512
+    assert lib.y_b200_gemm_fp8_f32_workspace_bytes(256, 256, 256) == 2 * 65536 + 256
+    assert lib.y_b200_swiglu_workspace_bytes(4096, 22016) == 256 + 4096 * 11008 * 2
+    assert lib.y_b200_rmsnorm_workspace_bytes(8192) == 8192 * 4 + 256
+    assert b"sm_100a" in lib.y_b200_version()
+
+
+def test_context_creation_never_aborts_without_a_device():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    assert runtime.CudaContext.new() is None  # src/cuda_runtime.rs:330-364

@@ -90,6 +90,58 @@ SIGNATURES = {
     "y_free_string": (None, [_vp]),
 }
 
+
+
+class Arg(C.Structure):
+    class _V(C.Union):
+        _fields_ = [("ptr", C.c_uint64), ("f32", C.c_float), ("i32", C.c_int32)]
+
+    _fields_ = [("kind", C.c_int), ("v", _V)]
+
+
+ARG_PTR, ARG_F32, ARG_I32 = 0, 1, 2
+_u3 = C.POINTER(C.c_uint)
+_u32p = C.POINTER(C.c_uint32)
+
+# include/y_b200_runtime.h
+SIGNATURES.update({
+    "y_ctx_create": (_vp, []),
+    "y_ctx_destroy": (None, [_vp]),
+    "y_ctx_device_name": (C.c_char_p, [_vp]),
+    "y_ctx_device_attribute": (_i, [_vp, _i, C.POINTER(C.c_int)]),
+    "y_ctx_mem_info": (_i, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),
+    "y_ctx_synchronize": (_i, [_vp]),
+    "y_ctx_alloc": (_vp, [_vp, _sz]),
+    "y_buf_free": (None, [_vp]),
+    "y_buf_device_ptr": (_u64, [_vp]),
+    "y_buf_len_bytes": (_sz, [_vp]),
+    "y_ctx_memset_u8": (_i, [_vp, _vp, C.c_uint8]),
+    "y_ctx_memcpy_htod_at": (_i, [_vp, _vp, _sz, _vp, _sz]),
+    "y_ctx_memcpy_dtoh_at": (_i, [_vp, _vp, _sz, _vp, _sz]),
+    "y_ctx_memcpy_dtod": (_i, [_vp, _vp, _vp]),
+    "y_ctx_load_module": (_vp, [_vp, C.c_char_p, C.c_char_p]),
+    "y_kernel_free": (None, [_vp]),
+    "y_kernel_set_max_dynamic_smem": (_i, [_vp, C.c_uint]),
+    "y_kernel_launch_info": (_i, [_vp, C.POINTER(LaunchInfo)]),
+    "y_ctx_launch": (_i, [_vp, _vp, _u3, _u3, C.c_uint, C.POINTER(Arg), _i]),
+    "y_ctx_time_launches": (_i, [_vp, _vp, _u3, _u3, C.c_uint, C.POINTER(Arg), _i, _i, C.c_uint,
+                                 C.POINTER(C.c_double)]),
+    "y_autotune_persist_key": (_vp, [_u32, _u32, _u32, _i, C.c_char_p]),
+    "y_autotune_parse_persisted": (_i, [C.c_char_p, _u32p]),
+    "y_autotune_set_profile_path": (None, [C.c_char_p]),
+    "y_autotune_store": (_i, [_u32, _u32, _u32, _i, C.c_char_p, _u32p]),
+    "y_autotune_lookup": (_i, [_u32, _u32, _u32, _i, C.c_char_p, _u32p, _u32p]),
+    "y_autotune_set_mode": (None, [_i]),
+    "y_autotune_clear_cache": (None, []),
+    "y_autotune_is_launchable": (_i, [_u32p, _u32, _i]),
+    "y_autotune_score": (C.c_double, [_u32p, _u32, _u32, _u32, _i]),
+    "y_autotune_tied": (_i, [C.c_double, C.c_double, C.c_double, C.c_double]),
+    "y_autotune_select_winner": (_sz, [C.POINTER(C.c_double), _sz]),
+    "y_autotune_plan_weight_replicas": (_sz, [_sz, _sz, _sz, _sz, _sz]),
+    "y_autotune_measure_fp8_json": (_vp, [_u32, _u32, _u32]),
+    "y_parse_launch_config": (_i, [C.c_char_p, _u32, _u32, _u32p]),
+})
+
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.restype = _res

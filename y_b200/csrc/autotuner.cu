@@ -372,13 +372,23 @@ size_t plan_weight_replicas(size_t b_bytes, size_t a_bytes, size_t c_bytes, size
 }
 
 std::string current_gpu_name() {
+    static std::mutex mu;
+    static std::map<int, std::string> names;
     int dev = 0;
-    cudaDeviceProp prop;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+    if (cudaGetDevice(&dev) != cudaSuccess) {
         (void)cudaGetLastError();
         return "NVIDIA B200";
     }
-    return prop.name;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = names.find(dev);
+    if (it != names.end()) return it->second;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return "NVIDIA B200";
+    }
+    names[dev] = prop.name;
+    return names[dev];
 }
 
 // ---- on-device tuning of the FP8 GEMM -------------------------------------------

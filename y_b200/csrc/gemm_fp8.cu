@@ -23,6 +23,7 @@
 // status word and the CTA unwinds through the common teardown.
 #include <cuda.h>
 
+#include "autotuner.cuh"
 #include "common.cuh"
 
 namespace yb {
@@ -374,14 +375,12 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int k, int bo
     return 0;
 }
 
-int pick_cta_n(int m, int n) {
-    // Tile table for B200 (148 SMs): the widest tile keeps shared-memory traffic
-    // per MMA lowest; narrower tiles only when the grid would leave most SMs idle.
-    const int m_tiles = (m + kCtaM - 1) / kCtaM;
-    const int sms = sm_count();
-    if ((long long)m_tiles * ((n + 255) / 256) >= sms || n >= 4096) return 256;
-    if ((long long)m_tiles * ((n + 127) / 128) >= sms / 2 || n > 512) return 128;
-    return 64;
+// Tile choice goes through the autotuner: override, caches, persisted
+// measurement, (optional) fresh measurement, analytic score.
+int pick_cta_n(int m, int n, int k) {
+    const Candidate c = autotune((uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8,
+                                 current_gpu_name(), sm_count());
+    return (c.cta_n == 64 || c.cta_n == 128 || c.cta_n == 256) ? (int)c.cta_n : 256;
 }
 
 template <int BN, int EPI, int OUT>
@@ -463,7 +462,7 @@ extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
     int rc = validate(a);
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int bn = a->cta_n ? a->cta_n : pick_cta_n(a->m, a->n);
+    const int bn = a->cta_n ? a->cta_n : pick_cta_n(a->m, a->n, a->k);
     CUtensorMap ta, tb;
     if ((rc = make_operand_map(&ta, a->a, a->m, a->k, kCtaM))) return rc;
     if ((rc = make_operand_map(&tb, a->bt, a->n, a->k, bn))) return rc;
@@ -494,7 +493,7 @@ extern "C" int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b20
         return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8_launch_info: bad shape M=%d N=%d K=%d", m, n, k);
     if (cta_n != 0 && cta_n != 64 && cta_n != 128 && cta_n != 256)
         return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_launch_info: cta_n must be 0, 64, 128 or 256");
-    const int bn = cta_n ? cta_n : pick_cta_n(m, n);
+    const int bn = cta_n ? cta_n : pick_cta_n(m, n, k);
     const long long tiles = (long long)((m + kCtaM - 1) / kCtaM) * ((n + bn - 1) / bn);
     const int sms = sm_count();
     out->grid[0] = (unsigned)(tiles < sms ? tiles : sms);
