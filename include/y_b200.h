@@ -133,6 +133,30 @@ Y_B200_API int y_b200_gemm_fp8_f32(const float* a, const float* b, float scale_a
                         int m, int n, int k, void* workspace, size_t workspace_bytes,
                         void* stream);
 
+/* The same GEMM for callers that cannot allocate device memory when they call:
+ * an engine whose own pool already owns all of HBM, a latency-critical loop
+ * where cudaMalloc (a device-wide lock, possibly a synchronisation) is not
+ * allowed, a host that hands a plugin nothing but its inputs and outputs.
+ * No counterpart in the reference, whose launch path always allocates its
+ * buffers itself.
+ * The e4m3 operand copies go to a fixed array inside the library image instead
+ * of a workspace: every GPU that loads the library holds
+ * Y_B200_STATIC_OPERAND_BYTES + 256 bytes of it until the process exits.
+ * Limit: round256(M*K) + round256(N*K) <= Y_B200_STATIC_OPERAND_BYTES (for
+ * example 2048 x 2048 x 2048); larger problems return Y_B200_ERR_WORKSPACE and
+ * must use y_b200_gemm_fp8_f32. The call itself makes no cudaMalloc / cudaFree
+ * and uses no allocating library routine.
+ * The first call on each device looks up the array's device address (with that
+ * device current); make that first call before any stream capture begins.
+ * All calls on a device share the one array and it keeps the last call's
+ * contents: calls that can overlap on the GPU (different streams, different
+ * threads) race on it and must be serialised by the caller. A bounded wait that
+ * runs out is recorded inside the array, not in the word y_b200_device_status
+ * reads; the next call on an idle stream reports it as Y_B200_ERR_DEVICE. */
+#define Y_B200_STATIC_OPERAND_BYTES (8u << 20)
+Y_B200_API int y_b200_gemm_fp8_f32_static(const float* a, const float* b, float scale_a, float scale_b,
+                                          float* c, int m, int n, int k, void* stream);
+
 /* Fused SwiGLU GEMM with FP8 re-quantisation (replaces gemm_f16_swiglu_<tag>,
  * src/ptx_emitter.rs:5064-5565, with FP8 operands and interleaved gate|up):
  * h = bf16(silu(g) * u) -> fresh per-tensor scale -> q = e4m3(h / scale).

@@ -23,6 +23,8 @@
 // status word and the CTA unwinds through the common teardown.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "autotuner.cuh"
 #include "common.cuh"
 
@@ -575,4 +577,112 @@ extern "C" int y_b200_gemm_fp8_swiglu_requant(const y_b200_gemm_fp8_args* args, 
     if (rc) return rc;
     return quantize_from_amax(h, Y_B200_BF16, (size_t)args->m * (size_t)(args->n / 2), amax, q,
                               scale_out, st);
+}
+
+// ---- allocation-free variant of the f32 drop-in GEMM -----------------------------
+// Some callers must not allocate device memory at call time: a serving loop that
+// has handed all of HBM to its own pool, a latency-critical path where cudaMalloc
+// (which takes a device-wide lock and may synchronise) is forbidden, a plugin
+// host that only grants the library its input and output buffers. For them the
+// operand copies live in a fixed array that is part of the library image, so
+// every GPU that loads liby_b200.so holds these bytes until the process exits.
+namespace yb {
+namespace {
+
+constexpr size_t kStaticHeader = 256;                       // status word + two scale slots
+constexpr size_t kStaticOperandBytes = Y_B200_STATIC_OPERAND_BYTES;  // e4m3 copies of A and Bt together
+constexpr size_t kStaticScratchBytes = kStaticHeader + kStaticOperandBytes;
+
+// In host code this name is only a handle for the runtime; the device address
+// is obtained once per device with cudaGetSymbolAddress (below).
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device, looked up on the
+// first call on that device (with that device current) and cached.
+int static_scratch_ptr(unsigned char** out) {
+    static std::mutex mu;
+    static unsigned char* ptrs[64] = {};
+    int dev = 0;
+    YB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(Y_B200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        YB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (p == nullptr) return fail(Y_B200_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        ptrs[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = ptrs[dev];
+    return 0;
+}
+
+}  // namespace
+}  // namespace yb
+
+extern "C" int y_b200_gemm_fp8_f32_static(const float* a, const float* b, float scale_a, float scale_b,
+                                          float* c, int m, int n, int k, void* stream) {
+    if (!a || !b || !c) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_f32_static: null pointer");
+    if (m < 1 || n < 1 || k < 1 || k % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8_f32_static: need M, N >= 1 and K %% 16 == 0 (M=%d N=%d K=%d)", m, n, k);
+    if (!(scale_a > 0.0f) || !(scale_b > 0.0f))
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_f32_static: scales must be positive");
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_fp8_f32_static: a and b must be 16-byte aligned");
+    const size_t a_bytes = ((size_t)m * k + 255) & ~(size_t)255, b_bytes = ((size_t)n * k + 255) & ~(size_t)255;
+    if (a_bytes + b_bytes > kStaticOperandBytes)
+        return fail(Y_B200_ERR_WORKSPACE,
+                    "y_b200_gemm_fp8_f32_static: M*K + N*K = %zu bytes of e4m3 operands exceed the built-in "
+                    "scratch of %zu bytes; use y_b200_gemm_fp8_f32 with a caller-provided workspace",
+                    a_bytes + b_bytes, kStaticOperandBytes);
+    unsigned char* base = nullptr;
+    int rc = static_scratch_ptr(&base);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    DeviceStatus* status = reinterpret_cast<DeviceStatus*>(base);
+    float* slots = reinterpret_cast<float*>(base + 64);
+    void* aq = base + kStaticHeader;
+    void* bq = base + kStaticHeader + a_bytes;
+    // The scratch keeps the previous call's contents. If the stream is idle, look
+    // at what that call left in the status word (it is not the word
+    // y_b200_device_status reads) before clearing it; the operand areas are fully
+    // overwritten by the quantise kernels and need no clearing.
+    if (cudaStreamQuery(st) == cudaSuccess) {
+        DeviceStatus prev;
+        YB_CUDA(cudaMemcpy(&prev, status, sizeof prev, cudaMemcpyDeviceToHost));
+        if (prev.code != 0) {
+            YB_CUDA(cudaMemset(status, 0, sizeof(DeviceStatus)));
+            return fail(Y_B200_ERR_DEVICE,
+                        "y_b200_gemm_fp8_f32_static: the previous call on this device gave up a bounded wait "
+                        "(code %u at 0x%x, CTA %u); its output is not valid", prev.code, prev.where, prev.block);
+        }
+    } else {
+        (void)cudaGetLastError();
+    }
+    YB_CUDA(cudaMemsetAsync(status, 0, sizeof(DeviceStatus), st));
+    if ((rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, slots, aq, st))) return rc;
+    if ((rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, slots + 1, bq, st))) return rc;
+    // Tile from the analytic score only: no cache file, no measurement run.
+    int bn = 256;
+    double best = -1.0;
+    for (const Candidate& cand : generate_candidates((uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8)) {
+        const double s = score_candidate(cand, (uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8, sm_count());
+        if (is_launchable(cand, (uint32_t)k, Precision::Fp8) && s > best) { best = s; bn = (int)cand.cta_n; }
+    }
+    CUtensorMap ta, tb;
+    if ((rc = make_operand_map(&ta, aq, m, k, kCtaM))) return rc;
+    if ((rc = make_operand_map(&tb, bq, n, k, bn))) return rc;
+    GemmParams p = {};
+    p.c = c;
+    p.m = m; p.n = n; p.k = k;
+    p.scale_a = scale_a; p.scale_b = scale_b;
+    p.status = status;
+    p.m_tiles = (m + kCtaM - 1) / kCtaM;
+    p.n_tiles = (n + bn - 1) / bn;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    switch (bn) {
+        case 256: return launch_epi<256>(ta, tb, p, Y_B200_EPI_NONE, Y_B200_F32, grid, st);
+        case 128: return launch_epi<128>(ta, tb, p, Y_B200_EPI_NONE, Y_B200_F32, grid, st);
+        default: return launch_epi<64>(ta, tb, p, Y_B200_EPI_NONE, Y_B200_F32, grid, st);
+    }
 }
