@@ -35,6 +35,9 @@ DECODE_K, DECODE_N = 4096, 11008
 NOMINAL_FP8_TFLOPS = 4500.0
 
 
+_emit = print  # replaced in main() by a writer to the process's original stdout
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -54,8 +57,39 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+        self._nv = None
+        try:  # initialise NVML up front so sampling starts with the timed region
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self._nv = (nv, h, nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run_nvml(self) -> bool:
+        """Fast path: read clocks and reasons through NVML (read-only queries)."""
+        if self._nv is None:
+            return False
+        nv, h, mx = self._nv
+        bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+                "hw_thermal_slowdown": 0x40}
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                flags = ["Active" if r & bits[n] else "Not Active"
+                         for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
+                self.samples.append([str(mhz), str(mx), str(pw)] + flags)
+            except Exception:
+                pass
+            self._stop.wait(0.0005)
+        return True
 
     def _run(self):
+        if self._run_nvml():
+            return
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
@@ -77,12 +111,13 @@ class ClockSampler:
         self._t.join(timeout=10)
 
     def summary(self):
-        mhz, mx, reasons = [], 0.0, set()
+        mhz, mx, reasons, watts = [], 0.0, set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for s in self.samples:
             try:
                 mhz.append(float(s[0]))
                 mx = max(mx, float(s[1]))
+                watts.append(float(s[2]))
             except (ValueError, IndexError):
                 continue
             for name, v in zip(names, s[3:7]):
@@ -90,7 +125,8 @@ class ClockSampler:
                     reasons.add(name)
         mhz.sort()
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(mhz)}
+                "reasons": sorted(reasons), "samples": len(mhz), "sm_mhz_min": mhz[0] if mhz else None,
+                "power_w_max": max(watts) if watts else None}
 
 
 def cpu_step_sample(rows: int, seed: int = 1234):
@@ -121,6 +157,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if "RANK" in os.environ:
+        # torchrun pins OMP_NUM_THREADS=1 for its workers; this arm runs on rank 0 alone
+        # and is meant to use every host core (the oracle library reads it when loaded).
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     rows = 64
     step, cores = cpu_step_sample(rows)
     for _ in range(max(args.warmup, 1)):
@@ -131,7 +171,7 @@ def run_reference(args):
     dt = (time.perf_counter() - t0) / args.steps
     tflops = 2.0 * rows * K * N_SHARD / dt / 1e12
     sample = f"{rows} of {M} output rows per step (RMSNorm+quantise of those rows, GEMM against the full {N_SHARD}x{K} shard)"
-    print(json.dumps({
+    _emit(json.dumps({
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over e4m3 (CPU)", "data": "synthetic",
@@ -184,6 +224,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
+    from y_b200 import colpar
     from y_b200 import quant as q
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -202,9 +243,7 @@ def run_ours(args):
     gamma = (torch.rand(K, device=dev, generator=gen) + 0.5).to(torch.float16)
     gen.manual_seed(5678 + rank)
     w = torch.randn(K, N_SHARD, device=dev, dtype=torch.float16, generator=gen)  # B [K, N] row-major
-    w_amax = q.amax(w)
-    if world > 1:
-        dist.all_reduce(w_amax, op=dist.ReduceOp.MAX)  # one scale for the whole (sharded) B
+    w_amax = colpar.agree_amax(q.amax(w))  # one scale for the whole (sharded) B
     sb = q.scale_from_amax(w_amax)
     bqt = q.quantize_fp8(w, sb, transpose=True)  # [N_shard, K] e4m3, K-major
     del w
@@ -278,7 +317,7 @@ def run_ours(args):
     if world > 1:
         def gather_step():
             step(x)
-            dist.all_gather_into_tensor(gathered, c)
+            colpar.gather_columns(c, out=gathered)
 
         for _ in range(2):
             gather_step()
@@ -330,7 +369,7 @@ def run_ours(args):
                 "value": 2.0 * rows * K * N_SHARD / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                 "sample": f"{rows} of {M} output rows per step, {reps} steps in {dt * reps:.1f} s"}
     if rank == 0:
-        print(json.dumps(line))
+        _emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
@@ -350,6 +389,13 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-rows", type=int, default=64)
     args = ap.parse_args()
+    # Only the JSON line may reach stdout: libraries (NCCL prints its version there) write
+    # to file descriptor 1 directly, so point it at stderr and keep the real one aside.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    global _emit
+    _emit = lambda text: os.write(real_stdout, (text + "\n").encode())
     if args.impl == "reference":
         run_reference(args)
     else:

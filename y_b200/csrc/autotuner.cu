@@ -117,13 +117,13 @@ void clear_autotune_cache() {
 // (128 e4m3 or 64 16-bit elements); stages is what fits the 227 KB of shared
 // memory. INT4 decode: cta_m = tokens padded to the 8-wide MMA operand,
 // cta_n = 16-column weight tile, cta_k = K covered by one ring slot
-// (8 groups x 128), stages = ring slots.
+// (16 groups x 128), stages = ring slots.
 std::vector<Candidate> generate_candidates(uint32_t m, uint32_t n, uint32_t k, Precision p) {
     (void)n; (void)k;
     std::vector<Candidate> out;
     if (p == Precision::Int4) {
         const uint32_t cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32);
-        out.push_back({cta_m, 16, 1024, 8, 1, cta_m == 32 ? 16u : 20u, 8});
+        out.push_back({cta_m, 16, 2048, 16, 1, cta_m == 8 ? 10u : (cta_m == 16 ? 8u : 6u), 16});
         return out;
     }
     const uint32_t cta_k = p == Precision::Fp8 ? 128u : 64u;

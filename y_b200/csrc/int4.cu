@@ -93,16 +93,18 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---- decode GEMM ------------------------------------------------------------------
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 16;
 constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kUnitGroups = 8;                         // one group per consumer warp
-constexpr int kUnitBytes = kUnitGroups * kBlkBytes;    // 8448
-constexpr int kRoundTiles = 5;                         // 16-column tiles kept in registers
+constexpr int kUnitGroups = kConsumerWarps;            // one group per consumer warp
+constexpr int kUnitBytes = kUnitGroups * kBlkBytes;    // 16896
 
+// NT = 8-token operand tiles (M <= 8 * NT). round_tiles = 16-column weight tiles
+// whose accumulators a warp keeps in registers at once.
 template <int NT>
 struct DecodeCfg {
-    static constexpr int slots = NT == 4 ? 16 : 20;
-    static constexpr int red_floats = kConsumerWarps * kRoundTiles * NT * 128;
+    static constexpr int round_tiles = NT == 4 ? 3 : 5;
+    static constexpr int slots = NT == 1 ? 10 : (NT == 2 ? 8 : 6);
+    static constexpr int red_floats = kConsumerWarps * round_tiles * NT * 128;
     static constexpr int ring_bytes = slots * kUnitBytes;
     static constexpr int smem_bytes = ring_bytes + red_floats * 4 + 2 * slots * 8 + 16;
 };
@@ -116,19 +118,19 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// (w & 0x000F000F) | 0x6400 per half = 1024 + u; minus 1032 gives u - 8.
-__device__ __forceinline__ uint32_t deq_lo(uint32_t w) {
-    uint32_t h = (w & 0x000f000fu) | 0x64006400u;
-    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&h), __half2_raw{0x6408, 0x6408});
-    return *reinterpret_cast<uint32_t*>(&r);
-}
-// (w & 0x00F000F0) | 0x6400 per half = 1024 + 16u; times 1/16 minus 72 gives u - 8.
-__device__ __forceinline__ uint32_t deq_hi(uint32_t w) {
-    uint32_t h = (w & 0x00f000f0u) | 0x64006400u;
-    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&h), __half2_raw{0x2c00, 0x2c00},
-                        __half2_raw{0xd480, 0xd480});
-    return *reinterpret_cast<uint32_t*>(&r);
-}
+// Dequantisation costs one logic instruction per f16 pair. With u = q + 8 the
+// stored offset-binary nibble:
+//   (w & 0x000F000F) | 0x6400  is the f16 pair 1024 + u = q + 1032   (ulp 1 at 1024)
+//   (w & 0x00F000F0) | 0x5400  is the f16 pair   64 + u = q +   72   (ulp 1/16 at 64)
+// The offsets are not subtracted per weight. They are the same for every weight
+// column, so their contribution to a group's partial sum,
+// 1032 * sum(x over the "lo" K slots) + 72 * sum(x over the "hi" K slots), is
+// computed once per (group, token) by one MMA pass with a constant operand and
+// the group's accumulator starts at its negative. All products are exact in f32.
+__device__ __forceinline__ uint32_t deq_lo(uint32_t w) { return (w & 0x000f000fu) | 0x64006400u; }
+__device__ __forceinline__ uint32_t deq_hi(uint32_t w) { return (w & 0x00f000f0u) | 0x54005400u; }
+constexpr uint32_t kOffsetLo = 0x64086408u;  // f16 pair (1032, 1032)
+constexpr uint32_t kOffsetHi = 0x54805480u;  // f16 pair (72, 72)
 
 __device__ __forceinline__ void consumer_bar() {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
@@ -139,6 +141,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
     int4_decode_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ wstream,
                        __half* __restrict__ out, int M, int N, int K, DeviceStatus* status) {
     using Cfg = DecodeCfg<NT>;
+    constexpr int kRoundTiles = Cfg::round_tiles;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     float* red = reinterpret_cast<float*>(smem + Cfg::ring_bytes);
@@ -169,25 +172,25 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
     if (warp == kConsumerWarps) {
         // ---- producer: stream this CTA's contiguous share through the ring ----
         if (lane == 0) {
-            uint32_t unit = 0;
+            uint32_t slot = 0, sphase = 0;
             bool ok = true;
             for (int r0 = t_begin; r0 < t_end && ok; r0 += kRoundTiles) {
                 const int rt = min(kRoundTiles, t_end - r0);
                 for (int p = 0; p < phases && ok; ++p) {
                     const int ng = min(kUnitGroups, ngroups - p * kUnitGroups);
-                    for (int t = 0; t < rt; ++t, ++unit) {
-                        const uint32_t s = unit % Cfg::slots, ph = (unit / Cfg::slots) & 1u;
-                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) {
-                            report_timeout(status, abort_flag, 0x100u, unit);
+                    for (int t = 0; t < rt; ++t) {
+                        if (!mbar_wait(empty0 + 8 * slot, sphase ^ 1u, abort_flag)) {
+                            report_timeout(status, abort_flag, 0x100u, (unsigned)(r0 + t));
                             ok = false;
                             break;
                         }
                         const uint32_t bytes = (uint32_t)ng * kBlkBytes;
-                        mbar_expect_tx(full0 + 8 * s, bytes);
-                        bulk_load_1d(ring0 + s * kUnitBytes,
+                        mbar_expect_tx(full0 + 8 * slot, bytes);
+                        bulk_load_1d(ring0 + slot * kUnitBytes,
                                      wstream + ((size_t)(r0 + t) * ngroups + (size_t)p * kUnitGroups) *
                                                    kBlkBytes,
-                                     bytes, full0 + 8 * s);
+                                     bytes, full0 + 8 * slot);
+                        if (++slot == Cfg::slots) { slot = 0; sphase ^= 1u; }
                     }
                 }
             }
@@ -195,7 +198,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
     } else {
         // ---- consumers -------------------------------------------------------
         const int gq = lane >> 2, c = lane & 3;
-        uint32_t unit = 0;
+        uint32_t slot = 0, sphase = 0;  // ring position of the next unit
         bool dead = false;
         for (int r0 = t_begin; r0 < t_end; r0 += kRoundTiles) {
             const int rt = min(kRoundTiles, t_end - r0);
@@ -224,16 +227,29 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
                                 x + (size_t)tok * K + (size_t)g * 128 + pp * 32 + c * 8));
                     }
                 }
+                // Offset contribution of this group (see deq_lo / deq_hi): identical for
+                // all 16 weight columns, so one MMA pass with a constant operand.
+                float neg_off[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int pp = 0; pp < 4; ++pp) {
+                        mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].x, xf[j][pp].y);
+                        mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].z, xf[j][pp].w);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) neg_off[j][i] = -o[i];
+                }
 #pragma unroll
                 for (int t = 0; t < kRoundTiles; ++t) {
                     if (t < rt) {
-                        const uint32_t s = unit % Cfg::slots, ph = (unit / Cfg::slots) & 1u;
-                        if (!dead && !mbar_wait(full0 + 8 * s, ph, abort_flag)) {
-                            report_timeout(status, abort_flag, 0x200u + warp, unit);
+                        if (!dead && !mbar_wait(full0 + 8 * slot, sphase, abort_flag)) {
+                            report_timeout(status, abort_flag, 0x200u + warp, (unsigned)(r0 + t));
                             dead = true;
                         }
                         if (valid && !dead) {
-                            const uint8_t* blk = ring + s * kUnitBytes + warp * kBlkBytes;
+                            const uint8_t* blk = ring + slot * kUnitBytes + warp * kBlkBytes;
                             const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
                             const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
                             const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
@@ -245,13 +261,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
 #pragma unroll
                             for (int j = 0; j < NT; ++j)
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) tmp[j][i] = 0.0f;
+                                for (int i = 0; i < 4; ++i) tmp[j][i] = neg_off[j][i];
 #pragma unroll
                             for (int pp = 0; pp < 4; ++pp) {
+                                const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
                                 const uint32_t a0 = deq_lo(wA[pp]), a1 = deq_lo(wB[pp]);
                                 const uint32_t a2 = deq_hi(wA[pp]), a3 = deq_hi(wB[pp]);
-                                const uint32_t e0 = deq_lo(wA[pp] >> 8), e1 = deq_lo(wB[pp] >> 8);
-                                const uint32_t e2 = deq_hi(wA[pp] >> 8), e3 = deq_hi(wB[pp] >> 8);
+                                const uint32_t e0 = deq_lo(hA), e1 = deq_lo(hB);
+                                const uint32_t e2 = deq_hi(hA), e3 = deq_hi(hB);
 #pragma unroll
                                 for (int j = 0; j < NT; ++j) {
                                     mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
@@ -267,8 +284,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
                             }
                         }
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(empty0 + 8 * s);
-                        ++unit;
+                        if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+                        if (++slot == Cfg::slots) { slot = 0; sphase ^= 1u; }
                     }
                 }
             }

@@ -73,12 +73,12 @@ int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out
         const int sms = sm_count();
         out->grid[0] = (unsigned)(tiles < sms ? tiles : sms);
         out->grid[1] = out->grid[2] = 1;
-        out->block[0] = 288; out->block[1] = out->block[2] = 1;
+        out->block[0] = 544; out->block[1] = out->block[2] = 1;
         out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
         const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
-        const int slots = nt == 4 ? 16 : 20;
-        out->dyn_smem_bytes = (unsigned)(slots * 8448 + 8 * 5 * nt * 128 * 4 + 2 * slots * 8 + 16);
-        out->cta_m = 8 * nt; out->cta_n = 16; out->cta_k = 1024; out->stages = slots;
+        const int slots = nt == 1 ? 10 : (nt == 2 ? 8 : 6), round_tiles = nt == 4 ? 3 : 5;
+        out->dyn_smem_bytes = (unsigned)(slots * 16896 + 16 * round_tiles * nt * 128 * 4 + 2 * slots * 8 + 16);
+        out->cta_m = 8 * nt; out->cta_n = 16; out->cta_k = 2048; out->stages = slots;
         return 0;
     }
     int rc = y_b200_gemm_fp8_launch_info(m, n, kk, 0, out);
