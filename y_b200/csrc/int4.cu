@@ -5,8 +5,8 @@
 // exactly once), so it is built around keeping every SM's share of the stream
 // in flight from the first cycle: the streaming layout makes each CTA's share
 // one contiguous byte range, a producer warp issues it as 1-D bulk copies into
-// a shared-memory ring (up to ~165 KB outstanding per SM), and eight consumer
-// warps dequantise in registers and feed mma.sync.m16n8k16 (f16 x f16 -> f32)
+// a shared-memory ring (up to ~165 KB outstanding per SM), and 16 consumer warps
+// (8 for 32-token launches) dequantise in registers and feed mma.sync.m16n8k16 (f16 x f16 -> f32)
 // with the weights as the 16-row operand and the M <= 32 tokens as the 8-wide
 // operand. The group scale multiplies each group's f32 partial sum, so the
 // integer weights enter the MMA exactly. K is split across the warps of a
@@ -93,19 +93,22 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---- decode GEMM ------------------------------------------------------------------
-constexpr int kConsumerWarps = 16;
-constexpr int kDecodeThreads = (kConsumerWarps + 1) * 32;
-constexpr int kUnitGroups = kConsumerWarps;            // one group per consumer warp
-constexpr int kUnitBytes = kUnitGroups * kBlkBytes;    // 16896
+
 
 // NT = 8-token operand tiles (M <= 8 * NT). round_tiles = 16-column weight tiles
 // whose accumulators a warp keeps in registers at once.
 template <int NT>
 struct DecodeCfg {
-    static constexpr int round_tiles = NT == 4 ? 3 : 5;
-    static constexpr int slots = NT == 1 ? 10 : (NT == 2 ? 8 : 6);
-    static constexpr int red_floats = kConsumerWarps * round_tiles * NT * 128;
-    static constexpr int ring_bytes = slots * kUnitBytes;
+    // Consumer warps = K groups per ring slot (one group per warp). 32-token launches keep
+    // 4x the accumulators and activation fragments per thread, so they run 8 warps (more
+    // registers per thread) instead of 16.
+    static constexpr int warps = NT == 4 ? 8 : 16;
+    static constexpr int threads = (warps + 1) * 32;
+    static constexpr int unit_bytes = warps * kBlkBytes;
+    static constexpr int round_tiles = 5;
+    static constexpr int slots = NT == 1 ? 10 : (NT == 2 ? 8 : 16);
+    static constexpr int red_floats = warps * round_tiles * NT * 128;
+    static constexpr int ring_bytes = slots * unit_bytes;
     static constexpr int smem_bytes = ring_bytes + red_floats * 4 + 2 * slots * 8 + 16;
 };
 
@@ -132,16 +135,18 @@ __device__ __forceinline__ uint32_t deq_hi(uint32_t w) { return (w & 0x00f000f0u
 constexpr uint32_t kOffsetLo = 0x64086408u;  // f16 pair (1032, 1032)
 constexpr uint32_t kOffsetHi = 0x54805480u;  // f16 pair (72, 72)
 
+template <int THREADS>
 __device__ __forceinline__ void consumer_bar() {
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kDecodeThreads, 1)
+__global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
     int4_decode_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ wstream,
                        __half* __restrict__ out, int M, int N, int K, DeviceStatus* status) {
     using Cfg = DecodeCfg<NT>;
     constexpr int kRoundTiles = Cfg::round_tiles;
+    constexpr int kConsumerWarps = Cfg::warps, kUnitGroups = Cfg::warps, kUnitBytes = Cfg::unit_bytes;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     float* red = reinterpret_cast<float*>(smem + Cfg::ring_bytes);
@@ -162,6 +167,12 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
         mbar_fence_init();
     }
     __syncthreads();
+    // Programmatic dependent launch: the next kernel in the stream may start its own
+    // prologue and weight copies while this one is still running (the weights are not
+    // written by anything in the stream), which hides the launch gap between decode
+    // GEMMs of consecutive layers. Whatever can depend on earlier kernels (the
+    // activations, the output buffer) is only touched after griddepcontrol.wait below.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int ngroups = K / 128;
     const int phases = (ngroups + kUnitGroups - 1) / kUnitGroups;
@@ -197,6 +208,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
         }
     } else {
         // ---- consumers -------------------------------------------------------
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // earlier kernels' writes to x / out are complete
         const int gq = lane >> 2, c = lane & 3;
         uint32_t slot = 0, sphase = 0;  // ring position of the next unit
         bool dead = false;
@@ -298,7 +310,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
                 for (int j = 0; j < NT; ++j)
                     *reinterpret_cast<float4*>(mine + (t * NT + j) * 128 + lane * 4) =
                         make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
-            consumer_bar();
+            consumer_bar<kConsumerWarps * 32>();
             const int nout = rt * NT * 128;
             for (int e = threadIdx.x; e < nout; e += kConsumerWarps * 32) {
                 float v = red[e];
@@ -309,7 +321,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1)
                 const int tok = 8 * j + 2 * (l & 3) + (i & 1);
                 if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
             }
-            consumer_bar();
+            consumer_bar<kConsumerWarps * 32>();
         }
     }
 }
@@ -328,15 +340,36 @@ int launch_decode(const void* x, const void* wstream, void* out, int m, int n, i
     }
     const int tiles = n / 16;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    int4_decode_kernel<NT><<<grid, kDecodeThreads, Cfg::smem_bytes, st>>>(
-        static_cast<const __half*>(x), static_cast<const uint8_t*>(wstream),
-        static_cast<__half*>(out), m, n, k, device_status_ptr());
-    return check_cuda(cudaGetLastError(), "int4_decode_kernel launch");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)Cfg::threads);
+    cfg.dynamicSmemBytes = Cfg::smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, int4_decode_kernel<NT>, static_cast<const __half*>(x),
+                                         static_cast<const uint8_t*>(wstream), static_cast<__half*>(out), m, n, k,
+                                         device_status_ptr()),
+                      "int4_decode_kernel launch");
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
+
+// Launch geometry of the decode kernel for the host launch API.
+void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsigned* smem, int* slots,
+                            int* unit_k) {
+    const int tiles = n > 0 ? n / 16 : 0;
+    *grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
+    if (m <= 8) { *block = DecodeCfg<1>::threads; *smem = DecodeCfg<1>::smem_bytes; *slots = DecodeCfg<1>::slots; *unit_k = DecodeCfg<1>::warps * 128; }
+    else if (m <= 16) { *block = DecodeCfg<2>::threads; *smem = DecodeCfg<2>::smem_bytes; *slots = DecodeCfg<2>::slots; *unit_k = DecodeCfg<2>::warps * 128; }
+    else { *block = DecodeCfg<4>::threads; *smem = DecodeCfg<4>::smem_bytes; *slots = DecodeCfg<4>::slots; *unit_k = DecodeCfg<4>::warps * 128; }
+}
+
 }  // namespace yb
 
 using namespace yb;

@@ -34,6 +34,9 @@ struct y_kernel {
     int device;
 };
 
+namespace yb {
+void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsigned* smem, int* slots, int* unit_k);
+}
 using namespace yb;
 
 namespace {
@@ -69,16 +72,12 @@ void cand_to7(const Candidate& c, uint32_t out[7]) {
 int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out) {
     memset(out, 0, sizeof *out);
     if (k->entry == Entry::Int4Decode) {
-        const int tiles = n > 0 ? n / 16 : 0;
-        const int sms = sm_count();
-        out->grid[0] = (unsigned)(tiles < sms ? tiles : sms);
+        int slots = 0, unit_k = 0;
+        decode_launch_geometry(m, n, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &slots, &unit_k);
         out->grid[1] = out->grid[2] = 1;
-        out->block[0] = 544; out->block[1] = out->block[2] = 1;
+        out->block[1] = out->block[2] = 1;
         out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
-        const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
-        const int slots = nt == 1 ? 10 : (nt == 2 ? 8 : 6), round_tiles = nt == 4 ? 3 : 5;
-        out->dyn_smem_bytes = (unsigned)(slots * 16896 + 16 * round_tiles * nt * 128 * 4 + 2 * slots * 8 + 16);
-        out->cta_m = 8 * nt; out->cta_n = 16; out->cta_k = 2048; out->stages = slots;
+        out->cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32); out->cta_n = 16; out->cta_k = unit_k; out->stages = slots;
         return 0;
     }
     int rc = y_b200_gemm_fp8_launch_info(m, n, kk, 0, out);
