@@ -19,7 +19,6 @@ import json
 import os
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -48,85 +47,90 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+_REASON_NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+
+def clock_sampler_main(gpu_id: str):
+    """Child process: reads SM clock, power and throttle reasons of one GPU through NVML
+    (read-only queries) as fast as NVML answers and prints one line per sample,
+    stamped with the system-wide monotonic clock, until its stdin closes."""
+    import select
+
+    import pynvml as nv
+
+    nv.nvmlInit()
+    uuid, _, index = gpu_id.partition("|")  # "GPU-<uuid>|<index>": the index is the fallback
+    try:
+        h = nv.nvmlDeviceGetHandleByUUID(uuid.encode())
+    except Exception:
+        h = nv.nvmlDeviceGetHandleByIndex(int(index or 0))
+    mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+    bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+    out = []
+    print("ready", flush=True)
+    while not select.select([sys.stdin], [], [], 0.0)[0]:
+        t = time.monotonic()
+        mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+        out.append("%.6f,%d,%d,%.1f,%s" % (t, mhz, mx, pw, ",".join("1" if r & bits[n] else "0" for n in _REASON_NAMES)))
+        if len(out) > 200000:
+            break
+    sys.stdout.write("\n".join(out) + "\n")
+    sys.stdout.flush()
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    """Samples one GPU's SM clock and throttle reasons from a child process (a thread of
+    this process is starved by the launch loop) and reports the samples that fall
+    inside named windows of the monotonic clock."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
-        self._nv = None
-        try:  # initialise NVML up front so sampling starts with the timed region
-            import pynvml as nv
-
-            nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            self._nv = (nv, h, nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+    def __init__(self, gpu_id: str):
+        self.windows, self.samples, self.proc = {}, [], None
+        try:
+            self.proc = subprocess.Popen([sys.executable, os.path.abspath(__file__), "--clock-sampler", gpu_id],
+                                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                                         text=True)
+            if self.proc.stdout.readline().strip() != "ready":
+                self.proc = None
         except Exception:
-            self._nv = None
+            self.proc = None
 
-    def _run_nvml(self) -> bool:
-        """Fast path: read clocks and reasons through NVML (read-only queries)."""
-        if self._nv is None:
-            return False
-        nv, h, mx = self._nv
-        bits = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
-                "hw_thermal_slowdown": 0x40}
-        while not self._stop.is_set():
-            try:
-                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
-                flags = ["Active" if r & bits[n] else "Not Active"
-                         for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
-                self.samples.append([str(mhz), str(mx), str(pw)] + flags)
-            except Exception:
-                pass
-            self._stop.wait(0.0005)
-        return True
+    def window(self, name):
+        sampler = self
 
-    def _run(self):
-        if self._run_nvml():
+        class _W:
+            def __enter__(self):
+                self.t0 = time.monotonic()
+
+            def __exit__(self, *exc):
+                sampler.windows[name] = (self.t0, time.monotonic())
+
+        return _W()
+
+    def close(self):
+        if self.proc is None:
             return
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True,
-                                     timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([s.strip() for s in out.split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.05)
+        try:
+            out, _ = self.proc.communicate(input="stop\n", timeout=30)
+            for ln in out.splitlines():
+                f = ln.split(",")
+                if len(f) == 8:
+                    self.samples.append((float(f[0]), float(f[1]), float(f[2]), float(f[3]), [v == "1" for v in f[4:]]))
+        except Exception:
+            self.proc.kill()
+        self.proc = None
 
-    def __enter__(self):
-        self._t = threading.Thread(target=self._run, daemon=True)
-        self._t.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        self._t.join(timeout=10)
-
-    def summary(self):
-        mhz, mx, reasons, watts = [], 0.0, set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            try:
-                mhz.append(float(s[0]))
-                mx = max(mx, float(s[1]))
-                watts.append(float(s[2]))
-            except (ValueError, IndexError):
-                continue
-            for name, v in zip(names, s[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        mhz.sort()
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(mhz), "sm_mhz_min": mhz[0] if mhz else None,
-                "power_w_max": max(watts) if watts else None}
+    def summary(self, name):
+        t0, t1 = self.windows.get(name, (0.0, -1.0))
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        mhz = sorted(s[1] for s in inside)
+        reasons = sorted({n for s in inside for n, on in zip(_REASON_NAMES, s[4]) if on})
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                "sm_max_mhz": max((s[2] for s in inside), default=None), "reasons": reasons,
+                "samples": len(mhz), "sm_mhz_min": mhz[0] if mhz else None,
+                "power_w_max": max((s[3] for s in inside), default=None),
+                "window_ms": (t1 - t0) * 1e3 if inside else None}
 
 
 def cpu_step_sample(rows: int, seed: int = 1234):
@@ -235,6 +239,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
+    uuid = str(torch.cuda.get_device_properties(local).uuid)
+    clk = ClockSampler(("" if uuid.startswith("GPU-") else "GPU-") + uuid + "|" + str(local))
 
     # ---- synthetic inputs (seeded; same X on every rank, a different weight shard per rank)
     gen = torch.Generator(device=dev)
@@ -289,9 +295,8 @@ def run_ours(args):
     q.device_status()
 
     # ---- device-resident timed region
-    with ClockSampler(local) as clk:
+    with clk.window("value"):
         ms = timed(lambda: step(x, record=True), args.steps)
-    clocks = clk.summary()
     ms_per_step = ms / args.steps
     flops_step = 2.0 * M * K * N_SHARD * world
     value = flops_step / (ms_per_step * 1e-3) / 1e12
@@ -309,7 +314,11 @@ def run_ours(args):
 
     for _ in range(2):
         e2e_step()
-    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    with clk.window("e2e"):
+        e2e_ms = timed(e2e_step, args.steps) / args.steps
+    clk.close()
+    clocks = clk.summary("value")
+    clocks["e2e_region"] = clk.summary("e2e")
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
 
     # ---- the exchange step, reported separately
@@ -382,13 +391,16 @@ TRAFFIC_BYTES_PER_LAUNCH = None
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the INT4 decode section")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-rows", type=int, default=64)
+    ap.add_argument("--clock-sampler", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
+    if args.clock_sampler is not None:
+        return clock_sampler_main(args.clock_sampler)
     # Only the JSON line may reach stdout: libraries (NCCL prints its version there) write
     # to file descriptor 1 directly, so point it at stderr and keep the real one aside.
     sys.stdout.flush()

@@ -110,6 +110,8 @@ typedef struct y_b200_gemm_fp8_args {
     float* amax_out;   /* EPI_SWIGLU only */
     int cta_n;         /* 0 = pick from the tile table; else 64, 128 or 256 */
     int max_ctas;      /* 0 = one persistent CTA per SM */
+    int cta_m;         /* 0 = pick from the tile table; 128 = one CTA per tile; 256 = a pair of
+                          CTAs (cluster of 2) shares each 256 x 256 tile (needs cta_n 0 or 256) */
 } y_b200_gemm_fp8_args;
 
 Y_B200_API int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* args, void* stream);

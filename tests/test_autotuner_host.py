@@ -104,6 +104,8 @@ def test_launchability_follows_the_kernels_contract():
     assert not lib.y_autotune_is_launchable(u32(128, 256, 128, 4, 1, 4), 4100, FP8)  # K % 16
     assert not lib.y_autotune_is_launchable(u32(64, 64, 64, 2, 2, 3), 4096, FP8)     # an sm_89 tile
     assert not lib.y_autotune_is_launchable(u32(128, 256, 128, 0, 1, 4), 4096, FP8)
+    assert lib.y_autotune_is_launchable(u32(256, 256, 128, 4, 1, 6), 4096, FP8)      # CTA pair
+    assert not lib.y_autotune_is_launchable(u32(256, 128, 128, 4, 1, 6), 4096, FP8)  # the pair has one shape
     assert lib.y_autotune_is_launchable(u32(8, 16, 1024, 8, 1, 20), 4096, INT4)
     assert not lib.y_autotune_is_launchable(u32(8, 16, 1024, 8, 1, 20), 4000, INT4)
 
@@ -113,6 +115,12 @@ def test_analytic_score_prefers_wide_tiles_unless_the_grid_starves():
     assert big[0] > big[1] > big[2]
     small = [lib.y_autotune_score(u32(128, n, 128, 4, 1, 4), 256, 256, 256, FP8) for n in (256, 128, 64)]
     assert small[2] > small[0]
+    # the CTA-pair tile halves the A traffic again: it wins where the grid is full, and
+    # is not offered where its second CTA would only multiply padding
+    pair = u32(256, 256, 128, 4, 1, 6)
+    assert lib.y_autotune_score(pair, 8192, 8192, 8192, FP8) > big[0]
+    assert runtime.autotune_select_config(8192, 8192, 8192, True)["cta_m"] == 256
+    assert runtime.autotune_select_config(128, 8192, 8192, True)["cta_m"] == 128
 
 
 def rows(*r):

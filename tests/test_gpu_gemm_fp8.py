@@ -42,16 +42,40 @@ def test_exact_integer_gemm(q, m, n, k, cta_n):
     assert np.array_equal(c.cpu().numpy().astype(np.float64), ref)
 
 
+@pytest.mark.parametrize("m,n,k", [
+    (256, 256, 128), (256, 256, 512), (512, 768, 512),       # whole 256 x 256 tiles
+    (300, 500, 384), (513, 257, 256), (17, 9, 64), (130, 130, 192), (200, 72, 80),  # ragged, K tail
+    (2048, 2304, 1024), (4864, 4864, 256),                   # several tiles per CTA pair; 19 x 19 tiles
+])
+def test_exact_integer_gemm_cta_pair(q, m, n, k):
+    """The cta_group::2 kernel: two CTAs of a cluster share each 256 x 256 tile."""
+    aq, av = _int_codes((m, k), 3000 + m + k)
+    bq, bv = _int_codes((n, k), 4000 + n + k)
+    ref = av.astype(np.float64) @ bv.astype(np.float64).T
+    c = q.gemm_fp8_codes(dev(aq), dev(bq), 1.0, 1.0, cta_m=256)
+    q.device_status()
+    assert np.array_equal(c.cpu().numpy().astype(np.float64), ref)
+    # an odd CTA budget is rounded down to whole pairs
+    c = q.gemm_fp8_codes(dev(aq), dev(bq), 1.0, 1.0, cta_m=256, max_ctas=5)
+    q.device_status()
+    assert np.array_equal(c.cpu().numpy().astype(np.float64), ref)
+
+
 def test_every_cta_n_agrees_and_repeated_launches_are_bit_identical(q):
     m, n, k = 640, 768, 512
     _, _, sa, sb, aq, bqt = quantised_operands(m, n, k)
     ad, bd = dev(aq), dev(bqt)
     outs = [q.gemm_fp8_codes(ad, bd, sa, sb, cta_n=t) for t in (64, 128, 256)]
+    outs.append(q.gemm_fp8_codes(ad, bd, sa, sb, cta_m=256))
     q.device_status()
+    for o in outs[:3]:
+        assert torch.equal(outs[3], o)  # the K order of the accumulation does not depend on the tile
     # the shared-memory race detector of the reference harness: relaunch with fixed
     # inputs, require bit-identical output (tests/test_fp8_gemm_correctness.py:156-171)
     for _ in range(20):
         again = q.gemm_fp8_codes(ad, bd, sa, sb, cta_n=256)
+        assert torch.equal(again, outs[2])
+        again = q.gemm_fp8_codes(ad, bd, sa, sb, cta_m=256)
         assert torch.equal(again, outs[2])
     ref = oracle.gemm_fp8(aq, bqt, sa, sb)
     for o in outs:
@@ -65,16 +89,18 @@ def test_scale_epilogue_and_output_types(q, m, n, k, out):
     kind = {"f32": oracle.OUT_F32, "f16": oracle.OUT_F16, "bf16": oracle.OUT_BF16}[out]
     dt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[out]
     sad = torch.tensor([sa], dtype=torch.float32, device="cuda")
-    c = q.gemm_fp8_codes(dev(aq), dev(bqt), sad, sb, out_dtype=dt)  # one device scale, one by value
-    q.device_status()
     ref = oracle.gemm_fp8(aq, bqt, sa, sb, out_kind=kind)
-    got = c.cpu().numpy() if out == "f32" else host_bits(c)
-    assert_gemm_close(to_f64(got, kind), to_f64(ref, kind), out)
+    for cta_m in (128, 256):
+        c = q.gemm_fp8_codes(dev(aq), dev(bqt), sad, sb, out_dtype=dt, cta_m=cta_m)  # one device scale, one by value
+        q.device_status()
+        got = c.cpu().numpy() if out == "f32" else host_bits(c)
+        assert_gemm_close(to_f64(got, kind), to_f64(ref, kind), out)
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 512, 256), (130, 72, 192)])
 @pytest.mark.parametrize("bias_dtype", ["f16", "f32"])
-def test_bias_relu_epilogue(q, m, n, k, bias_dtype):
+@pytest.mark.parametrize("cta_m", [128, 256])
+def test_bias_relu_epilogue(q, m, n, k, bias_dtype, cta_m):
     _, _, sa, sb, aq, bqt = quantised_operands(m, n, k)
     bias = oracle.fill_normal_f16(n, oracle.SEED_B + 1, 0.1)
     if bias_dtype == "f16":
@@ -83,7 +109,8 @@ def test_bias_relu_epilogue(q, m, n, k, bias_dtype):
         bo = bias.view(np.float16).astype(np.float32)
         bd = dev(bo)
     for epi, oepi in ((q.EPI_BIAS, oracle.EPI_BIAS), (q.EPI_BIAS_RELU, oracle.EPI_BIAS_RELU)):
-        c = q.gemm_fp8_codes(dev(aq), dev(bqt), sa, sb, bias=bd, epilogue=epi, out_dtype=torch.bfloat16)
+        c = q.gemm_fp8_codes(dev(aq), dev(bqt), sa, sb, bias=bd, epilogue=epi, out_dtype=torch.bfloat16,
+                             cta_m=cta_m)
         q.device_status()
         ref = oracle.gemm_fp8(aq, bqt, sa, sb, bias=bo, epilogue=oepi, out_kind=oracle.OUT_BF16)
         got = to_f64(host_bits(c), oracle.OUT_BF16)
@@ -93,9 +120,10 @@ def test_bias_relu_epilogue(q, m, n, k, bias_dtype):
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 512, 256), (100, 88, 128)])
-def test_swiglu_requant(q, m, n, k):
+@pytest.mark.parametrize("cta_m", [128, 256])
+def test_swiglu_requant(q, m, n, k, cta_m):
     a, b, sa, sb, aq, bqt = quantised_operands(m, n, k)
-    codes, scale, h = q.gemm_fp8_swiglu_requant(dev(aq), dev(bqt), sa, sb)
+    codes, scale, h = q.gemm_fp8_swiglu_requant(dev(aq), dev(bqt), sa, sb, cta_m=cta_m)
     q.device_status()
     h_ref = oracle.gemm_fp8(aq, bqt, sa, sb, epilogue=oracle.EPI_SWIGLU, out_kind=oracle.OUT_BF16)
     h_got = host_bits(h)
@@ -180,4 +208,7 @@ def test_preconditions_are_errors(q):
     a = torch.zeros(16, 32, dtype=torch.uint8, device="cuda")
     with pytest.raises(YB200Error) as e:
         q.gemm_fp8_codes(a, a, 1.0, 1.0, epilogue=q.EPI_BIAS)  # bias epilogue, no bias
+    assert e.value.code == ERR_INVALID
+    with pytest.raises(YB200Error) as e:
+        q.gemm_fp8_codes(a, a, 1.0, 1.0, cta_m=256, cta_n=128)  # the CTA pair has one tile shape
     assert e.value.code == ERR_INVALID

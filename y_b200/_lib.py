@@ -35,7 +35,7 @@ class GemmFp8Args(C.Structure):
         ("bias", C.c_void_p), ("bias_kind", C.c_int),
         ("epilogue", C.c_int), ("out_kind", C.c_int),
         ("amax_out", C.c_void_p),
-        ("cta_n", C.c_int), ("max_ctas", C.c_int),
+        ("cta_n", C.c_int), ("max_ctas", C.c_int), ("cta_m", C.c_int),
     ]
 
 

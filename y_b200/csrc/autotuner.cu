@@ -128,6 +128,10 @@ std::vector<Candidate> generate_candidates(uint32_t m, uint32_t n, uint32_t k, P
         return out;
     }
     const uint32_t cta_k = p == Precision::Fp8 ? 128u : 64u;
+    // cta_m = 256: a pair of CTAs (cluster of 2) shares each 256 x 256 tile; per CTA a
+    // stage is 16 KB of A + 16 KB of B, so 6 stages fit. With a single 128-row block of A
+    // the second CTA of the pair would only multiply padding.
+    if (p == Precision::Fp8 && m > 128) out.push_back({256, 256, cta_k, 4, 1, 6, 4});
     out.push_back({128, 256, cta_k, 4, 1, 4, 4});
     out.push_back({128, 128, cta_k, 4, 1, 6, 4});
     out.push_back({128, 64, cta_k, 4, 1, 8, 4});
@@ -139,8 +143,9 @@ bool is_launchable(const Candidate& c, uint32_t k, Precision p) {
     if (p == Precision::Int4)
         return c.cta_n == 16 && (c.cta_m == 8 || c.cta_m == 16 || c.cta_m == 32) && k % 128 == 0;
     const uint32_t ebytes = p == Precision::Fp8 ? 1u : 2u;
-    return c.cta_m == 128 && (c.cta_n == 64 || c.cta_n == 128 || c.cta_n == 256) &&
-           c.cta_k * ebytes == 128 && (k * ebytes) % 16 == 0 && c.num_stages >= 2;
+    const bool one_cta = c.cta_m == 128 && (c.cta_n == 64 || c.cta_n == 128 || c.cta_n == 256);
+    const bool cta_pair = p == Precision::Fp8 && c.cta_m == 256 && c.cta_n == 256;
+    return (one_cta || cta_pair) && c.cta_k * ebytes == 128 && (k * ebytes) % 16 == 0 && c.num_stages >= 2;
 }
 
 // Analytic fallback: wave efficiency on `sm_count` persistent CTAs times the
@@ -151,8 +156,9 @@ double score_candidate(const Candidate& c, uint32_t m, uint32_t n, uint32_t k, P
     (void)k;
     if (p == Precision::Int4) return 1.0;
     const double tiles = ceil((double)m / c.cta_m) * ceil((double)n / c.cta_n);
-    const double waves = ceil(tiles / (double)sm_count);
-    const double wave_eff = tiles / (waves * sm_count);
+    const double slots = floor((double)sm_count * 128.0 / c.cta_m);  // a 256-row tile occupies two SMs
+    const double waves = ceil(tiles / slots);
+    const double wave_eff = tiles / (waves * slots);
     const double useful = ((double)m * n) / (tiles * c.cta_m * c.cta_n);  // ragged-edge waste
     const double traffic = 1.0 / c.cta_m + 1.0 / c.cta_n;
     return wave_eff * useful / traffic;
@@ -462,6 +468,7 @@ int tune_gemm_fp8(uint32_t m, uint32_t n, uint32_t k, std::vector<Measured>* out
         g.scale_a = s; g.scale_b = s;
         g.out_kind = Y_B200_BF16;
         g.cta_n = (int)cand.cta_n;
+        g.cta_m = (int)cand.cta_m;
         if (y_b200_gemm_fp8(&g, nullptr) || y_b200_device_status(nullptr)) continue;
         double num = 0.0, den = 0.0;
         bool ok = true;

@@ -208,18 +208,23 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         if (k.k % 64 != 0) return std::string();  // caller reports the K precondition
         Candidate c = autotune((uint32_t)k.m, (uint32_t)k.n, (uint32_t)k.k, Precision::Fp8,
                                "NVIDIA B200", 148);
+        const bool pair = c.cta_m == 256;  // a cluster of two CTAs per 256 x 256 tile
         const long long tiles = ((k.m + c.cta_m - 1) / c.cta_m) * ((k.n + c.cta_n - 1) / c.cta_n);
-        const long long grid = tiles < 148 ? tiles : 148;
-        const unsigned smem = c.num_stages * (128u * 128u + c.cta_n * 128u) + (2 * c.num_stages + 4) * 8 + 16 + 1024;
+        const long long ctas = pair ? 2 * tiles : tiles;
+        const long long cap = pair ? 148 & ~1 : 148;
+        const long long grid = ctas < cap ? ctas : cap;
+        // Per CTA and stage: 128 rows of A, and of B either the whole N tile or half of the pair's.
+        const unsigned b_rows = pair ? 128u : c.cta_n;
+        const unsigned smem = c.num_stages * (128u * 128u + b_rows * 128u) + (2 * c.num_stages + 4) * 8 + 16 + 1024;
         snprintf(buf, sizeof buf,
                  "// [Y FP8 TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %ux%ux%u | %ux%u warps | "
-                 "tcgen05.mma.cta_group::1.kind::f8f6f4 e4m3 x e4m3 -> f32 (TMEM)\n"
+                 "tcgen05.mma.cta_group::%d.kind::f8f6f4 e4m3 x e4m3 -> f32 (TMEM)\n"
                  "// Operands are quantised to e4m3 by separate HBM-bound kernels; epilogue dequants by scale_a*scale_b.\n"
-                 "// Launch grid required: (%lld, 1, 1) CTAs, block (192,1,1); persistent over %lld tiles, %u stages.\n"
+                 "// Launch grid required: (%lld, 1, 1) CTAs, block (192,1,1), cluster (%d,1,1); persistent over %lld tiles, %u stages.\n"
                  "// Dynamic shared memory required: %u bytes.\n"
                  "// Workspace required: %zu bytes.\n",
-                 k.m, k.n, k.k, c.cta_m, c.cta_n, c.cta_k, c.warps_m, c.warps_n, grid, tiles,
-                 c.num_stages, smem,
+                 k.m, k.n, k.k, c.cta_m, c.cta_n, c.cta_k, c.warps_m, c.warps_n, pair ? 2 : 1, grid,
+                 pair ? 2 : 1, tiles, c.num_stages, smem,
                  y_b200_gemm_fp8_f32_workspace_bytes((int)k.m, (int)k.n, (int)k.k));
         out += buf;
     } else if (fam == KernelFamily::RmsnormResidual) {

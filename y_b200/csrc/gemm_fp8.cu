@@ -128,6 +128,76 @@ __device__ __forceinline__ void store_vec(void* dst, const float* v) {
     }
 }
 
+// Drains one accumulator of BN columns for this thread's row: TMEM lane -> registers
+// (32 columns at a time) -> scale (+ bias, ReLU | SwiGLU with running amax) -> global.
+// `t_addr` already carries the warp's lane quarter; `col_base` is the tile's first column.
+template <int BN, int EPI, int OUT>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_addr, int row, int col_base,
+                                                  float scale, bool rows_aligned, int n_out,
+                                                  uint32_t& amax_bits) {
+    constexpr int esize = OUT == Y_B200_F32 ? 4 : 2;
+#pragma unroll 1
+    for (int ch = 0; ch < BN / 32; ++ch) {
+        const int col0 = col_base + ch * 32;
+        if (col0 >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + ch * 32, r);
+        tc_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * scale;
+
+        if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int col = col0 + j;
+                float b = 0.0f;
+                if (col < p.n)
+                    b = p.bias_kind == Y_B200_F16 ? __half2float(__ldg(static_cast<const __half*>(p.bias) + col))
+                                                  : __ldg(static_cast<const float*>(p.bias) + col);
+                v[j] += b;
+                if (EPI == Y_B200_EPI_BIAS_RELU) v[j] = fmaxf(v[j], 0.0f);
+            }
+        }
+
+        if (EPI == Y_B200_EPI_SWIGLU) {
+            // columns 2j (gate) and 2j+1 (up) -> output column col0/2 + j
+            float h[16];
+            uint32_t packed[8];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) h[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                packed[j] = pack_bf16x2(h[2 * j], h[2 * j + 1]);
+                // amax over the bf16-rounded values, as f32 bit patterns
+                amax_bits = max(amax_bits, (packed[j] << 16) & 0x7fffffffu);
+                amax_bits = max(amax_bits, packed[j] & 0x7fff0000u);
+            }
+            if (row < p.m) {
+                const int ocol0 = col0 / 2;
+                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + (size_t)row * n_out + ocol0;
+                if (rows_aligned && col0 + 32 <= p.n) {
+                    uint4* d = reinterpret_cast<uint4*>(dst);
+                    d[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    d[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (ocol0 + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
+                }
+            }
+        } else if (row < p.m) {
+            if (rows_aligned && col0 + 32 <= p.n) {
+                store_vec<OUT, 32>(static_cast<char*>(p.c) + ((size_t)row * p.n + col0) * esize, v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (col0 + j < p.n) store_scalar<OUT>(p.c, (size_t)row * p.n + col0 + j, v[j]);
+            }
+        }
+    }
+}
+
 template <int BN, int EPI, int OUT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -260,67 +330,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tc_fence_after();
             const int row = tm * kCtaM + quarter * 32 + lane;
             const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-#pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                const int col0 = tn * BN + ch * 32;
-                if (col0 >= p.n) break;  // uniform across the warp
-                uint32_t r[32];
-                tmem_ld_32x32(t_addr + ch * 32, r);
-                tc_wait_ld();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * scale;
-
-                if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int col = col0 + j;
-                        float b = 0.0f;
-                        if (col < p.n)
-                            b = p.bias_kind == Y_B200_F16
-                                    ? __half2float(__ldg(static_cast<const __half*>(p.bias) + col))
-                                    : __ldg(static_cast<const float*>(p.bias) + col);
-                        v[j] += b;
-                        if (EPI == Y_B200_EPI_BIAS_RELU) v[j] = fmaxf(v[j], 0.0f);
-                    }
-                }
-
-                if (EPI == Y_B200_EPI_SWIGLU) {
-                    // columns 2j (gate) and 2j+1 (up) -> output column col0/2 + j
-                    float h[16];
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) h[j] = silu_mul(v[2 * j], v[2 * j + 1]);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        packed[j] = pack_bf16x2(h[2 * j], h[2 * j + 1]);
-                        // amax over the bf16-rounded values, as f32 bit patterns
-                        amax_bits = max(amax_bits, (packed[j] << 16) & 0x7fffffffu);
-                        amax_bits = max(amax_bits, packed[j] & 0x7fff0000u);
-                    }
-                    if (row < p.m) {
-                        const int ocol0 = col0 / 2;
-                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + (size_t)row * n_out + ocol0;
-                        if (rows_aligned && col0 + 32 <= p.n) {
-                            uint4* d = reinterpret_cast<uint4*>(dst);
-                            d[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                            d[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (ocol0 + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
-                        }
-                    }
-                } else if (row < p.m) {
-                    if (rows_aligned && col0 + 32 <= p.n) {
-                        store_vec<OUT, 32>(static_cast<char*>(p.c) + ((size_t)row * p.n + col0) * esize, v);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < p.n) store_scalar<OUT>(p.c, (size_t)row * p.n + col0 + j, v[j]);
-                    }
-                }
-            }
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, tn * BN, scale, rows_aligned, n_out, amax_bits);
             // This thread's TMEM reads are complete (wait::ld above): hand the
             // accumulator buffer back to the MMA warp.
             tc_fence_before();
@@ -340,6 +350,171 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::tmem_cols);
+    }
+}
+
+// ---- CTA-pair variant: 256 x 256 tile per pair of SMs -------------------------------------
+// Same roles and rings as gemm_fp8_kernel, but two CTAs of a cluster share each MMA
+// (tcgen05.mma.cta_group::2, M = 256): CTA r of the pair loads rows [128r, 128r+128) of the
+// A tile and rows [128r, 128r+128) of the 256-row B tile into its own shared memory and
+// keeps accumulator rows [128r, 128r+128) in its own tensor memory. Per k-block an SM
+// stages 32 KB instead of 48 KB (6 stages instead of 4 fit) for the same MMA work, which
+// is what the L2 -> SM path and the power budget care about. The even CTA's MMA thread
+// issues; completion is signalled to both CTAs' barriers. No load is shared between CTAs.
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = 2 * kCtaM * kCtaK;  // 16 KB of A + 16 KB of B per CTA
+constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairBarBytes + 1024;
+
+template <int EPI, int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+    constexpr int BN = 256;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t ring0 = (raw_addr + 1023u) & ~1023u;
+    uint8_t* ring_ptr = smem_raw + (ring0 - raw_addr);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + kPairStages * kPairStageBytes);
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = full0 + 8 * kPairStages;
+    const uint32_t tfull0 = empty0 + 8 * kPairStages;
+    const uint32_t tempty0 = tfull0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int num_tiles = p.m_tiles * p.n_tiles;  // tiles of 256 x 256
+    const int num_kb = (p.k + kCtaK - 1) / kCtaK;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(full0 + 8 * s, 1);   // the even CTA's producer arrives; bytes come from both CTAs
+            mbar_init(empty0 + 8 * s, 1);  // one commit per use
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull0 + 8 * a, 1);
+            mbar_init(tempty0 + 8 * a, 8);  // 4 epilogue warps of each CTA (used in the even CTA only)
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_slot), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both CTAs) --------------------
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                int tm, tn;
+                tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) {
+                        report_timeout(p.status, abort_flag, 0x10u, (unsigned)kb);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = ring0 + stage * kPairStageBytes;
+                    if (leader) mbar_expect_tx(full0 + 8 * stage, 2 * kPairStageBytes);
+                    tma_load_2d_pair(dst, &tmap_a, full0 + 8 * stage, kb * kCtaK, tm * 256 + (int)rank * kCtaM);
+                    tma_load_2d_pair(dst + kCtaM * kCtaK, &tmap_b, full0 + 8 * stage, kb * kCtaK,
+                                     tn * BN + (int)rank * 128);
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (even CTA only) ------------------
+        if (leader && elect_one()) {
+            constexpr uint32_t idesc = make_idesc(256, BN, 0u, 0u);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+                const uint32_t as = it & 1, aphase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * as, aphase ^ 1u, abort_flag)) {
+                    report_timeout(p.status, abort_flag, 0x20u, (unsigned)it);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase, abort_flag)) {
+                        report_timeout(p.status, abort_flag, 0x21u, (unsigned)kb);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = ring0 + stage * kPairStageBytes;
+                    const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + kCtaM * kCtaK);
+#pragma unroll
+                    for (int k = 0; k < kCtaK / kUmmaK; ++k)
+                        umma_f8f6f4_pair(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
+                                         b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc, (uint32_t)((kb | k) != 0));
+                    tc_commit_pair(empty0 + 8 * stage, 3);  // both CTAs' stages are free again
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit_pair(tfull0 + 8 * as, 3);  // accumulator complete in both CTAs
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (both CTAs, own 128 rows) ------------
+        const int quarter = warp & 3;
+        const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
+                            (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
+        constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
+        const int n_out = p.n / out_div;
+        constexpr int esize = OUT == Y_B200_F32 ? 4 : 2;
+        const bool rows_aligned = ((size_t)n_out * esize) % 16 == 0 &&
+                                  (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0;
+        const uint32_t tempty_leader = mapa_shared(tempty0, 0);
+        uint32_t amax_bits = 0;
+        bool dead = false;
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+            int tm, tn;
+            tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+            const uint32_t as = it & 1, aphase = (it >> 1) & 1;
+            if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
+                report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
+                dead = true;
+            }
+            if (dead) break;
+            tc_fence_after();
+            const int row = tm * 256 + (int)rank * kCtaM + quarter * 32 + lane;
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, tn * BN, scale, rows_aligned, n_out, amax_bits);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * as);
+        }
+        if (EPI == Y_B200_EPI_SWIGLU && p.amax_out != nullptr) {
+            amax_bits = warp_max_u32(amax_bits);
+            if (lane == 0 && amax_bits != 0u) atomicMax(p.amax_out, amax_bits);
+        }
+    }
+
+    // Neither CTA may leave while its partner can still touch its barriers or memory.
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -379,10 +554,30 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int k, int bo
 
 // Tile choice goes through the autotuner: override, caches, persisted
 // measurement, (optional) fresh measurement, analytic score.
-int pick_cta_n(int m, int n, int k) {
+struct TileShape {
+    int cta_m;  // 128: one CTA per tile; 256: a CTA pair per tile
+    int cta_n;
+};
+
+// `want_m` / `want_n` are the caller's overrides (0 = no preference).
+TileShape pick_tile(int m, int n, int k, int want_m, int want_n) {
+    if (want_m == 256) return {256, 256};
+    if (want_n != 0) return {128, want_n};
+    if (want_m == 128) {
+        // Best one-CTA tile by the analytic score.
+        TileShape best = {128, 256};
+        double best_score = -1.0;
+        for (const Candidate& cand : generate_candidates((uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8)) {
+            if (cand.cta_m != 128 || !is_launchable(cand, (uint32_t)k, Precision::Fp8)) continue;
+            const double s = score_candidate(cand, (uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8, sm_count());
+            if (s > best_score) { best_score = s; best = {128, (int)cand.cta_n}; }
+        }
+        return best;
+    }
     const Candidate c = autotune((uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8,
                                  current_gpu_name(), sm_count());
-    return (c.cta_n == 64 || c.cta_n == 128 || c.cta_n == 256) ? (int)c.cta_n : 256;
+    if (c.cta_m == 256 && c.cta_n == 256) return {256, 256};
+    return {128, (c.cta_n == 64 || c.cta_n == 128 || c.cta_n == 256) ? (int)c.cta_n : 256};
 }
 
 template <int BN, int EPI, int OUT>
@@ -427,6 +622,46 @@ int launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
     return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad epilogue %d", epi);
 }
 
+template <int EPI, int OUT>
+int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                    cudaStream_t st) {
+    static bool configured[64] = {};
+    int dev = 0;
+    YB_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        YB_CUDA(cudaFuncSetAttribute(gemm_fp8_pair_kernel<EPI, OUT>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+        configured[dev] = true;
+    }
+    gemm_fp8_pair_kernel<EPI, OUT><<<grid, kGemmThreads, kPairSmemBytes, st>>>(ta, tb, p);
+    return check_cuda(cudaGetLastError(), "gemm_fp8_pair_kernel launch");
+}
+
+template <int EPI>
+int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_kind,
+                    int grid, cudaStream_t st) {
+    switch (out_kind) {
+        case Y_B200_F32: return launch_pair_one<EPI, Y_B200_F32>(ta, tb, p, grid, st);
+        case Y_B200_F16: return launch_pair_one<EPI, Y_B200_F16>(ta, tb, p, grid, st);
+        case Y_B200_BF16: return launch_pair_one<EPI, Y_B200_BF16>(ta, tb, p, grid, st);
+    }
+    return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad out_kind %d", out_kind);
+}
+
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int epi, int out_kind,
+                int grid, cudaStream_t st) {
+    switch (epi) {
+        case Y_B200_EPI_NONE: return launch_pair_out<Y_B200_EPI_NONE>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS: return launch_pair_out<Y_B200_EPI_BIAS>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_RELU: return launch_pair_out<Y_B200_EPI_BIAS_RELU>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_SWIGLU:
+            if (out_kind != Y_B200_BF16)
+                return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: the SwiGLU epilogue writes bf16");
+            return launch_pair_one<Y_B200_EPI_SWIGLU, Y_B200_BF16>(ta, tb, p, grid, st);
+    }
+    return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad epilogue %d", epi);
+}
+
 int validate(const y_b200_gemm_fp8_args* a) {
     if (!a) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: null argument block");
     if (!a->a || !a->bt || !a->c) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: null operand pointer");
@@ -445,7 +680,40 @@ int validate(const y_b200_gemm_fp8_args* a) {
         return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: SwiGLU needs an even N (gate|up pairs), got %d", a->n);
     if (a->cta_n != 0 && a->cta_n != 64 && a->cta_n != 128 && a->cta_n != 256)
         return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: cta_n must be 0, 64, 128 or 256");
+    if (a->cta_m != 0 && a->cta_m != 128 && a->cta_m != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: cta_m must be 0, 128 or 256");
+    if (a->cta_m == 256 && a->cta_n != 0 && a->cta_n != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: cta_m 256 (CTA pair) needs cta_n 0 or 256");
     return 0;
+}
+
+// Builds the tensor maps for `tile`, sizes the persistent grid and launches.
+// `p` arrives with everything but m_tiles / n_tiles filled in.
+int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, int epi, int out_kind,
+                 int max_ctas, cudaStream_t st) {
+    CUtensorMap ta, tb;
+    int rc;
+    // Every CTA loads 128 rows of A; of B it loads its whole N tile, or its 128-row half
+    // of the pair's 256.
+    if ((rc = make_operand_map(&ta, a, p.m, p.k, kCtaM))) return rc;
+    if ((rc = make_operand_map(&tb, bt, p.n, p.k, tile.cta_m == 256 ? 128 : tile.cta_n))) return rc;
+    p.m_tiles = (p.m + tile.cta_m - 1) / tile.cta_m;
+    p.n_tiles = (p.n + tile.cta_n - 1) / tile.cta_n;
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles > 0x3fffffffLL) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: too many tiles");
+    int cap = max_ctas > 0 ? max_ctas : sm_count();
+    if (tile.cta_m == 256) {
+        cap &= ~1;
+        if (cap < 2) cap = 2;
+        const int grid = (int)(2 * tiles < cap ? 2 * tiles : cap);
+        return launch_pair(ta, tb, p, epi, out_kind, grid, st);
+    }
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    switch (tile.cta_n) {
+        case 256: return launch_epi<256>(ta, tb, p, epi, out_kind, grid, st);
+        case 128: return launch_epi<128>(ta, tb, p, epi, out_kind, grid, st);
+        default: return launch_epi<64>(ta, tb, p, epi, out_kind, grid, st);
+    }
 }
 
 int smem_for(int bn) {
@@ -464,11 +732,8 @@ extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
     int rc = validate(a);
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int bn = a->cta_n ? a->cta_n : pick_cta_n(a->m, a->n, a->k);
-    CUtensorMap ta, tb;
-    if ((rc = make_operand_map(&ta, a->a, a->m, a->k, kCtaM))) return rc;
-    if ((rc = make_operand_map(&tb, a->bt, a->n, a->k, bn))) return rc;
-    GemmParams p;
+    const TileShape tile = pick_tile(a->m, a->n, a->k, a->cta_m, a->cta_n);
+    GemmParams p = {};
     p.c = a->c;
     p.m = a->m; p.n = a->n; p.k = a->k;
     p.scale_a = a->scale_a; p.scale_b = a->scale_b;
@@ -476,17 +741,7 @@ extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
     p.bias = a->bias; p.bias_kind = a->bias_kind;
     p.amax_out = reinterpret_cast<unsigned int*>(a->amax_out);
     p.status = device_status_ptr();
-    p.m_tiles = (a->m + kCtaM - 1) / kCtaM;
-    p.n_tiles = (a->n + bn - 1) / bn;
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    if (tiles > 0x7fffffffLL) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: too many tiles");
-    int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
-    const int grid = (int)(tiles < cap ? tiles : cap);
-    switch (bn) {
-        case 256: return launch_epi<256>(ta, tb, p, a->epilogue, a->out_kind, grid, st);
-        case 128: return launch_epi<128>(ta, tb, p, a->epilogue, a->out_kind, grid, st);
-        default: return launch_epi<64>(ta, tb, p, a->epilogue, a->out_kind, grid, st);
-    }
+    return launch_tiled(a->a, a->bt, p, tile, a->epilogue, a->out_kind, a->max_ctas, st);
 }
 
 extern "C" int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b200_launch_info* out) {
@@ -495,17 +750,22 @@ extern "C" int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b20
         return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8_launch_info: bad shape M=%d N=%d K=%d", m, n, k);
     if (cta_n != 0 && cta_n != 64 && cta_n != 128 && cta_n != 256)
         return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8_launch_info: cta_n must be 0, 64, 128 or 256");
-    const int bn = cta_n ? cta_n : pick_cta_n(m, n, k);
-    const long long tiles = (long long)((m + kCtaM - 1) / kCtaM) * ((n + bn - 1) / bn);
+    const TileShape tile = pick_tile(m, n, k, 0, cta_n);
+    const long long tiles = (long long)((m + tile.cta_m - 1) / tile.cta_m) * ((n + tile.cta_n - 1) / tile.cta_n);
     const int sms = sm_count();
-    out->grid[0] = (unsigned)(tiles < sms ? tiles : sms);
+    const bool pair = tile.cta_m == 256;
+    const long long ctas = pair ? 2 * tiles : tiles;
+    const int cap = pair ? (sms & ~1) : sms;
+    out->grid[0] = (unsigned)(ctas < cap ? ctas : cap);
     out->grid[1] = out->grid[2] = 1;
     out->block[0] = kGemmThreads;
     out->block[1] = out->block[2] = 1;
-    out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
-    out->dyn_smem_bytes = (unsigned)smem_for(bn);
+    out->cluster[0] = pair ? 2 : 1;
+    out->cluster[1] = out->cluster[2] = 1;
+    out->dyn_smem_bytes = pair ? (unsigned)kPairSmemBytes : (unsigned)smem_for(tile.cta_n);
     out->workspace_bytes = 0;
-    out->cta_m = kCtaM; out->cta_n = bn; out->cta_k = kCtaK; out->stages = stages_for(bn);
+    out->cta_m = tile.cta_m; out->cta_n = tile.cta_n; out->cta_k = kCtaK;
+    out->stages = pair ? kPairStages : stages_for(tile.cta_n);
     return 0;
 }
 
@@ -661,28 +921,12 @@ extern "C" int y_b200_gemm_fp8_f32_static(const float* a, const float* b, float 
     YB_CUDA(cudaMemsetAsync(status, 0, sizeof(DeviceStatus), st));
     if ((rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, slots, aq, st))) return rc;
     if ((rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, slots + 1, bq, st))) return rc;
-    // Tile from the analytic score only: no cache file, no measurement run.
-    int bn = 256;
-    double best = -1.0;
-    for (const Candidate& cand : generate_candidates((uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8)) {
-        const double s = score_candidate(cand, (uint32_t)m, (uint32_t)n, (uint32_t)k, Precision::Fp8, sm_count());
-        if (is_launchable(cand, (uint32_t)k, Precision::Fp8) && s > best) { best = s; bn = (int)cand.cta_n; }
-    }
-    CUtensorMap ta, tb;
-    if ((rc = make_operand_map(&ta, aq, m, k, kCtaM))) return rc;
-    if ((rc = make_operand_map(&tb, bq, n, k, bn))) return rc;
+    // One-CTA tile from the analytic score only: no cache file, no measurement run.
+    const TileShape tile = pick_tile(m, n, k, 128, 0);
     GemmParams p = {};
     p.c = c;
     p.m = m; p.n = n; p.k = k;
     p.scale_a = scale_a; p.scale_b = scale_b;
     p.status = status;
-    p.m_tiles = (m + kCtaM - 1) / kCtaM;
-    p.n_tiles = (n + bn - 1) / bn;
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    switch (bn) {
-        case 256: return launch_epi<256>(ta, tb, p, Y_B200_EPI_NONE, Y_B200_F32, grid, st);
-        case 128: return launch_epi<128>(ta, tb, p, Y_B200_EPI_NONE, Y_B200_F32, grid, st);
-        default: return launch_epi<64>(ta, tb, p, Y_B200_EPI_NONE, Y_B200_F32, grid, st);
-    }
+    return launch_tiled(aq, bq, p, tile, Y_B200_EPI_NONE, Y_B200_F32, 0, st);
 }

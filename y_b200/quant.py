@@ -125,9 +125,11 @@ def _scale_fields(args: GemmFp8Args, name: str, s) -> None:
 
 def gemm_fp8_codes(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b, *, bias=None,
                    epilogue: int = EPI_NONE, out_dtype=torch.float32, out: torch.Tensor | None = None,
-                   amax_out: torch.Tensor | None = None, cta_n: int = 0, max_ctas: int = 0):
+                   amax_out: torch.Tensor | None = None, cta_n: int = 0, max_ctas: int = 0,
+                   cta_m: int = 0):
     """C = epilogue((sa*sb) * aq @ bqt^T). aq [M, K], bqt [N, K] e4m3 codes
-    (uint8 or float8_e4m3fn). Scales are floats or 1-element f32 device tensors."""
+    (uint8 or float8_e4m3fn). Scales are floats or 1-element f32 device tensors.
+    cta_m / cta_n force a tile (cta_m 256 = the CTA-pair kernel); 0 asks the tile table."""
     _dev(aq, "aq"), _dev(bqt, "bqt")
     (m, k), (n, k2) = aq.shape, bqt.shape
     if k != k2:
@@ -145,7 +147,7 @@ def gemm_fp8_codes(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b, *, bia
         args.bias, args.bias_kind = bias.data_ptr(), _kind(bias, "bias")
     args.epilogue, args.out_kind = epilogue, out_kind
     args.amax_out = amax_out.data_ptr() if amax_out is not None else None
-    args.cta_n, args.max_ctas = cta_n, max_ctas
+    args.cta_n, args.max_ctas, args.cta_m = cta_n, max_ctas, cta_m
     check(lib.y_b200_gemm_fp8(C.byref(args), _stream()))
     return c
 
@@ -184,7 +186,7 @@ def gemm_fp8_f32(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: floa
 
 
 def gemm_fp8_swiglu_requant(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b,
-                            workspace: torch.Tensor | None = None, cta_n: int = 0):
+                            workspace: torch.Tensor | None = None, cta_n: int = 0, cta_m: int = 0):
     """silu(gate) * up on interleaved gate|up columns, re-quantised to e4m3 with
     a fresh per-tensor scale. Returns (codes [M, N/2], scale, h_bf16 view)."""
     _dev(aq, "aq"), _dev(bqt, "bqt")
@@ -198,7 +200,7 @@ def gemm_fp8_swiglu_requant(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_
     args.m, args.n, args.k = m, n, k
     _scale_fields(args, "scale_a", scale_a)
     _scale_fields(args, "scale_b", scale_b)
-    args.cta_n = cta_n
+    args.cta_n, args.cta_m = cta_n, cta_m
     args.c = ws.data_ptr()  # replaced by the library; must be non-null for validation
     check(lib.y_b200_gemm_fp8_swiglu_requant(C.byref(args), q.data_ptr(), s.data_ptr(),
                                              ws.data_ptr(), ws.numel(), _stream()))
