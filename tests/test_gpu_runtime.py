@@ -59,7 +59,7 @@ def test_compile_load_launch_matches_oracle(rt):
     with pytest.raises(YB200Error, match="no kernel named"):
         ctx.load_module(image, "gemm_fp8_512")
     info = kern.launch_info()
-    assert info.block[0] == 192 and info.dyn_smem_bytes > 48 * 1024 and info.workspace_bytes > 0
+    assert info.block[0] == 320 and info.dyn_smem_bytes > 48 * 1024 and info.workspace_bytes > 0
     kern.set_max_dynamic_smem(info.dyn_smem_bytes)
     m = n = k = 256
     rng = np.random.default_rng(1)
@@ -99,7 +99,7 @@ def test_measured_autotune_ranks_persists_and_is_reused(rt, tmp_path):
     lib.y_autotune_set_profile_path(str(prof).encode())
     try:
         ranked = json.loads(take_string(lib.y_autotune_measure_fp8_json(1024, 1024, 1024)))
-        assert 1 <= len(ranked) <= 3 and all(r["best_us"] > 0 and r["tflops"] > 1 for r in ranked)
+        assert 1 <= len(ranked) <= 4 and all(r["best_us"] > 0 and r["tflops"] > 1 for r in ranked)
         assert all(r["best_us"] <= r["median_us"] <= r["max_us"] for r in ranked)
         text = prof.read_text()
         assert text.startswith("AUTOTUNE_FP8_1024x1024x1024_NVIDIAB200=")

@@ -3,10 +3,12 @@
 // multi-stage shared-memory ring, and the scale / bias / ReLU / SwiGLU
 // epilogues applied while draining tensor memory.
 //
-// One persistent CTA per SM, 192 threads, warp-specialised:
+// One persistent CTA per SM, 320 threads, warp-specialised:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      MMA issuer (one elected lane); owns the TMEM allocation
-//   warps 2..5  epilogue; warp w drains TMEM lanes 32*(w%4) .. +31
+//   warps 2..9  epilogue; warp w drains TMEM lanes 32*(w%4) .. +31 (the lanes the
+//               hardware lets it read) and the column half (w-2)/4 of the tile, so
+//               every scheduler has two epilogue warps to switch between
 // The accumulator is double-buffered in TMEM (2 x CTA_N columns) so the
 // epilogue of tile i overlaps the main loop of tile i+1. Tiles are visited in
 // grouped-raster order (8 M-tiles per group, column-first) so the CTAs running
@@ -40,7 +42,9 @@ namespace {
 constexpr int kCtaM = 128;
 constexpr int kCtaK = 128;  // bytes of K per stage = one swizzle span
 constexpr int kUmmaK = 32;  // K per tcgen05.mma for 8-bit operands
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kBiasBytes = kEpiWarps * 128 * 4;  // per epilogue warp: its column half's bias as f32
 constexpr int kSwizzleGroup = 8;  // M-tiles per raster group
 
 struct GemmParams {
@@ -63,7 +67,7 @@ struct GemmCfg {
     static constexpr int stage_bytes = a_bytes + b_bytes;
     static constexpr int stages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int tmem_cols = 2 * BN;  // 128, 256 or 512: powers of two >= 32
-    static constexpr int bar_bytes = (2 * stages + 4) * 8 + 16;
+    static constexpr int bar_bytes = (2 * stages + 4) * 8 + 16 + kBiasBytes;
     // +1024 so the ring can be aligned to the swizzle-atom size at run time.
     static constexpr int smem_bytes = stages * stage_bytes + bar_bytes + 1024;
 };
@@ -128,16 +132,34 @@ __device__ __forceinline__ void store_vec(void* dst, const float* v) {
     }
 }
 
-// Drains one accumulator of BN columns for this thread's row: TMEM lane -> registers
-// (32 columns at a time) -> scale (+ bias, ReLU | SwiGLU with running amax) -> global.
-// `t_addr` already carries the warp's lane quarter; `col_base` is the tile's first column.
+// One epilogue warp copies the bias of its BN / 2 columns into its own slice of shared
+// memory as f32 (zero beyond N). Only the warp itself reads the slice, so a warp-level
+// sync on either side is all the ordering it needs.
+template <int BN>
+__device__ __forceinline__ void stage_bias(const GemmParams& p, float* bias_s, int col_base, int lane) {
+    __syncwarp();  // the previous tile's reads are done
+    for (int i = lane; i < BN / 2; i += 32) {
+        const int col = col_base + i;
+        float b = 0.0f;
+        if (col < p.n)
+            b = p.bias_kind == Y_B200_F16 ? __half2float(__ldg(static_cast<const __half*>(p.bias) + col))
+                                          : __ldg(static_cast<const float*>(p.bias) + col);
+        bias_s[i] = b;
+    }
+    __syncwarp();
+}
+
+// Drains this warp's half of one accumulator (BN / 2 columns) for this thread's row:
+// TMEM lane -> registers (32 columns at a time) -> scale (+ bias, ReLU | SwiGLU with
+// running amax) -> global. `t_addr` already carries the warp's lane quarter and column
+// half; `col_base` is the first column of the half; `bias_s` holds the half's bias.
 template <int BN, int EPI, int OUT>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_addr, int row, int col_base,
                                                   float scale, bool rows_aligned, int n_out,
-                                                  uint32_t& amax_bits) {
+                                                  const float* bias_s, uint32_t& amax_bits) {
     constexpr int esize = OUT == Y_B200_F32 ? 4 : 2;
 #pragma unroll 1
-    for (int ch = 0; ch < BN / 32; ++ch) {
+    for (int ch = 0; ch < BN / 64; ++ch) {
         const int col0 = col_base + ch * 32;
         if (col0 >= p.n) break;  // uniform across the warp
         uint32_t r[32];
@@ -148,15 +170,15 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * scale;
 
         if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) {
+            const float4* b4 = reinterpret_cast<const float4*>(bias_s + ch * 32);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int col = col0 + j;
-                float b = 0.0f;
-                if (col < p.n)
-                    b = p.bias_kind == Y_B200_F16 ? __half2float(__ldg(static_cast<const __half*>(p.bias) + col))
-                                                  : __ldg(static_cast<const float*>(p.bias) + col);
-                v[j] += b;
-                if (EPI == Y_B200_EPI_BIAS_RELU) v[j] = fmaxf(v[j], 0.0f);
+            for (int j = 0; j < 8; ++j) {
+                const float4 b = b4[j];  // the same address in every lane: a broadcast
+                v[4 * j] += b.x; v[4 * j + 1] += b.y; v[4 * j + 2] += b.z; v[4 * j + 3] += b.w;
+            }
+            if (EPI == Y_B200_EPI_BIAS_RELU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
             }
         }
 
@@ -216,6 +238,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t tempty0 = tfull0 + 16;               // 2 barriers: accumulator drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::stages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* bias_all = reinterpret_cast<float*>(tmem_slot + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = p.m_tiles * p.n_tiles;
@@ -228,7 +251,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, 128);
+            mbar_init(tempty0 + 8 * a, kEpiWarps);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -308,6 +331,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int quarter = warp & 3;  // TMEM lanes this warp may touch
+        const int half = (warp - 2) >> 2;  // column half of the tile this warp drains
+        float* bias_s = bias_all + (warp - 2) * 128;
         const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
                             (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
         constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
@@ -322,6 +347,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             int tm, tn;
             tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
             const uint32_t as = it & 1, aphase = (it >> 1) & 1;
+            const int col_base = tn * BN + half * (BN / 2);
+            if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane);
             if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
                 report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
                 dead = true;
@@ -329,12 +356,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             if (dead) break;
             tc_fence_after();
             const int row = tm * kCtaM + quarter * 32 + lane;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, tn * BN, scale, rows_aligned, n_out, amax_bits);
-            // This thread's TMEM reads are complete (wait::ld above): hand the
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + half * (BN / 2);
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, amax_bits);
+            // The warp's TMEM reads are complete (wait::ld above): hand its part of the
             // accumulator buffer back to the MMA warp.
             tc_fence_before();
-            mbar_arrive(tempty0 + 8 * as);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * as);
         }
         if (EPI == Y_B200_EPI_SWIGLU && p.amax_out != nullptr) {
             // Rows beyond M and columns beyond N were zero-filled, so they add
@@ -363,7 +391,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // issues; completion is signalled to both CTAs' barriers. No load is shared between CTAs.
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kCtaM * kCtaK;  // 16 KB of A + 16 KB of B per CTA
-constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16;
+constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16 + kBiasBytes;
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairBarBytes + 1024;
 
 template <int EPI, int OUT>
@@ -382,6 +410,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const uint32_t tempty0 = tfull0 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* bias_all = reinterpret_cast<float*>(tmem_slot + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -397,7 +426,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull0 + 8 * a, 1);
-            mbar_init(tempty0 + 8 * a, 8);  // 4 epilogue warps of each CTA (used in the even CTA only)
+            mbar_init(tempty0 + 8 * a, 2 * kEpiWarps);  // the epilogue warps of both CTAs (used in the even CTA only)
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -475,6 +504,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     } else {
         // ------------------------------ epilogue (both CTAs, own 128 rows) ------------
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        float* bias_s = bias_all + (warp - 2) * 128;
         const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
                             (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
         constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
@@ -490,6 +521,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             int tm, tn;
             tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
             const uint32_t as = it & 1, aphase = (it >> 1) & 1;
+            const int col_base = tn * BN + half * (BN / 2);
+            if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane);
             if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
                 report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
                 dead = true;
@@ -497,8 +530,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             if (dead) break;
             tc_fence_after();
             const int row = tm * 256 + (int)rank * kCtaM + quarter * 32 + lane;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN;
-            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, tn * BN, scale, rows_aligned, n_out, amax_bits);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + half * (BN / 2);
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, amax_bits);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * as);

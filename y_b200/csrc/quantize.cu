@@ -133,14 +133,18 @@ __global__ void __launch_bounds__(kThreads)
 // ---- transposed quantise -----------------------------------------------------------
 // x [rows, cols] -> q [cols, rows]. One CTA moves a 128(row) x 64(col) tile
 // through shared memory so both the reads (along cols) and the writes (along
-// rows) are contiguous. Edges are handled element-wise.
+// rows) are contiguous. A thread converts 4 rows x 8 columns and stores, per
+// column, one 32-bit word holding its 4 row bytes; the word index within a
+// tile row is XORed with 4 * (column / 8), which spreads the 32 lanes of a warp
+// over the 32 banks and keeps every aligned group of 4 words together for the
+// 16-byte reads of the second phase. Edges are handled element-wise.
 constexpr int kTR = 128, kTC = 64;
 template <int KIND, bool SCALE_IS_AMAX>
 __global__ void __launch_bounds__(kThreads)
     quantize_transpose_kernel(const void* __restrict__ x, size_t rows, size_t cols,
                               const float* __restrict__ s, uint8_t* __restrict__ q,
                               float* __restrict__ scale_out) {
-    __shared__ __align__(16) uint8_t tile[kTC][kTR + 16];
+    __shared__ __align__(16) uint32_t tile[kTC][kTR / 4];
     const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
     const float inv = inv_scale(scale);
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&
@@ -148,39 +152,44 @@ __global__ void __launch_bounds__(kThreads)
         scale_out[0] = scale;
     const size_t r0 = (size_t)blockIdx.y * kTR, c0 = (size_t)blockIdx.x * kTC;
     const bool vec_in = (cols % 8 == 0);
-    // 128 rows x 8 column-vectors = 1024 vector slots, 4 per thread.
+    {
+        // 32 row quads x 8 column vectors = 256 slots, one per thread.
+        const int rq = threadIdx.x / 8, cv = threadIdx.x % 8;
+        const size_t gc = c0 + (size_t)cv * 8;
+        float f[4][8];
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-        int slot = it * kThreads + threadIdx.x;
-        int r = slot / 8, cv = slot % 8;
-        size_t gr = r0 + r, gc = c0 + (size_t)cv * 8;
-        float f[8];
-        if (gr < rows && vec_in && gc + 8 <= cols) {
-            Elem<KIND>::load8(x, gr * cols + gc, f);
-        } else {
+        for (int i = 0; i < 4; ++i) {
+            const size_t gr = r0 + (size_t)rq * 4 + i;
+            if (gr < rows && vec_in && gc + 8 <= cols) {
+                Elem<KIND>::load8(x, gr * cols + gc, f[i]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                f[j] = (gr < rows && gc + j < cols) ? Elem<KIND>::load1(x, gr * cols + gc + j) : 0.0f;
+                for (int j = 0; j < 8; ++j)
+                    f[i][j] = (gr < rows && gc + j < cols) ? Elem<KIND>::load1(x, gr * cols + gc + j) : 0.0f;
+            }
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-            tile[cv * 8 + j][r] = (uint8_t)(cvt_e4m3x2(__fmul_rn(f[j], inv), 0.0f) & 0xff);
+            tile[cv * 8 + j][rq ^ (cv * 4)] =
+                cvt_e4m3x4(__fmul_rn(f[0][j], inv), __fmul_rn(f[1][j], inv), __fmul_rn(f[2][j], inv),
+                           __fmul_rn(f[3][j], inv));
     }
     __syncthreads();
     // 64 output rows x 8 sixteen-byte vectors = 512 slots, 2 per thread.
     const bool vec_out = (rows % 16 == 0);
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
-        int slot = it * kThreads + threadIdx.x;
-        int c = slot / 8, rv = slot % 8;
-        size_t gc = c0 + c, gr = r0 + (size_t)rv * 16;
+        const int slot = it * kThreads + threadIdx.x;
+        const int c = slot / 8, rv = slot % 8;
+        const size_t gc = c0 + c, gr = r0 + (size_t)rv * 16;
         if (gc >= cols) continue;
+        const uint4 v = *reinterpret_cast<const uint4*>(&tile[c][(rv ^ (c / 8)) * 4]);
         if (vec_out && gr + 16 <= rows) {
-            *reinterpret_cast<uint4*>(q + gc * rows + gr) =
-                *reinterpret_cast<const uint4*>(&tile[c][rv * 16]);
+            *reinterpret_cast<uint4*>(q + gc * rows + gr) = v;
         } else {
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             for (int j = 0; j < 16; ++j)
-                if (gr + j < rows) q[gc * rows + gr + j] = tile[c][rv * 16 + j];
+                if (gr + j < rows) q[gc * rows + gr + j] = (uint8_t)(w[j / 4] >> (8 * (j % 4)));
         }
     }
 }
@@ -192,9 +201,10 @@ __global__ void __launch_bounds__(kThreads)
 // butterfly (xor 16, 8, 4, 2, 1); the eight warp totals are added in warp
 // order; mean = total / hidden; rstd = 1 / sqrt(mean + eps) with correctly
 // rounded division and square root. y = (x * rstd) * gamma.
+__device__ __forceinline__ float rms_rstd_from_partial(float acc, size_t hidden, float eps);
+
 __device__ __forceinline__ float rms_row_rstd(const __half* __restrict__ xr, size_t hidden,
                                               float eps) {
-    __shared__ float warp_tot[8];
     const size_t nvec = hidden / 8;
     float acc = 0.0f;
     for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
@@ -203,6 +213,12 @@ __device__ __forceinline__ float rms_row_rstd(const __half* __restrict__ xr, siz
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc = __fmaf_rn(f[j], f[j], acc);
     }
+    return rms_rstd_from_partial(acc, hidden, eps);
+}
+
+// Adds the thread's partial sums in the fixed order described above.
+__device__ __forceinline__ float rms_rstd_from_partial(float acc, size_t hidden, float eps) {
+    __shared__ float warp_tot[8];
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1)
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
@@ -215,21 +231,61 @@ __device__ __forceinline__ float rms_row_rstd(const __half* __restrict__ xr, siz
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 
+// VPT > 0: the row has at most VPT * 256 vectors and stays in registers between
+// the sum of squares and the amax, so it is read once. VPT == 0: any length,
+// second pass re-reads the row (from L1/L2).
+template <int VPT>
 __global__ void __launch_bounds__(kThreads)
     rmsnorm_stats_kernel(const __half* __restrict__ x, const __half* __restrict__ gamma,
                          size_t hidden, float eps, float* __restrict__ rstd_out,
                          unsigned int* __restrict__ amax_out) {
     const __half* xr = x + (size_t)blockIdx.x * hidden;
-    const float rstd = rms_row_rstd(xr, hidden, eps);
-    if (threadIdx.x == 0) rstd_out[blockIdx.x] = rstd;
-    float m = 0.0f;
     const size_t nvec = hidden / 8;
-    for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
-        float f[8], g[8];
-        Elem<Y_B200_F16>::load8(xr, v * 8, f);
-        Elem<Y_B200_F16>::load8(gamma, v * 8, g);
+    float m = 0.0f;
+    if constexpr (VPT > 0) {
+        uint4 raw[VPT];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(__fmul_rn(__fmul_rn(f[j], rstd), g[j])));
+        for (int i = 0; i < VPT; ++i) {
+            const size_t v = threadIdx.x + (size_t)i * kThreads;
+            raw[i] = v < nvec ? *reinterpret_cast<const uint4*>(xr + v * 8) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        float acc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {  // absent vectors are zeros: fma(0, 0, acc) = acc
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                acc = __fmaf_rn(f.x, f.x, acc);
+                acc = __fmaf_rn(f.y, f.y, acc);
+            }
+        }
+        const float rstd = rms_rstd_from_partial(acc, hidden, eps);
+        if (threadIdx.x == 0) rstd_out[blockIdx.x] = rstd;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const size_t v = threadIdx.x + (size_t)i * kThreads;
+            if (v >= nvec) continue;
+            float g[8];
+            Elem<Y_B200_F16>::load8(gamma, v * 8, g);
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[i]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                m = fmaxf(m, fabsf(__fmul_rn(__fmul_rn(f.x, rstd), g[2 * j])));
+                m = fmaxf(m, fabsf(__fmul_rn(__fmul_rn(f.y, rstd), g[2 * j + 1])));
+            }
+        }
+    } else {
+        const float rstd = rms_row_rstd(xr, hidden, eps);
+        if (threadIdx.x == 0) rstd_out[blockIdx.x] = rstd;
+        for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
+            float f[8], g[8];
+            Elem<Y_B200_F16>::load8(xr, v * 8, f);
+            Elem<Y_B200_F16>::load8(gamma, v * 8, g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(__fmul_rn(__fmul_rn(f[j], rstd), g[j])));
+        }
     }
     block_atomic_max(m, amax_out);
 }
@@ -242,9 +298,12 @@ __global__ void __launch_bounds__(kThreads)
     const float scale = scale_from_amax(amax[0]);
     const float inv = inv_scale(scale);
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out != nullptr) scale_out[0] = scale;
-    const __half* xr = x + (size_t)blockIdx.x * hidden;
-    uint8_t* qr = q + (size_t)blockIdx.x * hidden;
-    const float rstd = rstd_in[blockIdx.x];
+    // Rows are taken last to first: the statistics kernel ran first to last, so the
+    // rows it touched most recently, which L2 still holds, are read first.
+    const size_t row = gridDim.x - 1 - blockIdx.x;
+    const __half* xr = x + row * hidden;
+    uint8_t* qr = q + row * hidden;
+    const float rstd = rstd_in[row];
     const size_t nvec = hidden / 8;
     for (size_t v = threadIdx.x; v < nvec; v += kThreads) {
         float f[8], g[8];
@@ -435,9 +494,17 @@ extern "C" int y_b200_rmsnorm_quantize_fp8(const void* x_f16, const void* gamma_
     unsigned int* amax = static_cast<unsigned int*>(workspace);
     float* rstd = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
     YB_CUDA(cudaMemsetAsync(amax, 0, sizeof(unsigned int), st));
-    rmsnorm_stats_kernel<<<(unsigned)rows, kThreads, 0, st>>>(
-        static_cast<const __half*>(x_f16), static_cast<const __half*>(gamma_f16), hidden, eps, rstd,
-        amax);
+    const __half* xh = static_cast<const __half*>(x_f16);
+    const __half* gh = static_cast<const __half*>(gamma_f16);
+    const size_t nvec = hidden / 8;
+    if (nvec <= kThreads)
+        rmsnorm_stats_kernel<1><<<(unsigned)rows, kThreads, 0, st>>>(xh, gh, hidden, eps, rstd, amax);
+    else if (nvec <= 2 * kThreads)
+        rmsnorm_stats_kernel<2><<<(unsigned)rows, kThreads, 0, st>>>(xh, gh, hidden, eps, rstd, amax);
+    else if (nvec <= 4 * kThreads)
+        rmsnorm_stats_kernel<4><<<(unsigned)rows, kThreads, 0, st>>>(xh, gh, hidden, eps, rstd, amax);
+    else
+        rmsnorm_stats_kernel<0><<<(unsigned)rows, kThreads, 0, st>>>(xh, gh, hidden, eps, rstd, amax);
     YB_CUDA(cudaGetLastError());
     rmsnorm_quantize_kernel<<<(unsigned)rows, kThreads, 0, st>>>(
         static_cast<const __half*>(x_f16), static_cast<const __half*>(gamma_f16), hidden, rstd,
