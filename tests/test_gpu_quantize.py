@@ -71,7 +71,7 @@ def test_transposed_quantise_bit_exact(q, rows, cols):
     assert np.array_equal(qd.cpu().numpy(), oracle.quantize_fp8_f16_transpose(x, s))
 
 
-@pytest.mark.parametrize("rows,hidden", [(6, 512), (3, 8), (33, 2048), (64, 8192), (5, 4096 + 256)])
+@pytest.mark.parametrize("rows,hidden", [(6, 512), (3, 8), (33, 2048), (64, 8192), (5, 4096 + 256), (3, 16384 + 8), (2000, 1024)])
 def test_rmsnorm_quantise_bit_exact(q, rows, hidden):
     x = oracle.fill_normal_f16(rows * hidden, oracle.SEED_A + 7).reshape(rows, hidden)
     g = oracle.fill_uniform_f16(hidden, oracle.SEED_A + 2, 0.5, 1.5)

@@ -314,4 +314,32 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
 
 #endif  // __CUDACC__
 
+// ---- programmatic dependent launch ------------------------------------------------
+// A kernel launched with launch_pdl may start while the kernel before it in the
+// stream is still running (once every CTA of that kernel has called
+// pdl_launch_dependents or exited). It must call pdl_wait before it touches anything
+// an earlier kernel may write or still read; after pdl_wait the earlier kernel has
+// completed and its writes are visible. Both calls are no-ops in a kernel that was
+// launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                       Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace yb

@@ -266,6 +266,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this CTA's own shared and tensor memory, so it may
+    // overlap the tail of the kernel before this one in the stream; the operands, the
+    // device-side scales and the output buffer may not.
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -441,6 +446,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();  // as in gemm_fp8_kernel: only global memory has to wait for the previous kernel
+    pdl_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------ TMA producer (both CTAs) --------------------
@@ -625,8 +632,8 @@ int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::smem_bytes));
         configured[dev] = true;
     }
-    gemm_fp8_kernel<BN, EPI, OUT><<<grid, kGemmThreads, Cfg::smem_bytes, st>>>(ta, tb, p);
-    return check_cuda(cudaGetLastError(), "gemm_fp8_kernel launch");
+    return check_cuda(launch_pdl(gemm_fp8_kernel<BN, EPI, OUT>, grid, kGemmThreads, Cfg::smem_bytes, st, ta, tb, p),
+                      "gemm_fp8_kernel launch");
 }
 
 template <int BN, int EPI>
@@ -666,8 +673,8 @@ int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPara
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
         configured[dev] = true;
     }
-    gemm_fp8_pair_kernel<EPI, OUT><<<grid, kGemmThreads, kPairSmemBytes, st>>>(ta, tb, p);
-    return check_cuda(cudaGetLastError(), "gemm_fp8_pair_kernel launch");
+    return check_cuda(launch_pdl(gemm_fp8_pair_kernel<EPI, OUT>, grid, kGemmThreads, kPairSmemBytes, st, ta, tb, p),
+                      "gemm_fp8_pair_kernel launch");
 }
 
 template <int EPI>
