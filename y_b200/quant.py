@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from ._lib import (BF16, E4M3, EPI_BIAS, EPI_BIAS_RELU, EPI_NONE, EPI_SWIGLU, F16, F32,
-                   GemmFp8Args, check, lib)
+                   GemmFp8Args, LaunchInfo, check, lib)
 
 _KIND = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 _OUT_DTYPE = {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16}
@@ -121,6 +121,13 @@ def _scale_fields(args: GemmFp8Args, name: str, s) -> None:
     else:
         setattr(args, name + "_dev", None)
         setattr(args, name, float(s))
+
+
+def gemm_fp8_launch_info(m: int, n: int, k: int, cta_n: int = 0) -> LaunchInfo:
+    """Grid, block, cluster, shared memory and tile the library would use for this shape."""
+    info = LaunchInfo()
+    check(lib.y_b200_gemm_fp8_launch_info(m, n, k, cta_n, C.byref(info)))
+    return info
 
 
 def gemm_fp8_codes(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b, *, bias=None,
