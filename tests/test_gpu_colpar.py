@@ -1,0 +1,52 @@
+"""The column-parallel operator on one GPU: its device path against the oracle chain,
+and its pipelined host path (copy-in, kernels and copy-out on three streams, two
+buffer slots) against the device path over more steps than slots."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import assert_gemm_close, dev, f16_dev, host_bits, to_f64
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def layer_and_inputs(cuda):
+    from y_b200 import colpar, quant as q
+    m, k, n = 320, 512, 384
+    w = oracle.fill_normal_f16(k * n, oracle.SEED_B).reshape(k, n)
+    sb = oracle.scale_from_amax(oracle.amax_f16(w))
+    bqt_h = oracle.quantize_fp8_f16_transpose(w, sb)
+    g = oracle.fill_uniform_f16(k, oracle.SEED_A + 2, 0.5, 1.5)
+    layer = colpar.ColumnParallelFp8Linear(dev(bqt_h), sb, f16_dev(g), 1e-6, m)
+    xs = [oracle.fill_normal_f16(m * k, oracle.SEED_A + 100 + i).reshape(m, k) for i in range(5)]
+    return layer, xs, g, bqt_h, sb, q
+
+
+def test_forward_matches_the_oracle_chain(layer_and_inputs):
+    layer, xs, g, bqt_h, sb, q = layer_and_inputs
+    c = layer.forward(f16_dev(xs[0]))
+    q.device_status()
+    aq, sa = oracle.rmsnorm_quantize_fp8(xs[0], g, 1e-6)
+    ref = oracle.gemm_fp8(aq, bqt_h, sa, sb, out_kind=oracle.OUT_BF16)
+    assert_gemm_close(to_f64(host_bits(c), oracle.OUT_BF16), to_f64(ref, oracle.OUT_BF16))
+
+
+def test_host_pipeline_equals_device_path_step_by_step(layer_and_inputs):
+    layer, xs, g, bqt_h, sb, q = layer_and_inputs
+    m, k, n = layer.m, layer.k, layer.n_shard
+    want = [layer.forward(f16_dev(x)).clone() for x in xs]
+    torch.cuda.synchronize()
+    x_host = [torch.from_numpy(x.view(np.float16).copy()).pin_memory() for x in xs]
+    c_host = [torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for _ in xs]
+    for _ in range(3):  # several rounds: slots are reused while earlier steps are in flight
+        for c in c_host:
+            c.zero_()
+        for xh, ch in zip(x_host, c_host):
+            layer.submit_host(xh, ch)
+        layer.drain()
+        torch.cuda.synchronize()
+        q.device_status()
+        for ch, w in zip(c_host, want):
+            assert torch.equal(ch, w.cpu())

@@ -54,3 +54,81 @@ def assemble(gathered: torch.Tensor) -> torch.Tensor:
     """[world, M, N_s] -> row-major [M, world * N_s]."""
     world, m, n_s = gathered.shape
     return gathered.permute(1, 0, 2).reshape(m, world * n_s)
+
+
+class ColumnParallelFp8Linear:
+    """One rank's shard of `C = rmsnorm(X; gamma, eps) -> e4m3, then FP8 GEMM with the
+    pre-quantised weight shard -> bf16`, with a device path and a pipelined host path.
+
+    `forward(x)` runs the step on the current stream (x on the device). `submit_host`
+    takes pinned host buffers: the host->device copy of step i+1, the kernels of step
+    i and the device->host copy of step i-1 run on three streams at the same time, so
+    the two directions of the host link and the GPU overlap; `drain` makes the current
+    stream wait for everything submitted. Buffers are reused round-robin over `depth`
+    slots; a host output buffer may be read after `drain` (or after the event
+    `submit_host` returns has completed).
+    """
+
+    def __init__(self, bqt: torch.Tensor, scale_b, gamma: torch.Tensor, eps: float, m: int, depth: int = 2):
+        from . import quant as q
+
+        self._q = q
+        self.bqt, self.scale_b, self.gamma, self.eps = bqt, scale_b, gamma, float(eps)
+        self.n_shard, self.k = bqt.shape
+        self.m, self.depth = m, depth
+        dev = bqt.device
+        ws_bytes = int(q.lib.y_b200_rmsnorm_workspace_bytes(m))
+        self._ws = [torch.empty(ws_bytes, dtype=torch.uint8, device=dev) for _ in range(depth)]
+        self._aq = [torch.empty((m, self.k), dtype=torch.uint8, device=dev) for _ in range(depth)]
+        self._x = self._c = None  # host-path staging, allocated on first use
+        self._streams = None
+        self._count = 0
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, slot: int = 0) -> torch.Tensor:
+        q = self._q
+        aq, sa = q.rmsnorm_quantize_fp8(x, self.gamma, self.eps, workspace=self._ws[slot], out=self._aq[slot])
+        return q.gemm_fp8_codes(aq, self.bqt, sa, self.scale_b, out_dtype=torch.bfloat16, out=out)
+
+    def _host_state(self):
+        if self._streams is None:
+            dev = self.bqt.device
+            self._streams = tuple(torch.cuda.Stream(device=dev) for _ in range(3))
+            self._x = [torch.empty((self.m, self.k), dtype=torch.float16, device=dev) for _ in range(self.depth)]
+            self._c = [torch.empty((self.m, self.n_shard), dtype=torch.bfloat16, device=dev)
+                       for _ in range(self.depth)]
+            self._ev = [[torch.cuda.Event() for _ in range(self.depth)] for _ in range(3)]
+            for kind in self._ev:
+                for e in kind:
+                    e.record()
+        return self._streams
+
+    def submit_host(self, x_host: torch.Tensor, c_host: torch.Tensor) -> torch.cuda.Event:
+        s_in, s_cmp, s_out = self._host_state()
+        i = self._count % self.depth
+        self._count += 1
+        in_done, cmp_done, out_done = self._ev[0][i], self._ev[1][i], self._ev[2][i]
+        start = torch.cuda.Event()
+        start.record()  # work submitted earlier on the caller's stream (e.g. filling x_host) comes first
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(start)
+            s_in.wait_event(cmp_done)  # the kernels that last read this slot's x are done
+            self._x[i].copy_(x_host, non_blocking=True)
+            in_done.record()
+        with torch.cuda.stream(s_cmp):
+            s_cmp.wait_event(in_done)
+            s_cmp.wait_event(out_done)  # the copy that last read this slot's c is done
+            self.forward(self._x[i], out=self._c[i], slot=i)
+            cmp_done.record()
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(cmp_done)
+            c_host.copy_(self._c[i], non_blocking=True)
+            out_done.record()
+        return out_done
+
+    def drain(self) -> None:
+        if self._streams is None:
+            return
+        cur = torch.cuda.current_stream(self.bqt.device)
+        for kind in self._ev:
+            for e in kind:
+                cur.wait_event(e)

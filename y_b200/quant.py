@@ -93,16 +93,19 @@ def quantize_fp8_dynamic(x: torch.Tensor, transpose: bool = False, out: torch.Te
 
 
 def rmsnorm_quantize_fp8(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6,
-                         workspace: torch.Tensor | None = None):
+                         workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
     """y = x * rsqrt(mean(x^2) + eps) * gamma, quantised to e4m3 with a fresh
-    per-tensor scale. x [rows, hidden] f16, gamma [hidden] f16. Returns (codes, scale)."""
+    per-tensor scale. x [rows, hidden] f16, gamma [hidden] f16. Returns (codes, scale);
+    `out` (uint8 [rows, hidden]) receives the codes if given."""
     _dev(x, "x"), _dev(gamma, "gamma")
     if x.dtype != torch.float16 or gamma.dtype != torch.float16:
         raise ValueError("rmsnorm_quantize_fp8 takes f16 inputs")
     rows, hidden = x.shape
     need = lib.y_b200_rmsnorm_workspace_bytes(rows)
     ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x.device)
-    q = torch.empty((rows, hidden), dtype=torch.uint8, device=x.device)
+    q = out if out is not None else torch.empty((rows, hidden), dtype=torch.uint8, device=x.device)
+    if out is not None and (_dev(out, "out").shape != (rows, hidden) or out.dtype != torch.uint8):
+        raise ValueError("rmsnorm_quantize_fp8: out must be uint8 [rows, hidden]")
     s = torch.empty(1, dtype=torch.float32, device=x.device)
     check(lib.y_b200_rmsnorm_quantize_fp8(x.data_ptr(), gamma.data_ptr(), rows, hidden, eps,
                                           q.data_ptr(), s.data_ptr(), ws.data_ptr(), ws.numel(),
