@@ -123,8 +123,8 @@ std::vector<Candidate> generate_candidates(uint32_t m, uint32_t n, uint32_t k, P
     std::vector<Candidate> out;
     if (p == Precision::Int4) {
         const uint32_t cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32);
-        if (cta_m == 32) out.push_back({32, 16, 1024, 8, 1, 16, 8});
-        else out.push_back({cta_m, 16, 2048, 16, 1, cta_m == 8 ? 10u : 8u, 16});
+        if (cta_m == 32) out.push_back({32, 16, 1024, 8, 1, 6, 8});
+        else out.push_back({cta_m, 16, 2048, 16, 1, cta_m == 8 ? 3u : 4u, 16});
         return out;
     }
     const uint32_t cta_k = p == Precision::Fp8 ? 128u : 64u;

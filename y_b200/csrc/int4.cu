@@ -1,17 +1,19 @@
 // INT4 weight-only path: group quantise/pack, repack into the streaming layout,
 // and the small-M decode GEMM.
 //
-// The decode GEMM is HBM-bound weight streaming (K*N/2 bytes of weights read
-// exactly once), so it is built around keeping every SM's share of the stream
-// in flight from the first cycle: the streaming layout makes each CTA's share
-// one contiguous byte range, a producer warp issues it as 1-D bulk copies into
-// a shared-memory ring (up to ~165 KB outstanding per SM), and 16 consumer warps
-// (8 for 32-token launches) dequantise in registers and feed mma.sync.m16n8k16 (f16 x f16 -> f32)
-// with the weights as the 16-row operand and the M <= 32 tokens as the 8-wide
-// operand. The group scale multiplies each group's f32 partial sum, so the
-// integer weights enter the MMA exactly. K is split across the warps of a
-// CTA and reduced in shared memory in a fixed order: no atomics, results
-// overwrite the output and are run-to-run identical.
+// The decode GEMM is weight streaming (K*N/2 bytes of weights read exactly once),
+// so it is built around having every SM's share of the stream requested from its
+// first microsecond: the streaming layout makes each CTA's share one contiguous
+// byte range cut into 1056-byte blocks (one 16-column tile x one 128-row group),
+// each warp copies its own blocks into its own part of shared memory with
+// per-thread 16-byte asynchronous copies, many blocks ahead, and dequantises in
+// registers. Up to two tokens go through the FMA pipe; more go through
+// mma.sync.m16n8k16 (f16 x f16 -> f32) with the weights as the 16-row operand
+// and up to 32 tokens as 8-wide operands. The group scale multiplies each group's
+// f32 partial sum, so the integer weights enter the arithmetic exactly. K is split
+// across the warps of a CTA and reduced in shared memory in a fixed order: no
+// atomics, results overwrite the output and are run-to-run identical. Nothing in
+// the kernel waits on a barrier that another agent has to complete.
 #include "common.cuh"
 
 namespace yb {
@@ -94,22 +96,23 @@ __global__ void __launch_bounds__(256)
 
 // ---- decode GEMM ------------------------------------------------------------------
 
-
-// NT = 8-token operand tiles (M <= 8 * NT). round_tiles = 16-column weight tiles
-// whose accumulators a warp keeps in registers at once.
+// NT = 8-token operand tiles of the tensor path (M <= 8 * NT). round_tiles = 16-column
+// weight tiles whose accumulators a warp keeps in registers at once. Every warp streams
+// its own blocks: `depth` blocks (1056 bytes each) are in flight or waiting in the warp's
+// private part of shared memory.
 template <int NT>
 struct DecodeCfg {
-    // Consumer warps = K groups per ring slot (one group per warp). 32-token launches keep
-    // 4x the accumulators and activation fragments per thread, so they run 8 warps (more
+    // Warps = K groups worked on at once (one group per warp). 32-token launches keep 4x
+    // the accumulators and activation fragments per thread, so they run 8 warps (more
     // registers per thread) instead of 16.
     static constexpr int warps = NT == 4 ? 8 : 16;
-    static constexpr int threads = (warps + 1) * 32;
-    static constexpr int unit_bytes = warps * kBlkBytes;
+    static constexpr int threads = warps * 32;
     static constexpr int round_tiles = 5;
-    static constexpr int slots = NT == 1 ? 10 : (NT == 2 ? 8 : 16);
+    static constexpr int depth = NT == 1 ? 3 : (NT == 2 ? 4 : 6);
+    static constexpr int stage_bytes = warps * depth * kBlkBytes;
     static constexpr int red_floats = warps * round_tiles * NT * 128;
-    static constexpr int ring_bytes = slots * unit_bytes;
-    static constexpr int smem_bytes = ring_bytes + red_floats * 4 + 2 * slots * 8 + 16;
+    static constexpr int smem_bytes = stage_bytes + red_floats * 4;
+    static constexpr int unit_k = warps * 128;  // K covered by the warps of a CTA in one phase
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -128,90 +131,121 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 // The offsets are not subtracted per weight. They are the same for every weight
 // column, so their contribution to a group's partial sum,
 // 1032 * sum(x over the "lo" K slots) + 72 * sum(x over the "hi" K slots), is
-// computed once per (group, token) by one MMA pass with a constant operand and
-// the group's accumulator starts at its negative. All products are exact in f32.
-__device__ __forceinline__ uint32_t deq_lo(uint32_t w) { return (w & 0x000f000fu) | 0x64006400u; }
-__device__ __forceinline__ uint32_t deq_hi(uint32_t w) { return (w & 0x00f000f0u) | 0x54005400u; }
+// computed once per (group, token) and the group's accumulator starts at its
+// negative. All products are exact in f32.
+//
+// (w & mask) | exponent is one LOP3 only if at most one of the two constants is an
+// immediate. The compiler, knowing both, emitted two instructions per pair (the ncu
+// opcode counts showed 66 LOP3 per block where 32 are needed), so the constants are
+// read from constant memory into registers once per kernel and the LOP3 is written out.
+__constant__ uint32_t kDeqConst[4] = {0x000f000fu, 0x64006400u, 0x00f000f0u, 0x54005400u};
+struct DeqRegs {
+    uint32_t mask_lo, exp_lo, mask_hi, exp_hi;
+};
+__device__ __forceinline__ uint32_t and_or(uint32_t w, uint32_t mask, uint32_t orv) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(w), "r"(mask), "r"(orv));  // (w & mask) | orv
+    return d;
+}
 constexpr uint32_t kOffsetLo = 0x64086408u;  // f16 pair (1032, 1032)
 constexpr uint32_t kOffsetHi = 0x54805480u;  // f16 pair (72, 72)
 
-template <int THREADS>
-__device__ __forceinline__ void consumer_bar() {
-    asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// The blocks one warp works through, in order: rounds of up to round_tiles tiles; within a
+// round the warp's K groups (phase p -> group p * warps + warp); within a phase the tiles.
+// `src` runs along with the position so that a step is one add in the common case.
+struct BlockSeq {
+    const uint8_t* src;
+    int r0, rt, p, t;
+    __device__ __forceinline__ bool live(int t_end) const { return r0 < t_end; }
+};
+
+// Up to 8 * NT tokens per launch. A one- or two-token FMA-pipe variant (fma.rn.f32.f16 on
+// dequantised pairs, no tensor instructions) was built and measured: 240 instructions per
+// block against 130 here, 7.2 us against 7.0 us at K = 4096, N = 11008, so it was dropped.
+//
+// Weights reach shared memory by per-thread 16-byte asynchronous copies: lane l copies
+// exactly the two 16-byte units it will read back (plus, in lanes 0 and 1, the block's
+// scales), `depth` blocks ahead. A whole CTA's share of a 4096 x 11008 matrix (157 KB) is
+// requested in its first microsecond. (A single thread issuing 1-D bulk copies kept only
+// about 25 KB per SM in flight at DRAM latency, which held the kernel at 3.2 TB/s.)
+// The first copies are issued before griddepcontrol.wait: the weights do not depend on
+// the kernel before this one, the activations do.
 template <int NT>
 __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
     int4_decode_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ wstream,
-                       __half* __restrict__ out, int M, int N, int K, DeviceStatus* status) {
+                       __half* __restrict__ out, int M, int N, int K) {
     using Cfg = DecodeCfg<NT>;
-    constexpr int kRoundTiles = Cfg::round_tiles;
-    constexpr int kConsumerWarps = Cfg::warps, kUnitGroups = Cfg::warps, kUnitBytes = Cfg::unit_bytes;
+    constexpr int kRoundTiles = Cfg::round_tiles, kWarps = Cfg::warps, kDepth = Cfg::depth;
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* ring = smem;
-    float* red = reinterpret_cast<float*>(smem + Cfg::ring_bytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::ring_bytes + Cfg::red_floats * 4);
-    volatile uint32_t* abort_flag =
-        reinterpret_cast<volatile uint32_t*>(smem + Cfg::ring_bytes + Cfg::red_floats * 4 +
-                                             2 * Cfg::slots * 8);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + Cfg::slots);
-    const uint32_t ring0 = smem_u32(ring);
+    float* red = reinterpret_cast<float*>(smem + Cfg::stage_bytes);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::slots; ++s) {
-            mbar_init(full0 + 8 * s, 1);
-            mbar_init(empty0 + 8 * s, kConsumerWarps);
-        }
-        *abort_flag = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-    // Programmatic dependent launch: the next kernel in the stream may start its own
-    // prologue and weight copies while this one is still running (the weights are not
-    // written by anything in the stream), which hides the launch gap between decode
-    // GEMMs of consecutive layers. Whatever can depend on earlier kernels (the
-    // activations, the output buffer) is only touched after griddepcontrol.wait below.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const DeqRegs dq = {kDeqConst[0], kDeqConst[1], kDeqConst[2], kDeqConst[3]};
+    uint8_t* stage = smem + (size_t)warp * kDepth * kBlkBytes;
+    const uint32_t stage0 = smem_u32(stage);
+    pdl_launch_dependents();
 
     const int ngroups = K / 128;
-    const int phases = (ngroups + kUnitGroups - 1) / kUnitGroups;
+    const int my_phases = warp < ngroups ? (ngroups - warp + kWarps - 1) / kWarps : 0;
     const int T = N / 16;
     const int t_begin = (int)(((long long)blockIdx.x * T) / gridDim.x);
     const int t_end = (int)(((long long)(blockIdx.x + 1) * T) / gridDim.x);
 
-    if (warp == kConsumerWarps) {
-        // ---- producer: stream this CTA's contiguous share through the ring ----
-        if (lane == 0) {
-            uint32_t slot = 0, sphase = 0;
-            bool ok = true;
-            for (int r0 = t_begin; r0 < t_end && ok; r0 += kRoundTiles) {
-                const int rt = min(kRoundTiles, t_end - r0);
-                for (int p = 0; p < phases && ok; ++p) {
-                    const int ng = min(kUnitGroups, ngroups - p * kUnitGroups);
-                    for (int t = 0; t < rt; ++t) {
-                        if (!mbar_wait(empty0 + 8 * slot, sphase ^ 1u, abort_flag)) {
-                            report_timeout(status, abort_flag, 0x100u, (unsigned)(r0 + t));
-                            ok = false;
-                            break;
-                        }
-                        const uint32_t bytes = (uint32_t)ng * kBlkBytes;
-                        mbar_expect_tx(full0 + 8 * slot, bytes);
-                        bulk_load_1d(ring0 + slot * kUnitBytes,
-                                     wstream + ((size_t)(r0 + t) * ngroups + (size_t)p * kUnitGroups) *
-                                                   kBlkBytes,
-                                     bytes, full0 + 8 * slot);
-                        if (++slot == Cfg::slots) { slot = 0; sphase ^= 1u; }
-                    }
+    const size_t tile_stride = (size_t)ngroups * kBlkBytes;  // same group, next tile
+    const uint8_t* const wmine = wstream + (size_t)warp * kBlkBytes;  // this warp's group of phase 0, tile 0
+    BlockSeq ahead = {wmine + (size_t)t_begin * tile_stride, t_begin, min(kRoundTiles, t_end - t_begin), 0, 0};
+    const bool streaming = my_phases > 0;
+    // Requests the next block of the sequence into slot `slot` and steps the sequence. Every
+    // call commits one group, empty when the sequence has ended, so that "all but the newest
+    // kDepth - 1 groups are complete" always means "the oldest outstanding block has arrived".
+    auto request = [&](int slot) {
+        if (streaming && ahead.live(t_end)) {
+            const uint32_t dst = stage0 + slot * kBlkBytes;
+            cp_async_16(dst + lane * 16, ahead.src + lane * 16);
+            cp_async_16(dst + 512 + lane * 16, ahead.src + 512 + lane * 16);
+            if (lane < 2) cp_async_16(dst + 1024 + lane * 16, ahead.src + 1024 + lane * 16);
+            ahead.src += tile_stride;
+            if (++ahead.t == ahead.rt) {  // once per phase: recompute instead of stepping
+                ahead.t = 0;
+                if (++ahead.p == my_phases) {
+                    ahead.p = 0;
+                    ahead.r0 += kRoundTiles;
+                    ahead.rt = min(kRoundTiles, t_end - ahead.r0);
                 }
+                ahead.src = wmine + (size_t)ahead.r0 * tile_stride + (size_t)ahead.p * (kWarps * kBlkBytes);
             }
         }
-    } else {
-        // ---- consumers -------------------------------------------------------
-        asm volatile("griddepcontrol.wait;" ::: "memory");  // earlier kernels' writes to x / out are complete
-        const int gq = lane >> 2, c = lane & 3;
-        uint32_t slot = 0, sphase = 0;  // ring position of the next unit
-        bool dead = false;
+        cp_async_commit();
+    };
+#pragma unroll 1
+    for (int i = 0; i < kDepth; ++i) request(i);
+    int slot = 0;
+    // The block in `slot` has arrived and every lane of the warp can read it.
+    auto acquire = [&]() -> const uint8_t* {
+        cp_async_wait<kDepth - 1>();
+        __syncwarp();
+        return stage + slot * kBlkBytes;
+    };
+    // Every lane is done with the block in `slot`: reuse the slot for the block kDepth ahead.
+    auto release = [&]() {
+        __syncwarp();
+        request(slot);
+        if (++slot == kDepth) slot = 0;
+    };
+
+    pdl_wait();  // earlier kernels' writes to x / reads of out are complete
+    const int gq = lane >> 2, c = lane & 3;
+    {
+        // ---- weights are the 16-row MMA operand, tokens the 8-wide one.
         for (int r0 = t_begin; r0 < t_end; r0 += kRoundTiles) {
             const int rt = min(kRoundTiles, t_end - r0);
             float acc[kRoundTiles][NT][4];
@@ -222,9 +256,8 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[t][j][i] = 0.0f;
 
-            for (int p = 0; p < phases; ++p) {
-                const int g = p * kUnitGroups + warp;
-                const bool valid = g < ngroups;
+            for (int p = 0; p < my_phases; ++p) {
+                const int g = p * kWarps + warp;
                 // Activation fragments of this warp's group: token gq + 8j,
                 // k = 128g + 32pp + 8c + (0..7).
                 uint4 xf[NT][4];
@@ -234,12 +267,12 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
 #pragma unroll
                     for (int pp = 0; pp < 4; ++pp) {
                         xf[j][pp] = make_uint4(0, 0, 0, 0);
-                        if (valid && tok < M)
+                        if (tok < M)
                             xf[j][pp] = __ldg(reinterpret_cast<const uint4*>(
                                 x + (size_t)tok * K + (size_t)g * 128 + pp * 32 + c * 8));
                     }
                 }
-                // Offset contribution of this group (see deq_lo / deq_hi): identical for
+                // Offset contribution of this group (see the dequantisation note above): identical for
                 // all 16 weight columns, so one MMA pass with a constant operand.
                 float neg_off[NT][4];
 #pragma unroll
@@ -253,52 +286,49 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) neg_off[j][i] = -o[i];
                 }
+                auto tile_step = [&](const int t) {
+                        const uint8_t* blk = acquire();
+                        const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
+                        const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
+                        const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
+                        const float s_lo = __half2float(sc[gq]);
+                        const float s_hi = __half2float(sc[gq + 8]);
+                        release();
+                        const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
+                        const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
+                        float tmp[NT][4];
 #pragma unroll
-                for (int t = 0; t < kRoundTiles; ++t) {
-                    if (t < rt) {
-                        if (!dead && !mbar_wait(full0 + 8 * slot, sphase, abort_flag)) {
-                            report_timeout(status, abort_flag, 0x200u + warp, (unsigned)(r0 + t));
-                            dead = true;
-                        }
-                        if (valid && !dead) {
-                            const uint8_t* blk = ring + slot * kUnitBytes + warp * kBlkBytes;
-                            const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
-                            const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
-                            const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
-                            const float s_lo = __half2float(sc[gq]);
-                            const float s_hi = __half2float(sc[gq + 8]);
-                            const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
-                            const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
-                            float tmp[NT][4];
+                        for (int j = 0; j < NT; ++j)
 #pragma unroll
-                            for (int j = 0; j < NT; ++j)
+                            for (int i = 0; i < 4; ++i) tmp[j][i] = neg_off[j][i];
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) tmp[j][i] = neg_off[j][i];
-#pragma unroll
-                            for (int pp = 0; pp < 4; ++pp) {
-                                const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
-                                const uint32_t a0 = deq_lo(wA[pp]), a1 = deq_lo(wB[pp]);
-                                const uint32_t a2 = deq_hi(wA[pp]), a3 = deq_hi(wB[pp]);
-                                const uint32_t e0 = deq_lo(hA), e1 = deq_lo(hB);
-                                const uint32_t e2 = deq_hi(hA), e3 = deq_hi(hB);
-#pragma unroll
-                                for (int j = 0; j < NT; ++j) {
-                                    mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
-                                    mma_16816(tmp[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
-                                }
-                            }
+                        for (int pp = 0; pp < 4; ++pp) {
+                            const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
+                            const uint32_t a0 = and_or(wA[pp], dq.mask_lo, dq.exp_lo), a1 = and_or(wB[pp], dq.mask_lo, dq.exp_lo);
+                            const uint32_t a2 = and_or(wA[pp], dq.mask_hi, dq.exp_hi), a3 = and_or(wB[pp], dq.mask_hi, dq.exp_hi);
+                            const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
+                            const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
 #pragma unroll
                             for (int j = 0; j < NT; ++j) {
-                                acc[t][j][0] = fmaf(s_lo, tmp[j][0], acc[t][j][0]);
-                                acc[t][j][1] = fmaf(s_lo, tmp[j][1], acc[t][j][1]);
-                                acc[t][j][2] = fmaf(s_hi, tmp[j][2], acc[t][j][2]);
-                                acc[t][j][3] = fmaf(s_hi, tmp[j][3], acc[t][j][3]);
+                                mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
+                                mma_16816(tmp[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
                             }
                         }
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(empty0 + 8 * slot);
-                        if (++slot == Cfg::slots) { slot = 0; sphase ^= 1u; }
-                    }
+#pragma unroll
+                        for (int j = 0; j < NT; ++j) {
+                            acc[t][j][0] = fmaf(s_lo, tmp[j][0], acc[t][j][0]);
+                            acc[t][j][1] = fmaf(s_lo, tmp[j][1], acc[t][j][1]);
+                            acc[t][j][2] = fmaf(s_hi, tmp[j][2], acc[t][j][2]);
+                            acc[t][j][3] = fmaf(s_hi, tmp[j][3], acc[t][j][3]);
+                        }
+                };
+                if (rt == kRoundTiles) {
+#pragma unroll
+                    for (int t = 0; t < kRoundTiles; ++t) tile_step(t);
+                } else {
+#pragma unroll
+                    for (int t = 0; t < kRoundTiles; ++t)
+                        if (t < rt) tile_step(t);
                 }
             }
 
@@ -310,20 +340,21 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
                 for (int j = 0; j < NT; ++j)
                     *reinterpret_cast<float4*>(mine + (t * NT + j) * 128 + lane * 4) =
                         make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
-            consumer_bar<kConsumerWarps * 32>();
+            __syncthreads();
             const int nout = rt * NT * 128;
-            for (int e = threadIdx.x; e < nout; e += kConsumerWarps * 32) {
+            for (int e = threadIdx.x; e < nout; e += kWarps * 32) {
                 float v = red[e];
 #pragma unroll
-                for (int w = 1; w < kConsumerWarps; ++w) v += red[w * (kRoundTiles * NT * 128) + e];
+                for (int w = 1; w < kWarps; ++w) v += red[w * (kRoundTiles * NT * 128) + e];
                 const int t = e / (NT * 128), j = (e / 128) % NT, l = (e % 128) / 4, i = e % 4;
                 const int col = (r0 + t) * 16 + (l >> 2) + 8 * (i >> 1);
                 const int tok = 8 * j + 2 * (l & 3) + (i & 1);
                 if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
             }
-            consumer_bar<kConsumerWarps * 32>();
+            __syncthreads();
         }
     }
+    cp_async_wait<0>();  // only empty groups can be left; nothing may be pending at exit
 }
 
 template <int NT>
@@ -340,19 +371,9 @@ int launch_decode(const void* x, const void* wstream, void* out, int m, int n, i
     }
     const int tiles = n / 16;
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)Cfg::threads);
-    cfg.dynamicSmemBytes = Cfg::smem_bytes;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, int4_decode_kernel<NT>, static_cast<const __half*>(x),
-                                         static_cast<const uint8_t*>(wstream), static_cast<__half*>(out), m, n, k,
-                                         device_status_ptr()),
+    return check_cuda(launch_pdl(int4_decode_kernel<NT>, (unsigned)grid, (unsigned)Cfg::threads, Cfg::smem_bytes, st,
+                                 static_cast<const __half*>(x), static_cast<const uint8_t*>(wstream),
+                                 static_cast<__half*>(out), m, n, k),
                       "int4_decode_kernel launch");
 }
 
@@ -365,9 +386,9 @@ void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsig
                             int* unit_k) {
     const int tiles = n > 0 ? n / 16 : 0;
     *grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-    if (m <= 8) { *block = DecodeCfg<1>::threads; *smem = DecodeCfg<1>::smem_bytes; *slots = DecodeCfg<1>::slots; *unit_k = DecodeCfg<1>::warps * 128; }
-    else if (m <= 16) { *block = DecodeCfg<2>::threads; *smem = DecodeCfg<2>::smem_bytes; *slots = DecodeCfg<2>::slots; *unit_k = DecodeCfg<2>::warps * 128; }
-    else { *block = DecodeCfg<4>::threads; *smem = DecodeCfg<4>::smem_bytes; *slots = DecodeCfg<4>::slots; *unit_k = DecodeCfg<4>::warps * 128; }
+    if (m <= 8) { *block = DecodeCfg<1>::threads; *smem = DecodeCfg<1>::smem_bytes; *slots = DecodeCfg<1>::depth; *unit_k = DecodeCfg<1>::unit_k; }
+    else if (m <= 16) { *block = DecodeCfg<2>::threads; *smem = DecodeCfg<2>::smem_bytes; *slots = DecodeCfg<2>::depth; *unit_k = DecodeCfg<2>::unit_k; }
+    else { *block = DecodeCfg<4>::threads; *smem = DecodeCfg<4>::smem_bytes; *slots = DecodeCfg<4>::depth; *unit_k = DecodeCfg<4>::unit_k; }
 }
 
 }  // namespace yb
