@@ -367,7 +367,9 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "api": "y_b200.colpar.ColumnParallelFp8Linear.submit_host (3-stream pipeline, depth 2)",
-                    "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N_SHARD * 2},
+                    "h2d_bytes_per_step": layer.host_bytes_per_step()[0], "d2h_bytes_per_step": layer.host_bytes_per_step()[1],
+                    "bytes_are": "per rank; with N > 1 each rank copies 1/N of X from the host and the ranks "
+                                 "all-gather it over NVLink"},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "tensor", "kernel": gemm_kernel, "achieved": gemm_tflops,
                          "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,

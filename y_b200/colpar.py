@@ -64,13 +64,21 @@ class ColumnParallelFp8Linear:
     takes pinned host buffers: the host->device copy of step i+1, the kernels of step
     i and the device->host copy of step i-1 run on three streams at the same time, so
     the two directions of the host link and the GPU overlap; `drain` makes the current
-    stream wait for everything submitted. Buffers are reused round-robin over `depth`
+    stream wait for everything submitted. With more than one rank the activations are
+    the same on every rank, so each rank copies only its 1/world of the rows from the
+    host and the ranks all-gather the rest over NVLink (every rank must call
+    `submit_host` the same number of times). Buffers are reused round-robin over `depth`
     slots; a host output buffer may be read after `drain` (or after the event
     `submit_host` returns has completed).
     """
 
-    def __init__(self, bqt: torch.Tensor, scale_b, gamma: torch.Tensor, eps: float, m: int, depth: int = 2):
+    def __init__(self, bqt: torch.Tensor, scale_b, gamma: torch.Tensor, eps: float, m: int, depth: int = 2,
+                 group=None):
         from . import quant as q
+
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
 
         self._q = q
         self.bqt, self.scale_b, self.gamma, self.eps = bqt, scale_b, gamma, float(eps)
@@ -112,11 +120,19 @@ class ColumnParallelFp8Linear:
         with torch.cuda.stream(s_in):
             s_in.wait_event(start)
             s_in.wait_event(cmp_done)  # the kernels that last read this slot's x are done
-            self._x[i].copy_(x_host, non_blocking=True)
+            if self.world > 1 and self.m % self.world == 0:
+                rows = self.m // self.world
+                mine = slice(self.rank * rows, (self.rank + 1) * rows)
+                self._x[i][mine].copy_(x_host[mine], non_blocking=True)
+            else:
+                mine = None
+                self._x[i].copy_(x_host, non_blocking=True)
             in_done.record()
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(in_done)
             s_cmp.wait_event(out_done)  # the copy that last read this slot's c is done
+            if mine is not None:  # in place: this rank's rows are already where the gather puts them
+                dist.all_gather_into_tensor(self._x[i], self._x[i][mine], group=self.group)
             self.forward(self._x[i], out=self._c[i], slot=i)
             cmp_done.record()
         with torch.cuda.stream(s_out):
@@ -124,6 +140,11 @@ class ColumnParallelFp8Linear:
             c_host.copy_(self._c[i], non_blocking=True)
             out_done.record()
         return out_done
+
+    def host_bytes_per_step(self) -> tuple[int, int]:
+        """(host->device, device->host) bytes this rank moves per `submit_host`."""
+        share = self.world if self.world > 1 and self.m % self.world == 0 else 1
+        return self.m * self.k * 2 // share, self.m * self.n_shard * 2
 
     def drain(self) -> None:
         if self._streams is None:
