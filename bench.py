@@ -185,6 +185,74 @@ def run_reference(args):
     }))
 
 
+def other_config_metrics(peaks):
+    """The remaining single-GPU configurations of the path, each timed with CUDA events over
+    back-to-back launches after warm-up (operands larger than L2 or rotated, as noted)."""
+    import torch
+
+    from y_b200 import quant as q
+
+    def timeit(fn, iters=20, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    out = {}
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    # fused bias + ReLU epilogue, 4096^3, bf16 out; three operand sets rotate (3 x 67 MB > L2)
+    m = n = k = 4096
+    sets = []
+    for i in range(3):
+        a = torch.randn(m, k, device="cuda", dtype=torch.float16)
+        b = torch.randn(k, n, device="cuda", dtype=torch.float16)
+        aq, sa = q.quantize_fp8_dynamic(a)
+        bqt, sb = q.quantize_fp8_dynamic(b, transpose=True)
+        sets.append((aq, bqt, sa, sb, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")))
+        del a, b
+    bias = (torch.randn(n, device="cuda") * 0.1).to(torch.float16)
+    it = [0]
+
+    def bias_relu():
+        aq, bqt, sa, sb, c = sets[it[0] % 3]
+        it[0] += 1
+        q.gemm_fp8_codes(aq, bqt, sa, sb, bias=bias, epilogue=q.EPI_BIAS_RELU, out_dtype=torch.bfloat16, out=c)
+
+    us = timeit(bias_relu, iters=30)
+    tf = 2.0 * m * n * k / us / 1e6
+    out["fp8_gemm_4096_bias_relu_bf16"] = {"us": round(us, 2), "tflops": round(tf, 1), "frac_of_2x_bf16_peak": round(tf / fp8_peak, 4)}
+    del sets
+    # SwiGLU GEMM + re-quantisation, M = K = 4096, N = 2 x 11008 (gate|up interleaved)
+    m, k, n = 4096, 4096, 22016
+    a = torch.randn(m, k, device="cuda", dtype=torch.float16)
+    aq, sa = q.quantize_fp8_dynamic(a)
+    w = torch.randn(k, n, device="cuda", dtype=torch.float16)
+    bqt, sb = q.quantize_fp8_dynamic(w, transpose=True)
+    del a, w
+    ws = torch.empty(int(q.lib.y_b200_swiglu_workspace_bytes(m, n)), dtype=torch.uint8, device="cuda")
+    us = timeit(lambda: q.gemm_fp8_swiglu_requant(aq, bqt, sa, sb, workspace=ws), iters=20)
+    tf = 2.0 * m * n * k / us / 1e6
+    out["fp8_swiglu_requant_4096x22016x4096"] = {"us": round(us, 2), "tflops": round(tf, 1),
+                                                 "frac_of_2x_bf16_peak": round(tf / fp8_peak, 4),
+                                                 "includes": "GEMM with SwiGLU epilogue and amax, then the e4m3 re-quantise kernel"}
+    del aq, bqt, ws
+    # dynamic per-tensor quantisation of 8192 x 8192 f16 (amax + quantise: 5 bytes per element)
+    x = torch.randn(8192, 8192, device="cuda", dtype=torch.float16)
+    for name, tr in (("quantize_fp8_dynamic_8192x8192", False), ("quantize_fp8_dynamic_transposed_8192x8192", True)):
+        us = timeit(lambda: q.quantize_fp8_dynamic(x, transpose=tr), iters=20)
+        gbs = 5.0 * x.numel() / us / 1e3
+        out[name] = {"us": round(us, 2), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                     "bytes": "5 per element: read twice (amax, quantise), write once"}
+    q.device_status()
+    return out
+
+
 def decode_metrics(peaks, iters=200):
     """INT4 decode GEMM, K=4096, N=11008, M in {1,4,8,32}: HBM-bound weight streaming.
     Launches are issued by the library's own timing loop (the mirror of the reference's
@@ -386,6 +454,7 @@ def run_ours(args):
     if rank == 0 and world == 1:
         if not args.no_decode:
             line["decode"] = decode_metrics(peaks)
+            line["other_configs"] = other_config_metrics(peaks)
         if not args.no_cpu:
             rows = args.cpu_rows
             stepfn, cores = cpu_step_sample(rows)

@@ -113,6 +113,15 @@ def test_full_size_properties(q):
     assert torch.equal(ct, codes.t().contiguous())
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_transposed_quantise_strips_at_bench_size(q, dtype):
+    # 8192 x 8192 is large enough for the strip kernel to give each CTA several row tiles
+    x = torch.randn(8192, 8192, device="cuda", dtype=dtype)
+    codes, s = q.quantize_fp8_dynamic(x)
+    ct, st = q.quantize_fp8_dynamic(x, transpose=True)
+    assert torch.equal(s, st) and torch.equal(ct, codes.t().contiguous())
+
+
 def test_bad_arguments_are_reported_not_launched(q):
     from y_b200._lib import YB200Error, ERR_ALIGN, ERR_SHAPE
     x = torch.zeros(64, dtype=torch.float16, device="cuda")

@@ -57,6 +57,23 @@ struct Elem<Y_B200_F32> {
     }
 };
 
+// Eight 16-bit elements held in a uint4 -> f32 (KIND is F16 or BF16).
+template <int KIND>
+__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (KIND == Y_B200_F16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+        } else {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    }
+}
+
 __device__ __forceinline__ void block_atomic_max(float local, unsigned int* out) {
     __shared__ unsigned int warp_max[kThreads / 32];
     unsigned int bits = __float_as_uint(local);  // local >= 0
@@ -76,6 +93,7 @@ __device__ __forceinline__ void block_atomic_max(float local, unsigned int* out)
 template <int KIND>
 __global__ void __launch_bounds__(kThreads) amax_kernel(const void* __restrict__ x, size_t n,
                                                         unsigned int* __restrict__ out) {
+    pdl_wait();
     const size_t n8 = n / 8;
     float m = 0.0f;
     for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n8;
@@ -89,10 +107,12 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const void* __restrict__
         size_t i = n8 * 8 + threadIdx.x;
         if (i < n) m = fmaxf(m, fabsf(Elem<KIND>::load1(x, i)));
     }
+    pdl_launch_dependents();
     block_atomic_max(m, out);
 }
 
 __global__ void scale_from_amax_kernel(const float* amax, float* scale) {
+    pdl_wait();
     scale[0] = scale_from_amax(amax[0]);
 }
 
@@ -103,6 +123,8 @@ template <int KIND, bool SCALE_IS_AMAX>
 __global__ void __launch_bounds__(kThreads)
     quantize_kernel(const void* __restrict__ x, size_t n, const float* __restrict__ s,
                     uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+    pdl_wait();
+    pdl_launch_dependents();
     const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
     const float inv = inv_scale(scale);
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
@@ -145,6 +167,8 @@ __global__ void __launch_bounds__(kThreads)
                               const float* __restrict__ s, uint8_t* __restrict__ q,
                               float* __restrict__ scale_out) {
     __shared__ __align__(16) uint32_t tile[kTC][kTR / 4];
+    pdl_wait();
+    pdl_launch_dependents();
     const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
     const float inv = inv_scale(scale);
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&
@@ -191,6 +215,60 @@ __global__ void __launch_bounds__(kThreads)
             for (int j = 0; j < 16; ++j)
                 if (gr + j < rows) q[gc * rows + gr + j] = (uint8_t)(w[j / 4] >> (8 * (j % 4)));
         }
+    }
+}
+
+// Full-tile, 16-bit-input variant: a CTA walks a strip of row tiles of one 64-column
+// band. The next tile's loads are issued before the current tile is converted, and the
+// shared-memory tile is double-buffered, so a CTA always has 16 KB of loads in flight and
+// synchronises once per tile. Same tile layout and swizzle as above.
+template <int KIND, bool SCALE_IS_AMAX>
+__global__ void __launch_bounds__(kThreads)
+    quantize_transpose_strip_kernel(const uint16_t* __restrict__ x, size_t rows, size_t cols,
+                                    const float* __restrict__ s, uint8_t* __restrict__ q,
+                                    float* __restrict__ scale_out, int tiles_per_cta) {
+    __shared__ __align__(16) uint32_t tile[2][kTC][kTR / 4];
+    pdl_wait();
+    pdl_launch_dependents();
+    const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
+    const float inv = inv_scale(scale);
+    if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&
+        threadIdx.x == 0)
+        scale_out[0] = scale;
+    const size_t c0 = (size_t)blockIdx.x * kTC;
+    const int row_tiles = (int)(rows / kTR);
+    const int rt0 = blockIdx.y * tiles_per_cta, rt1 = min(rt0 + tiles_per_cta, row_tiles);
+    const int rq = threadIdx.x / 8, cv = threadIdx.x % 8;
+    const uint16_t* xin = x + c0 + (size_t)cv * 8 + (size_t)rq * 4 * cols;  // row rq*4 of tile 0
+    const int oc0 = threadIdx.x / 8, orv = threadIdx.x % 8;                // write-out slots
+    uint4 cur[4], nxt[4];
+    auto load_tile = [&](int rt, uint4 (&dst)[4]) {
+        const uint16_t* p = xin + (size_t)rt * kTR * cols;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = *reinterpret_cast<const uint4*>(p + (size_t)i * cols);
+    };
+    if (rt0 < rt1) load_tile(rt0, cur);
+    int b = 0;
+    for (int rt = rt0; rt < rt1; ++rt, b ^= 1) {
+        if (rt + 1 < rt1) load_tile(rt + 1, nxt);
+        float f[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) unpack8<KIND>(cur[i], f[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            tile[b][cv * 8 + j][rq ^ (cv * 4)] =
+                cvt_e4m3x4(__fmul_rn(f[0][j], inv), __fmul_rn(f[1][j], inv), __fmul_rn(f[2][j], inv),
+                           __fmul_rn(f[3][j], inv));
+        __syncthreads();
+        const size_t r0 = (size_t)rt * kTR;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int c = oc0 + it * 32;
+            *reinterpret_cast<uint4*>(q + (c0 + c) * rows + r0 + (size_t)orv * 16) =
+                *reinterpret_cast<const uint4*>(&tile[b][c][(orv ^ (c / 8)) * 4]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
     }
 }
 
@@ -414,13 +492,13 @@ int launch_quantize(const void* x, int kind, size_t n, const float* s, void* q, 
     uint8_t* qq = static_cast<uint8_t*>(q);
     switch (kind) {
         case Y_B200_F16:
-            quantize_kernel<Y_B200_F16, IS_AMAX><<<grid, kThreads, 0, st>>>(x, n, s, qq, scale_out);
+            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_F16, IS_AMAX>, grid, kThreads, 0, st, x, n, s, qq, scale_out));
             break;
         case Y_B200_BF16:
-            quantize_kernel<Y_B200_BF16, IS_AMAX><<<grid, kThreads, 0, st>>>(x, n, s, qq, scale_out);
+            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_BF16, IS_AMAX>, grid, kThreads, 0, st, x, n, s, qq, scale_out));
             break;
         default:
-            quantize_kernel<Y_B200_F32, IS_AMAX><<<grid, kThreads, 0, st>>>(x, n, s, qq, scale_out);
+            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_F32, IS_AMAX>, grid, kThreads, 0, st, x, n, s, qq, scale_out));
             break;
     }
     return check_cuda(cudaGetLastError(), "quantize_kernel launch");
@@ -431,18 +509,29 @@ int launch_quantize_t(const void* x, int kind, size_t rows, size_t cols, const f
                       float* scale_out, cudaStream_t st) {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
     uint8_t* qq = static_cast<uint8_t*>(q);
+    if ((kind == Y_B200_F16 || kind == Y_B200_BF16) && rows % kTR == 0 && cols % kTC == 0 &&
+        (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(q) & 15u) == 0) {
+        // Strips of up to 8 row tiles; enough CTAs to fill the GPU several times over.
+        const int row_tiles = (int)(rows / kTR);
+        int tpc = 8;
+        while (tpc > 1 && (cols / kTC) * (size_t)((row_tiles + tpc - 1) / tpc) < (size_t)sm_count() * 8) tpc /= 2;
+        dim3 sgrid((unsigned)(cols / kTC), (unsigned)((row_tiles + tpc - 1) / tpc));
+        const uint16_t* xs = static_cast<const uint16_t*>(x);
+        if (kind == Y_B200_F16)
+            YB_CUDA(launch_pdl(quantize_transpose_strip_kernel<Y_B200_F16, IS_AMAX>, sgrid, kThreads, 0, st, xs, rows, cols, s, qq, scale_out, tpc));
+        else
+            YB_CUDA(launch_pdl(quantize_transpose_strip_kernel<Y_B200_BF16, IS_AMAX>, sgrid, kThreads, 0, st, xs, rows, cols, s, qq, scale_out, tpc));
+        return check_cuda(cudaGetLastError(), "quantize_transpose_strip_kernel launch");
+    }
     switch (kind) {
         case Y_B200_F16:
-            quantize_transpose_kernel<Y_B200_F16, IS_AMAX>
-                <<<grid, kThreads, 0, st>>>(x, rows, cols, s, qq, scale_out);
+            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_F16, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, qq, scale_out));
             break;
         case Y_B200_BF16:
-            quantize_transpose_kernel<Y_B200_BF16, IS_AMAX>
-                <<<grid, kThreads, 0, st>>>(x, rows, cols, s, qq, scale_out);
+            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_BF16, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, qq, scale_out));
             break;
         default:
-            quantize_transpose_kernel<Y_B200_F32, IS_AMAX>
-                <<<grid, kThreads, 0, st>>>(x, rows, cols, s, qq, scale_out);
+            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_F32, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, qq, scale_out));
             break;
     }
     return check_cuda(cudaGetLastError(), "quantize_transpose_kernel launch");
@@ -453,9 +542,9 @@ int launch_amax(const void* x, int kind, size_t n, float* amax_out, cudaStream_t
     int grid = grid_for(n / 8 + 1);
     unsigned int* out = reinterpret_cast<unsigned int*>(amax_out);
     switch (kind) {
-        case Y_B200_F16: amax_kernel<Y_B200_F16><<<grid, kThreads, 0, st>>>(x, n, out); break;
-        case Y_B200_BF16: amax_kernel<Y_B200_BF16><<<grid, kThreads, 0, st>>>(x, n, out); break;
-        default: amax_kernel<Y_B200_F32><<<grid, kThreads, 0, st>>>(x, n, out); break;
+        case Y_B200_F16: YB_CUDA(launch_pdl(amax_kernel<Y_B200_F16>, grid, kThreads, 0, st, x, n, out)); break;
+        case Y_B200_BF16: YB_CUDA(launch_pdl(amax_kernel<Y_B200_BF16>, grid, kThreads, 0, st, x, n, out)); break;
+        default: YB_CUDA(launch_pdl(amax_kernel<Y_B200_F32>, grid, kThreads, 0, st, x, n, out)); break;
     }
     return check_cuda(cudaGetLastError(), "amax_kernel launch");
 }
@@ -489,7 +578,7 @@ extern "C" int y_b200_amax(const void* x, int x_kind, size_t n, float* amax_out,
 
 extern "C" int y_b200_scale_from_amax(const float* amax, float* scale_out, void* stream) {
     if (!amax || !scale_out) return fail(Y_B200_ERR_INVALID, "y_b200_scale_from_amax: null pointer");
-    scale_from_amax_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(amax, scale_out);
+    YB_CUDA(launch_pdl(scale_from_amax_kernel, 1, 1, 0, static_cast<cudaStream_t>(stream), static_cast<const float*>(amax), scale_out));
     return check_cuda(cudaGetLastError(), "scale_from_amax_kernel launch");
 }
 
@@ -529,7 +618,7 @@ extern "C" int y_b200_quantize_fp8_dynamic(const void* x, int x_kind, size_t row
     else
         rc = launch_quantize<true>(x, x_kind, rows * cols, scale_out, q, nullptr, st);
     if (rc) return rc;
-    scale_from_amax_kernel<<<1, 1, 0, st>>>(scale_out, scale_out);
+    YB_CUDA(launch_pdl(scale_from_amax_kernel, 1, 1, 0, st, static_cast<const float*>(scale_out), scale_out));
     return check_cuda(cudaGetLastError(), "scale_from_amax_kernel launch");
 }
 
