@@ -241,7 +241,18 @@ def other_config_metrics(peaks):
     out["fp8_swiglu_requant_4096x22016x4096"] = {"us": round(us, 2), "tflops": round(tf, 1),
                                                  "frac_of_2x_bf16_peak": round(tf / fp8_peak, 4),
                                                  "includes": "GEMM with SwiGLU epilogue and amax, then the e4m3 re-quantise kernel"}
-    del aq, bqt, ws
+    # the whole gated MLP: SwiGLU GEMM + re-quantise + down projection 11008 -> 4096
+    wd = torch.randn(n // 2, k, device="cuda", dtype=torch.float16)
+    wd_t, sd = q.quantize_fp8_dynamic(wd, transpose=True)
+    del wd
+    mws = torch.empty(int(q.lib.y_b200_mlp_workspace_bytes(m, n // 2)), dtype=torch.uint8, device="cuda")
+    o = torch.empty(m, k, dtype=torch.bfloat16, device="cuda")
+    us = timeit(lambda: q.mlp_swiglu_fp8(aq, sa, bqt, sb.item(), wd_t, sd.item(), out=o, workspace=mws), iters=20)
+    fl = 2.0 * m * n * k + 2.0 * m * (n // 2) * k
+    out["fp8_gated_mlp_4096_h4096_i11008"] = {"us": round(us, 2), "tflops": round(fl / us / 1e6, 1),
+                                              "frac_of_2x_bf16_peak": round(fl / us / 1e6 / fp8_peak, 4),
+                                              "includes": "SwiGLU GEMM, e4m3 re-quantise, down projection; 3 kernels + memset"}
+    del aq, bqt, ws, wd_t, mws, o
     # dynamic per-tensor quantisation of 8192 x 8192 f16 (amax + quantise: 5 bytes per element)
     x = torch.randn(8192, 8192, device="cuda", dtype=torch.float16)
     for name, tr in (("quantize_fp8_dynamic_8192x8192", False), ("quantize_fp8_dynamic_transposed_8192x8192", True)):

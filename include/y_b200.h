@@ -169,6 +169,23 @@ Y_B200_API size_t y_b200_swiglu_workspace_bytes(int m, int n);
 Y_B200_API int y_b200_gemm_fp8_swiglu_requant(const y_b200_gemm_fp8_args* args, void* q, float* scale_out,
                                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Gated MLP on FP8 operands: out = (silu(A Wg) * (A Wu)) Wdown, the chain the
+ * reference's SwiGLU benchmark stops short of ("down projection not included",
+ * benchmark_y_swiglu_gemm_results.md:29). Three launches on one stream, no host
+ * synchronisation between them:
+ *   1. y_b200_gemm_fp8 with the SwiGLU epilogue: h = bf16(silu(g) * u), running amax;
+ *   2. h -> e4m3 with the fresh per-tensor scale (kept on the device);
+ *   3. y_b200_gemm_fp8: out = (scale_h * scale_down) * (hq @ Wdown_q), bf16 / f16 / f32.
+ * a [M, K] e4m3; w_gate_up_t [2*I, K] e4m3 (rows 2j gate, 2j+1 up); w_down_t
+ * [N_out, I] e4m3; out [M, N_out] of out_kind. scale_a_dev may be NULL (then
+ * scale_a is used). I % 16 == 0 and K % 16 == 0.
+ * workspace: y_b200_mlp_workspace_bytes(m, inter) bytes, 256-byte aligned. */
+Y_B200_API size_t y_b200_mlp_workspace_bytes(int m, int inter);
+Y_B200_API int y_b200_mlp_swiglu_fp8(const void* a, float scale_a, const float* scale_a_dev,
+                                     const void* w_gate_up_t, float scale_gate_up, const void* w_down_t,
+                                     float scale_down, void* out, int out_kind, int m, int k, int inter,
+                                     int n_out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- INT4 weight-only decode GEMM -------------------------------------------
  * The reference has no INT4 kernel (src/ptx_emitter.rs:7321-7330 is a dead
  * stub); its decode entries gemm_f16_decode_m<M> (tests/gemm_f16_decode_m1.ptx:6-9)

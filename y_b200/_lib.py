@@ -78,6 +78,9 @@ SIGNATURES = {
     "y_b200_gemm_fp8_f32_static": (_i, [_vp, _vp, _f, _f, _vp, _i, _i, _i, _vp]),
     "y_b200_swiglu_workspace_bytes": (_sz, [_i, _i]),
     "y_b200_gemm_fp8_swiglu_requant": (_i, [C.POINTER(GemmFp8Args), _vp, _vp, _vp, _sz, _vp]),
+    "y_b200_mlp_workspace_bytes": (_sz, [_i, _i]),
+    "y_b200_mlp_swiglu_fp8": (_i, [_vp, C.c_float, _vp, _vp, C.c_float, _vp, C.c_float, _vp, _i, _i, _i, _i, _i,
+                               _vp, _sz, _vp]),
     "y_b200_int4_quantize": (_i, [_vp, _sz, _sz, _vp, _vp, _vp]),
     "y_b200_int4_stream_bytes": (_sz, [_sz, _sz]),
     "y_b200_int4_repack": (_i, [_vp, _vp, _sz, _sz, _vp, _vp]),

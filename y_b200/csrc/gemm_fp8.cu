@@ -879,6 +879,47 @@ extern "C" int y_b200_gemm_fp8_swiglu_requant(const y_b200_gemm_fp8_args* args, 
                               scale_out, st);
 }
 
+extern "C" size_t y_b200_mlp_workspace_bytes(int m, int inter) {
+    if (m < 1 || inter < 1) return 0;
+    // SwiGLU workspace (amax word + bf16 h), then the e4m3 h codes, then the scale slot.
+    const size_t swiglu = (y_b200_swiglu_workspace_bytes(m, 2 * inter) + 255) & ~(size_t)255;
+    const size_t codes = ((size_t)m * (size_t)inter + 255) & ~(size_t)255;
+    return swiglu + codes + 256;
+}
+
+extern "C" int y_b200_mlp_swiglu_fp8(const void* a, float scale_a, const float* scale_a_dev,
+                                     const void* w_gate_up_t, float scale_gate_up, const void* w_down_t,
+                                     float scale_down, void* out, int out_kind, int m, int k, int inter,
+                                     int n_out, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!a || !w_gate_up_t || !w_down_t || !out) return fail(Y_B200_ERR_INVALID, "y_b200_mlp_swiglu_fp8: null pointer");
+    if (m < 1 || k < 1 || inter < 1 || n_out < 1 || k % 16 != 0 || inter % 16 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_mlp_swiglu_fp8: need M, N_out >= 1, K %% 16 == 0, I %% 16 == 0 (M=%d K=%d I=%d N_out=%d)",
+                    m, k, inter, n_out);
+    const size_t need = y_b200_mlp_workspace_bytes(m, inter);
+    if (!workspace || workspace_bytes < need)
+        return fail(Y_B200_ERR_WORKSPACE, "y_b200_mlp_swiglu_fp8: workspace needs %zu bytes", need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u)
+        return fail(Y_B200_ERR_ALIGN, "y_b200_mlp_swiglu_fp8: workspace needs 256-byte alignment");
+    const size_t swiglu_bytes = (y_b200_swiglu_workspace_bytes(m, 2 * inter) + 255) & ~(size_t)255;
+    const size_t code_bytes = ((size_t)m * (size_t)inter + 255) & ~(size_t)255;
+    char* ws = static_cast<char*>(workspace);
+    void* hq = ws + swiglu_bytes;
+    float* scale_h = reinterpret_cast<float*>(ws + swiglu_bytes + code_bytes);
+    y_b200_gemm_fp8_args up = {};
+    up.a = a; up.bt = w_gate_up_t; up.c = ws;  // c is replaced by the SwiGLU entry
+    up.m = m; up.n = 2 * inter; up.k = k;
+    up.scale_a = scale_a; up.scale_a_dev = scale_a_dev; up.scale_b = scale_gate_up;
+    int rc = y_b200_gemm_fp8_swiglu_requant(&up, hq, scale_h, ws, swiglu_bytes, stream);
+    if (rc) return rc;
+    y_b200_gemm_fp8_args down = {};
+    down.a = hq; down.bt = w_down_t; down.c = out;
+    down.m = m; down.n = n_out; down.k = inter;
+    down.scale_a = 1.0f; down.scale_a_dev = scale_h; down.scale_b = scale_down;
+    down.epilogue = Y_B200_EPI_NONE;
+    down.out_kind = out_kind;
+    return y_b200_gemm_fp8(&down, stream);
+}
+
 // ---- allocation-free variant of the f32 drop-in GEMM -----------------------------
 // Some callers must not allocate device memory at call time: a serving loop that
 // has handed all of HBM to its own pool, a latency-critical path where cudaMalloc

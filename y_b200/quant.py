@@ -218,6 +218,31 @@ def gemm_fp8_swiglu_requant(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_
     return q, s, h
 
 
+def mlp_swiglu_fp8(aq: torch.Tensor, scale_a, w_gate_up_t: torch.Tensor, scale_gate_up: float,
+                   w_down_t: torch.Tensor, scale_down: float, out_dtype=torch.bfloat16,
+                   out: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+    """out = (silu(A Wg) * (A Wu)) Wdown on e4m3 operands: SwiGLU GEMM, re-quantisation of
+    the hidden tensor with a fresh per-tensor scale, down projection; no host sync inside.
+    aq [M, K]; w_gate_up_t [2I, K] (gate|up rows interleaved); w_down_t [N_out, I]."""
+    _dev(aq, "aq"), _dev(w_gate_up_t, "w_gate_up_t"), _dev(w_down_t, "w_down_t")
+    (m, k), (n2, k2), (n_out, inter) = aq.shape, w_gate_up_t.shape, w_down_t.shape
+    if k != k2 or n2 != 2 * inter:
+        raise ValueError(f"shape mismatch: A {tuple(aq.shape)}, gate|up {tuple(w_gate_up_t.shape)}, "
+                         f"down {tuple(w_down_t.shape)}")
+    need = lib.y_b200_mlp_workspace_bytes(m, inter)
+    ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=aq.device)
+    o = out if out is not None else torch.empty((m, n_out), dtype=out_dtype, device=aq.device)
+    out_kind = {v: kk for kk, v in _OUT_DTYPE.items()}[o.dtype]
+    if isinstance(scale_a, torch.Tensor):
+        sa, sa_dev = 1.0, _dev(scale_a, "scale_a").data_ptr()
+    else:
+        sa, sa_dev = float(scale_a), None
+    check(lib.y_b200_mlp_swiglu_fp8(aq.data_ptr(), sa, sa_dev, w_gate_up_t.data_ptr(), float(scale_gate_up),
+                                    w_down_t.data_ptr(), float(scale_down), o.data_ptr(), out_kind, m, k, inter,
+                                    n_out, ws.data_ptr(), ws.numel(), _stream()))
+    return o
+
+
 # ---- INT4 weight-only ------------------------------------------------------------
 def int4_quantize(w: torch.Tensor):
     """w [K, N] f16 -> (qweight int32 [K/8, N], scales f16 [K/128, N])."""
