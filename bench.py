@@ -260,6 +260,14 @@ def other_config_metrics(peaks):
         gbs = 5.0 * x.numel() / us / 1e3
         out[name] = {"us": round(us, 2), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
                      "bytes": "5 per element: read twice (amax, quantise), write once"}
+    # fused add + RMSNorm with the residual stream, f16 in and out: 8 bytes per element
+    r = torch.randn(8192, 8192, device="cuda", dtype=torch.float16)
+    g = (torch.rand(8192, device="cuda") + 0.5).to(torch.float16)
+    o, nr = torch.empty_like(x), torch.empty_like(x)
+    us = timeit(lambda: q.fused_add_rmsnorm(x, r, g, 1e-5, out=o, new_residual=nr), iters=20)
+    gbs = 8.0 * x.numel() / us / 1e3
+    out["fused_add_rmsnorm_f16_8192x8192"] = {"us": round(us, 2), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                                              "bytes": "8 per element: read x and residual, write out and new residual"}
     q.device_status()
     return out
 

@@ -204,6 +204,17 @@ Y_B200_API int y_b200_int4_repack(const uint32_t* qweight, const void* scales_f1
 Y_B200_API int y_b200_gemm_int4_decode(const void* x_f16, const void* wstream, void* out_f16, int m, int n,
                             int k, void* stream);
 
+/* ---- fused add + RMSNorm with the residual stream ------------------------------
+ * Replaces rmsnorm_residual_<H> (src/ptx_emitter.rs:5773-6015; parameters X,
+ * Residual, Weight, Out, NewResidual, all f16; one CTA of 256 threads per row):
+ *   h = X + Residual (f32), Out = f16((h * rsqrt(mean(h^2) + eps)) * Weight),
+ *   NewResidual = f16(h).
+ * x, residual, out, new_residual [rows, hidden] f16; weight [hidden] f16. The reference
+ * fixes eps = 1e-5 and hidden % 256 == 0; here eps is a parameter and hidden % 8 == 0. */
+Y_B200_API int y_b200_rmsnorm_residual(const void* x_f16, const void* residual_f16, const void* weight_f16,
+                                       size_t rows, size_t hidden, float eps, void* out_f16,
+                                       void* new_residual_f16, void* stream);
+
 /* ---- input generator ---------------------------------------------------------
  * random_f16_bits (src/cuda_runtime.rs:657-682): element i = f(i + index0, seed),
  * a normal binary16 with exponent in 12..14. Written on the device. */

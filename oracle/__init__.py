@@ -33,14 +33,22 @@ def build(force: bool = False) -> None:
                        stdout=subprocess.DEVNULL)
 
 
-def _load(name: str) -> C.CDLL:
+def _stale(name: str, sources) -> bool:
     path = os.path.join(_HERE, name)
     if not os.path.exists(path):
-        build()
-    return C.CDLL(path)
+        return True
+    built = os.path.getmtime(path)
+    return any(os.path.getmtime(os.path.join(_HERE, s)) > built for s in sources
+               if os.path.exists(os.path.join(_HERE, s)))
 
 
-_lib = _load("liboracle.so")
+def _load(name: str, sources=()) -> C.CDLL:
+    if _stale(name, sources):  # missing, or older than its sources: make rebuilds what changed
+        subprocess.run(["make", "-C", _HERE], check=True, stdout=subprocess.DEVNULL)
+    return C.CDLL(os.path.join(_HERE, name))
+
+
+_lib = _load("liboracle.so", ("oracle.c", "oracle.h"))
 
 _u8p = C.POINTER(C.c_uint8)
 _u16p = C.POINTER(C.c_uint16)
@@ -76,6 +84,7 @@ _q16 = _sig("orc_quantize_fp8_f16", None, _u16p, C.c_size_t, C.c_float, _u8p)
 _q32 = _sig("orc_quantize_fp8_f32", None, _f32p, C.c_size_t, C.c_float, _u8p)
 _q16t = _sig("orc_quantize_fp8_f16_transpose", None, _u16p, C.c_size_t, C.c_size_t, C.c_float, _u8p)
 _rms = _sig("orc_rmsnorm_f16", C.c_float, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float, _f32p, _f32p)
+_rmsres = _sig("orc_rmsnorm_residual_f16", None, _u16p, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float, _u16p, _u16p)
 _rmsq = _sig("orc_rmsnorm_quantize_fp8", None, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float,
              _u8p, _f32p)
 _gemm8 = _sig("orc_gemm_fp8", None, _u8p, _u8p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float,
@@ -211,6 +220,16 @@ def rmsnorm_f16(x: np.ndarray, gamma: np.ndarray, eps: float):
     rstd = np.empty(rows, np.float32)
     amax = _rms(_p(x, _u16p), _p(gamma, _u16p), rows, hidden, eps, _p(y, _f32p), _p(rstd, _f32p))
     return y, rstd, float(amax)
+
+
+def rmsnorm_residual_f16(x: np.ndarray, residual: np.ndarray, weight: np.ndarray, eps: float):
+    """Fused add + RMSNorm on f16 bit patterns. Returns (out, new_residual), both uint16 [rows, hidden]."""
+    x, residual, weight = _c(x, np.uint16), _c(residual, np.uint16), _c(weight, np.uint16)
+    rows, hidden = x.shape
+    out = np.empty((rows, hidden), np.uint16)
+    new_res = np.empty((rows, hidden), np.uint16)
+    _rmsres(_p(x, _u16p), _p(residual, _u16p), _p(weight, _u16p), rows, hidden, eps, _p(out, _u16p), _p(new_res, _u16p))
+    return out, new_res
 
 
 def rmsnorm_quantize_fp8(x: np.ndarray, gamma: np.ndarray, eps: float):

@@ -327,6 +327,61 @@ void orc_rmsnorm_quantize_fp8(const uint16_t* x, const uint16_t* gamma, size_t r
 }
 
 /* ------------------------------------------------------------------------
+ * Fused add + RMSNorm with the residual stream, f16 in and out
+ *
+ * Follows emit_rmsnorm_residual_kernel (src/ptx_emitter.rs:5773-6015):
+ *   h = f32(x) + f32(residual)                (:5877, h stays f32 for the norm)
+ *   total = sum(h^2) over the row
+ *   mean = total * f32(1 / hidden)            (:5910, a multiply by the reciprocal)
+ *   inv_rms = rsqrt(mean + eps)               (:5914; the reference uses
+ *             rsqrt.approx.f32 and fixes eps = 1e-5; here rsqrt is the correctly
+ *             rounded 1/sqrt and eps is a parameter, so that results can be pinned)
+ *   out = f16_rn((h * inv_rms) * w)           (:5957-5959, two multiplies)
+ *   new_residual = f16_rn(h)                  (:6003)
+ * The sum of squares uses the same fixed order as the prologue above (worker t of
+ * 256 folds vectors t, t+256, ... with fma; butterfly inside blocks of 32; the
+ * eight block totals in order); the reference's own order is the same up to
+ * whether ptxas fuses its mul+add.
+ * ---------------------------------------------------------------------- */
+void orc_rmsnorm_residual_f16(const uint16_t* x, const uint16_t* residual, const uint16_t* weight,
+                              size_t rows, size_t hidden, float eps, uint16_t* out,
+                              uint16_t* new_residual) {
+    const float inv_hidden = 1.0f / (float)hidden;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; ++r) {
+        float* h = (float*)malloc(hidden * sizeof(float));
+        for (size_t c = 0; c < hidden; ++c)
+            h[c] = orc_f16_bits_to_f32(x[r * hidden + c]) + orc_f16_bits_to_f32(residual[r * hidden + c]);
+        float part[256];
+        size_t nvec = hidden / 8;
+        for (int t = 0; t < 256; ++t) {
+            float acc = 0.0f;
+            for (size_t v = (size_t)t; v < nvec; v += 256)
+                for (int j = 0; j < 8; ++j) acc = fmaf(h[v * 8 + (size_t)j], h[v * 8 + (size_t)j], acc);
+            part[t] = acc;
+        }
+        float total = 0.0f;
+        for (int w = 0; w < 8; ++w) {
+            float lane[32], next[32];
+            memcpy(lane, part + 32 * w, sizeof lane);
+            for (int off = 16; off >= 1; off >>= 1) {
+                for (int l = 0; l < 32; ++l) next[l] = lane[l] + lane[l ^ off];
+                memcpy(lane, next, sizeof lane);
+            }
+            total = (w == 0) ? lane[0] : total + lane[0];
+        }
+        float mean = total * inv_hidden;
+        float rstd = 1.0f / sqrtf(mean + eps);
+        for (size_t c = 0; c < hidden; ++c) {
+            float y = (h[c] * rstd) * orc_f16_bits_to_f32(weight[c]);
+            out[r * hidden + c] = orc_f32_to_f16_bits(y);
+            new_residual[r * hidden + c] = orc_f32_to_f16_bits(h[c]);
+        }
+        free(h);
+    }
+}
+
+/* ------------------------------------------------------------------------
  * GEMM + epilogues
  * ---------------------------------------------------------------------- */
 

@@ -69,6 +69,9 @@ void  orc_quantize_fp8_f16_transpose(const uint16_t* x, size_t rows, size_t cols
  * y_out (optional) receives the f32 normalised rows; returns amax(|y|).    */
 float orc_rmsnorm_f16(const uint16_t* x, const uint16_t* gamma, size_t rows,
                       size_t hidden, float eps, float* y_out, float* rstd_out);
+void  orc_rmsnorm_residual_f16(const uint16_t* x, const uint16_t* residual, const uint16_t* weight,
+                                size_t rows, size_t hidden, float eps, uint16_t* out,
+                                uint16_t* new_residual);
 void  orc_rmsnorm_quantize_fp8(const uint16_t* x, const uint16_t* gamma,
                                size_t rows, size_t hidden, float eps,
                                uint8_t* q, float* scale_out);

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import dev, f16_dev
+from helpers import dev, f16_dev, host_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -132,3 +132,47 @@ def test_bad_arguments_are_reported_not_launched(q):
         q.rmsnorm_quantize_fp8(torch.zeros(2, 12, dtype=torch.float16, device="cuda"),
                                torch.zeros(12, dtype=torch.float16, device="cuda"))
     assert e.value.code == ERR_SHAPE
+
+
+@pytest.mark.parametrize("rows,hidden", [(5, 256), (3, 8), (33, 2048), (64, 4096), (16, 8192), (5, 4096 + 256),
+                                         (3, 16384 + 8)])
+def test_fused_add_rmsnorm_bit_exact(q, rows, hidden):
+    """The reference's rmsnorm_residual_<H> kernel: Out and NewResidual, both f16."""
+    x = oracle.fill_normal_f16(rows * hidden, oracle.SEED_A + 11).reshape(rows, hidden)
+    r = oracle.fill_normal_f16(rows * hidden, oracle.SEED_A + 12).reshape(rows, hidden)
+    w = oracle.fill_uniform_f16(hidden, oracle.SEED_A + 2, 0.5, 1.5)
+    out, new_res = q.fused_add_rmsnorm(f16_dev(x), f16_dev(r), f16_dev(w), 1e-5)
+    ref_out, ref_res = oracle.rmsnorm_residual_f16(x, r, w, 1e-5)
+    assert np.array_equal(host_bits(new_res), ref_res)
+    assert np.array_equal(host_bits(out), ref_out)
+    # in place on the residual stream, as a decoder layer uses it
+    rd = f16_dev(r)
+    out2, nr2 = q.fused_add_rmsnorm(f16_dev(x), rd, f16_dev(w), 1e-5, new_residual=rd)
+    assert nr2.data_ptr() == rd.data_ptr()
+    assert np.array_equal(host_bits(rd), ref_res) and np.array_equal(host_bits(out2), ref_out)
+
+
+def test_fused_add_rmsnorm_through_the_launch_api(cuda):
+    """compile -> load_module('rmsnorm_residual_4096') -> launch with grid = rows."""
+    from y_b200 import runtime as rt
+    src = ("kernel rmsnorm_residual_4096(X: GlobalMemory<F16>, Residual: GlobalMemory<F16>, "
+           "Weight: GlobalMemory<F16>, Out: GlobalMemory<F16>, NewResidual: GlobalMemory<F16>) {}")
+    rows, hidden = 12, 4096
+    x = oracle.fill_normal_f16(rows * hidden, 21).reshape(rows, hidden)
+    r = oracle.fill_normal_f16(rows * hidden, 22).reshape(rows, hidden)
+    w = oracle.fill_uniform_f16(hidden, 23, 0.5, 1.5)
+    xd, rdv, wd = f16_dev(x), f16_dev(r), f16_dev(w)
+    out = torch.empty_like(xd)
+    nres = torch.empty_like(xd)
+    ctx = rt.CudaContext.new()
+    kern = ctx.load_module(rt.compile_to_ptx(src), "rmsnorm_residual_4096")
+    ctx.launch(kern, (rows, 1, 1), (256, 1, 1), 0,
+               [xd.data_ptr(), rdv.data_ptr(), wd.data_ptr(), out.data_ptr(), nres.data_ptr()])
+    ctx.synchronize()
+    ref_out, ref_res = oracle.rmsnorm_residual_f16(x, r, w, 1e-5)
+    assert np.array_equal(host_bits(out), ref_out) and np.array_equal(host_bits(nres), ref_res)
+    with pytest.raises(rt.YB200Error):
+        ctx.launch(kern, (rows, 1, 1), (128, 1, 1), 0,
+                   [xd.data_ptr(), rdv.data_ptr(), wd.data_ptr(), out.data_ptr(), nres.data_ptr()])
+    kern.free()
+    ctx.close()

@@ -232,3 +232,20 @@ def test_committed_path_vectors_still_hold(golden_dir):
     qw, sc = oracle.int4_quantize(w)
     assert np.array_equal(qw, g["int4_qweight"]) and np.array_equal(sc, g["int4_scales"])
     assert np.array_equal(oracle.int4_repack(qw, sc), g["int4_stream"])
+
+
+def test_fused_add_rmsnorm_restatement_against_float64():
+    """orc_rmsnorm_residual_f16 against the formula in float64: both outputs are within one
+    f16 rounding of it, and NewResidual is exactly the f16 rounding of the f32 sum."""
+    rows, hidden = 7, 768
+    x = oracle.fill_normal_f16(rows * hidden, 5).reshape(rows, hidden)
+    r = oracle.fill_normal_f16(rows * hidden, 6).reshape(rows, hidden)
+    w = oracle.fill_uniform_f16(hidden, 7, 0.5, 1.5)
+    out, new_res = oracle.rmsnorm_residual_f16(x, r, w, 1e-5)
+    xf, rf, wf = (a.view(np.float16).astype(np.float64) for a in (x, r, w))
+    h = xf + rf
+    ref = h / np.sqrt((h * h).mean(axis=1, keepdims=True) + 1e-5) * wf
+    got = out.view(np.float16).astype(np.float64)
+    assert np.all(np.abs(got - ref) <= np.maximum(np.abs(ref) * 2.0 ** -10, 2.0 ** -24))
+    h32 = x.view(np.float16).astype(np.float32) + r.view(np.float16).astype(np.float32)
+    assert np.array_equal(new_res, h32.astype(np.float16).view(np.uint16))

@@ -457,6 +457,106 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- fused add + RMSNorm with the residual stream (f16 in, f16 out) ------------------------
+// h = x + residual in f32; total = sum(h^2) in the fixed order above; mean = total * (1/hidden);
+// out = f16((h * rstd) * w); new_residual = f16(h). One 256-thread CTA per row. VPT > 0: the
+// row (at most VPT * 256 vectors) lives in registers as f32 between the two phases, so x and
+// residual are read once; VPT == 0: any length, the second phase re-reads them.
+__device__ __forceinline__ void add8_f16(const uint4& a, const uint4& b, float (&h)[8]) {
+    float fa[8], fb[8];
+    unpack8<Y_B200_F16>(a, fa);
+    unpack8<Y_B200_F16>(b, fb);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = __fadd_rn(fa[j], fb[j]);
+}
+
+__device__ __forceinline__ uint4 pack8_f16(const float (&v)[8]) {
+    return make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
+                      pack_f16x2(v[6], v[7]));
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(kThreads)
+    rmsnorm_residual_kernel(const __half* __restrict__ x, const __half* __restrict__ residual,
+                            const __half* __restrict__ weight, size_t hidden, float eps,
+                            __half* __restrict__ out, __half* __restrict__ new_residual) {
+    __shared__ float warp_tot[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row0 = (size_t)blockIdx.x * hidden;
+    const uint4* xv = reinterpret_cast<const uint4*>(x + row0);
+    const uint4* rv = reinterpret_cast<const uint4*>(residual + row0);
+    const uint4* wv = reinterpret_cast<const uint4*>(weight);
+    uint4* ov = reinterpret_cast<uint4*>(out + row0);
+    uint4* nv = reinterpret_cast<uint4*>(new_residual + row0);
+    const uint32_t nvec = (uint32_t)(hidden / 8);
+    const float inv_hidden = __fdiv_rn(1.0f, (float)hidden);
+    float acc = 0.0f;
+    if constexpr (VPT > 0) {
+        float h[VPT][8];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const uint32_t v = threadIdx.x + i * kThreads;
+            if (v < nvec) {
+                add8_f16(xv[v], rv[v], h[i]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[i][j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = __fmaf_rn(h[i][j], h[i][j], acc);
+        }
+        // Same reduction order as the prologue kernels; the mean is total * (1 / hidden)
+        // here (a multiply, as in the reference kernel), not a division.
+        float total;
+        {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+            if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            total = warp_tot[0];
+#pragma unroll
+            for (int w = 1; w < 8; ++w) total = __fadd_rn(total, warp_tot[w]);
+        }
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(total, inv_hidden), eps)));
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const uint32_t v = threadIdx.x + i * kThreads;
+            if (v >= nvec) continue;
+            float g[8], y[8];
+            unpack8<Y_B200_F16>(wv[v], g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = __fmul_rn(__fmul_rn(h[i][j], rstd), g[j]);
+            ov[v] = pack8_f16(y);
+            nv[v] = pack8_f16(h[i]);
+        }
+    } else {
+        for (uint32_t v = threadIdx.x; v < nvec; v += kThreads) {
+            float h[8];
+            add8_f16(xv[v], rv[v], h);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = __fmaf_rn(h[j], h[j], acc);
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+        if ((threadIdx.x & 31) == 0) warp_tot[threadIdx.x >> 5] = acc;
+        __syncthreads();
+        float total = warp_tot[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) total = __fadd_rn(total, warp_tot[w]);
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(total, inv_hidden), eps)));
+        for (uint32_t v = threadIdx.x; v < nvec; v += kThreads) {
+            float h[8], g[8], y[8];
+            add8_f16(xv[v], rv[v], h);
+            unpack8<Y_B200_F16>(wv[v], g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) y[j] = __fmul_rn(__fmul_rn(h[j], rstd), g[j]);
+            ov[v] = pack8_f16(y);
+            nv[v] = pack8_f16(h);
+        }
+    }
+}
+
 // ---- input generator --------------------------------------------------------------------
 __device__ __forceinline__ uint64_t splitmix64(uint64_t index, uint64_t seed) {
     uint64_t z = index * 0x9E3779B97F4A7C15ull + seed + 0x9E3779B97F4A7C15ull;
@@ -664,6 +764,34 @@ extern "C" int y_b200_rmsnorm_quantize_fp8(const void* x_f16, const void* gamma_
     YB_CUDA(launch_pdl(rmsnorm_quantize_kernel, (unsigned)rows, kThreads, 0, st, xh, gh, hidden, rstd,
                        reinterpret_cast<const float*>(amax), static_cast<uint8_t*>(q), scale_out));
     return check_cuda(cudaGetLastError(), "rmsnorm_quantize_kernel launch");
+}
+
+extern "C" int y_b200_rmsnorm_residual(const void* x_f16, const void* residual_f16, const void* weight_f16,
+                                       size_t rows, size_t hidden, float eps, void* out_f16,
+                                       void* new_residual_f16, void* stream) {
+    if (!x_f16 || !residual_f16 || !weight_f16 || !out_f16 || !new_residual_f16)
+        return fail(Y_B200_ERR_INVALID, "y_b200_rmsnorm_residual: null pointer");
+    if (hidden == 0 || hidden % 8 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_rmsnorm_residual: hidden=%zu must be a positive multiple of 8", hidden);
+    if (!aligned16(x_f16) || !aligned16(residual_f16) || !aligned16(weight_f16) || !aligned16(out_f16) ||
+        !aligned16(new_residual_f16))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_rmsnorm_residual: pointers must be 16-byte aligned");
+    if (rows == 0) return Y_B200_OK;
+    if (rows > 0x7fffffffu) return fail(Y_B200_ERR_SHAPE, "y_b200_rmsnorm_residual: too many rows");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xh = static_cast<const __half*>(x_f16);
+    const __half* rh = static_cast<const __half*>(residual_f16);
+    const __half* wh = static_cast<const __half*>(weight_f16);
+    __half* oh = static_cast<__half*>(out_f16);
+    __half* nh = static_cast<__half*>(new_residual_f16);
+    const size_t nvec = hidden / 8;
+    const unsigned grid = (unsigned)rows;
+    cudaError_t e;
+    if (nvec <= kThreads) e = launch_pdl(rmsnorm_residual_kernel<1>, grid, kThreads, 0, st, xh, rh, wh, hidden, eps, oh, nh);
+    else if (nvec <= 2 * kThreads) e = launch_pdl(rmsnorm_residual_kernel<2>, grid, kThreads, 0, st, xh, rh, wh, hidden, eps, oh, nh);
+    else if (nvec <= 4 * kThreads) e = launch_pdl(rmsnorm_residual_kernel<4>, grid, kThreads, 0, st, xh, rh, wh, hidden, eps, oh, nh);
+    else e = launch_pdl(rmsnorm_residual_kernel<0>, grid, kThreads, 0, st, xh, rh, wh, hidden, eps, oh, nh);
+    return check_cuda(e, "rmsnorm_residual_kernel launch");
 }
 
 extern "C" int y_b200_fill_random_f16(void* out_f16, size_t n, uint64_t index0, uint64_t seed,

@@ -23,7 +23,7 @@ struct y_buf {
     int device;
 };
 
-enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode };
+enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode, RmsnormResidual };
 
 struct y_kernel {
     Entry entry;
@@ -152,6 +152,21 @@ int launch_once(y_kernel* k, const unsigned grid[3], const unsigned block[3], un
                                            reinterpret_cast<const void*>(a[1].v.ptr),
                                            reinterpret_cast<void*>(a[2].v.ptr), a[3].v.i32, a[4].v.i32,
                                            a[5].v.i32, nullptr);
+        }
+        case Entry::RmsnormResidual: {
+            // (X, Residual, Weight, Out, NewResidual); one CTA of 256 threads per row, so the
+            // grid is the number of rows (src/ptx_emitter.rs:5773-5790). eps is the reference's 1e-5.
+            static const int kinds[5] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR};
+            int rc = expect_args(a, nargs, kinds, 5, "rmsnorm_residual_<H>");
+            if (rc) return rc;
+            if (!grid || grid[0] == 0 || grid[1] != 1 || grid[2] != 1)
+                return fail(Y_B200_ERR_INVALID, "rmsnorm_residual_<H>: the launch grid must be (rows, 1, 1)");
+            if (block && (block[0] != 256 || block[1] != 1 || block[2] != 1))
+                return fail(Y_B200_ERR_INVALID, "rmsnorm_residual_<H>: launch block (%u,%u,%u) differs from the kernel's own (256,1,1)",
+                            block[0], block[1], block[2]);
+            return y_b200_rmsnorm_residual(reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                                           reinterpret_cast<const void*>(a[2].v.ptr), grid[0], (size_t)k->k, 1e-5f,
+                                           reinterpret_cast<void*>(a[3].v.ptr), reinterpret_cast<void*>(a[4].v.ptr), nullptr);
         }
     }
     return fail(Y_B200_ERR_UNSUPPORTED, "unknown kernel entry");
@@ -311,6 +326,20 @@ extern "C" y_kernel* y_ctx_load_module(y_ctx* ctx, const char* image, const char
             return nullptr;
         }
         const std::string fam = img.substr(at + tag.size(), img.find_first_of(" \n", at + tag.size()) - at - tag.size());
+        if (fam == "rmsnorm_residual") {
+            // rmsnorm_residual_<H>: the hidden size is the name's suffix; rows come with the launch grid
+            const long long hidden = atoll(name.c_str() + strlen("rmsnorm_residual_"));
+            if (name.rfind("rmsnorm_residual_", 0) != 0 || hidden <= 0 || hidden % 8 != 0 || hidden > 0x7fffffff) {
+                fail(Y_B200_ERR_INVALID, "y_ctx_load_module: '%s' does not name a hidden size that is a multiple of 8", entry);
+                return nullptr;
+            }
+            k.entry = Entry::RmsnormResidual;
+            k.k = (int)hidden;
+            y_kernel* res = static_cast<y_kernel*>(malloc(sizeof(y_kernel)));
+            if (!res) return nullptr;
+            *res = k;
+            return res;
+        }
         if (fam != "gemm_fp8") {
             fail(Y_B200_ERR_UNSUPPORTED, "y_ctx_load_module: family '%s' of '%s' has no sm_100a kernel in this library",
                  fam.c_str(), entry);

@@ -113,6 +113,23 @@ def rmsnorm_quantize_fp8(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6
     return q, s
 
 
+def fused_add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5,
+                      out: torch.Tensor | None = None, new_residual: torch.Tensor | None = None):
+    """h = x + residual; returns (rmsnorm(h) * weight, h), both f16 [rows, hidden]
+    (the reference's rmsnorm_residual_<H> kernel; `new_residual` may alias `residual`)."""
+    _dev(x, "x"), _dev(residual, "residual"), _dev(weight, "weight")
+    if x.dtype != torch.float16 or residual.dtype != torch.float16 or weight.dtype != torch.float16:
+        raise ValueError("fused_add_rmsnorm takes f16 tensors")
+    if x.shape != residual.shape or weight.shape != (x.shape[1],):
+        raise ValueError("fused_add_rmsnorm: x and residual [rows, hidden], weight [hidden]")
+    rows, hidden = x.shape
+    o = out if out is not None else torch.empty_like(x)
+    nr = new_residual if new_residual is not None else torch.empty_like(x)
+    check(lib.y_b200_rmsnorm_residual(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), rows, hidden, eps,
+                                      o.data_ptr(), nr.data_ptr(), _stream()))
+    return o, nr
+
+
 # ---- FP8 GEMM -----------------------------------------------------------------
 def _scale_fields(args: GemmFp8Args, name: str, s) -> None:
     if isinstance(s, torch.Tensor):
