@@ -268,6 +268,14 @@ def other_config_metrics(peaks):
     gbs = 8.0 * x.numel() / us / 1e3
     out["fused_add_rmsnorm_f16_8192x8192"] = {"us": round(us, 2), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
                                               "bytes": "8 per element: read x and residual, write out and new residual"}
+    # rotary embedding, 8192 tokens x 32 heads x 128: 4 bytes per element + one position per row
+    del r, o, nr
+    xr = torch.randn(8192 * 32, 128, device="cuda", dtype=torch.float16)
+    pos = torch.randint(0, 4096, (8192 * 32,), dtype=torch.int32, device="cuda")
+    orope = torch.empty_like(xr)
+    us = timeit(lambda: q.rope(xr, pos, out=orope), iters=20)
+    gbs = (4.0 * xr.numel() + 4.0 * pos.numel()) / us / 1e3
+    out["rope_f16_8192x32x128"] = {"us": round(us, 2), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4)}
     q.device_status()
     return out
 

@@ -215,6 +215,16 @@ Y_B200_API int y_b200_rmsnorm_residual(const void* x_f16, const void* residual_f
                                        size_t rows, size_t hidden, float eps, void* out_f16,
                                        void* new_residual_f16, void* stream);
 
+/* ---- rotary position embedding ---------------------------------------------------
+ * Replaces rope_<head_dim> (src/ptx_emitter.rs:6016-6260; parameters X f16, Positions
+ * i32, Out f16; one warp per row, a row being one token's query or key vector of one
+ * head): interleaved pairs (2i, 2i+1), theta_i = Positions[row] * base^(-2i/head_dim),
+ *   out[2i] = x[2i] cos - x[2i+1] sin,  out[2i+1] = x[2i] sin + x[2i+1] cos.
+ * The reference fixes base = 10000 and takes head_dim % 64 == 0; here base is a
+ * parameter and head_dim is 64, 128 or 256. out may alias x. */
+Y_B200_API int y_b200_rope(const void* x_f16, const int32_t* positions, void* out_f16, size_t rows, int head_dim,
+                           float base, void* stream);
+
 /* ---- input generator ---------------------------------------------------------
  * random_f16_bits (src/cuda_runtime.rs:657-682): element i = f(i + index0, seed),
  * a normal binary16 with exponent in 12..14. Written on the device. */

@@ -85,6 +85,7 @@ _q32 = _sig("orc_quantize_fp8_f32", None, _f32p, C.c_size_t, C.c_float, _u8p)
 _q16t = _sig("orc_quantize_fp8_f16_transpose", None, _u16p, C.c_size_t, C.c_size_t, C.c_float, _u8p)
 _rms = _sig("orc_rmsnorm_f16", C.c_float, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float, _f32p, _f32p)
 _rmsres = _sig("orc_rmsnorm_residual_f16", None, _u16p, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float, _u16p, _u16p)
+_rope = _sig("orc_rope_f16", None, _u16p, C.POINTER(C.c_int32), C.c_size_t, C.c_int, C.c_float, _u16p)
 _rmsq = _sig("orc_rmsnorm_quantize_fp8", None, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float,
              _u8p, _f32p)
 _gemm8 = _sig("orc_gemm_fp8", None, _u8p, _u8p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float,
@@ -230,6 +231,15 @@ def rmsnorm_residual_f16(x: np.ndarray, residual: np.ndarray, weight: np.ndarray
     new_res = np.empty((rows, hidden), np.uint16)
     _rmsres(_p(x, _u16p), _p(residual, _u16p), _p(weight, _u16p), rows, hidden, eps, _p(out, _u16p), _p(new_res, _u16p))
     return out, new_res
+
+
+def rope_f16(x: np.ndarray, positions: np.ndarray, base: float = 10000.0) -> np.ndarray:
+    """Interleaved-pair rotary embedding on f16 bit patterns [rows, head_dim]; positions int32 [rows]."""
+    x, positions = _c(x, np.uint16), _c(positions, np.int32)
+    rows, head_dim = x.shape
+    out = np.empty((rows, head_dim), np.uint16)
+    _rope(_p(x, _u16p), positions.ctypes.data_as(C.POINTER(C.c_int32)), rows, head_dim, base, _p(out, _u16p))
+    return out
 
 
 def rmsnorm_quantize_fp8(x: np.ndarray, gamma: np.ndarray, eps: float):

@@ -382,6 +382,42 @@ void orc_rmsnorm_residual_f16(const uint16_t* x, const uint16_t* residual, const
 }
 
 /* ------------------------------------------------------------------------
+ * Rotary position embedding, interleaved pairs (2i, 2i+1), f16 in and out
+ *
+ * Follows emit_rope_kernel (src/ptx_emitter.rs:6046-6260):
+ *   theta_i = f32(pos) * inv_freq_i in f32,  inv_freq_i = base^(-2i/head_dim)
+ *   out[2i]   = fl(fl(x0*cos) - fl(x1*sin)),  out[2i+1] = fl(fl(x0*sin) + fl(x1*cos))
+ * one position per row (Positions[row], i32). The reference gets inv_freq from
+ * ex2.approx and the trig from sin.approx / cos.approx; here inv_freq_i is the f32
+ * rounding of the double-precision power (the library passes the same table to its
+ * kernel) and sin/cos are those of the f32 theta evaluated in double precision, so the
+ * only device-side freedom left is the last bit of sin/cos.
+ * ---------------------------------------------------------------------- */
+void orc_rope_inv_freq(int head_dim, float base, float* inv_freq) {
+    for (int i = 0; i < head_dim / 2; ++i)
+        inv_freq[i] = (float)pow((double)base, -2.0 * (double)i / (double)head_dim);
+}
+
+void orc_rope_f16(const uint16_t* x, const int32_t* positions, size_t rows, int head_dim, float base,
+                  uint16_t* out) {
+    float inv_freq[1024];
+    orc_rope_inv_freq(head_dim, base, inv_freq);
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; ++r) {
+        const float pos = (float)positions[r];
+        for (int i = 0; i < head_dim / 2; ++i) {
+            const float theta = pos * inv_freq[i];
+            const float s = (float)sin((double)theta), c = (float)cos((double)theta);
+            const float x0 = orc_f16_bits_to_f32(x[r * (size_t)head_dim + 2 * (size_t)i]);
+            const float x1 = orc_f16_bits_to_f32(x[r * (size_t)head_dim + 2 * (size_t)i + 1]);
+            const float a = x0 * c, b = x1 * s, d = x0 * s, e = x1 * c;
+            out[r * (size_t)head_dim + 2 * (size_t)i] = orc_f32_to_f16_bits(a - b);
+            out[r * (size_t)head_dim + 2 * (size_t)i + 1] = orc_f32_to_f16_bits(d + e);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------
  * GEMM + epilogues
  * ---------------------------------------------------------------------- */
 

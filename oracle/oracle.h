@@ -72,6 +72,9 @@ float orc_rmsnorm_f16(const uint16_t* x, const uint16_t* gamma, size_t rows,
 void  orc_rmsnorm_residual_f16(const uint16_t* x, const uint16_t* residual, const uint16_t* weight,
                                 size_t rows, size_t hidden, float eps, uint16_t* out,
                                 uint16_t* new_residual);
+void  orc_rope_inv_freq(int head_dim, float base, float* inv_freq);
+void  orc_rope_f16(const uint16_t* x, const int32_t* positions, size_t rows, int head_dim, float base,
+                   uint16_t* out);
 void  orc_rmsnorm_quantize_fp8(const uint16_t* x, const uint16_t* gamma,
                                size_t rows, size_t hidden, float eps,
                                uint8_t* q, float* scale_out);

@@ -176,3 +176,42 @@ def test_fused_add_rmsnorm_through_the_launch_api(cuda):
                    [xd.data_ptr(), rdv.data_ptr(), wd.data_ptr(), out.data_ptr(), nres.data_ptr()])
     kern.free()
     ctx.close()
+
+
+@pytest.mark.parametrize("rows,head_dim", [(1, 64), (37, 64), (200, 128), (33, 256), (4096, 128)])
+def test_rope_matches_oracle(q, rows, head_dim):
+    """Same inv_freq table and the same f32 theta on both sides, so only the last bit of
+    sin/cos can differ: outputs agree except for rare one-ulp f16 rounding flips."""
+    x = oracle.fill_normal_f16(rows * head_dim, oracle.SEED_A + 31).reshape(rows, head_dim)
+    rng = np.random.default_rng(rows + head_dim)
+    pos = rng.integers(0, 4096, size=rows).astype(np.int32)
+    pos[0] = 0
+    pos[-1] = 4095
+    out = q.rope(f16_dev(x), torch.from_numpy(pos).cuda())
+    got, ref = host_bits(out), oracle.rope_f16(x, pos)
+    gf, rf = got.view(np.float16).astype(np.float64), ref.view(np.float16).astype(np.float64)
+    assert np.all(np.abs(gf - rf) <= np.maximum(np.abs(rf) * 2.0 ** -10, 2.0 ** -14))  # one f16 ulp
+    assert (got != ref).mean() < 0.01
+    assert np.array_equal(got[pos == 0], x[pos == 0])  # position 0 is the identity
+    # in place
+    xd = f16_dev(x)
+    q.rope(xd, torch.from_numpy(pos).cuda(), out=xd)
+    assert np.array_equal(host_bits(xd), got)
+
+
+def test_rope_through_the_launch_api(cuda):
+    from y_b200 import runtime as rt
+    src = "kernel rope_128(X: GlobalMemory<F16>, Positions: GlobalMemory<I32>, Out: GlobalMemory<F16>) {}"
+    rows = 50
+    x = oracle.fill_normal_f16(rows * 128, 77).reshape(rows, 128)
+    pos = np.arange(rows, dtype=np.int32) * 80
+    xd, pd = f16_dev(x), torch.from_numpy(pos).cuda()
+    out = torch.empty_like(xd)
+    ctx = rt.CudaContext.new()
+    kern = ctx.load_module(rt.compile_to_ptx(src), "rope_128")
+    ctx.launch(kern, (rows, 1, 1), (32, 1, 1), 0, [xd.data_ptr(), pd.data_ptr(), out.data_ptr()])
+    ctx.synchronize()
+    from y_b200 import quant
+    assert torch.equal(out, quant.rope(xd, pd))
+    kern.free()
+    ctx.close()

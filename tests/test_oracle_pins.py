@@ -249,3 +249,21 @@ def test_fused_add_rmsnorm_restatement_against_float64():
     assert np.all(np.abs(got - ref) <= np.maximum(np.abs(ref) * 2.0 ** -10, 2.0 ** -24))
     h32 = x.view(np.float16).astype(np.float32) + r.view(np.float16).astype(np.float32)
     assert np.array_equal(new_res, h32.astype(np.float16).view(np.uint16))
+
+
+def test_rope_restatement_against_float64():
+    rows, hd = 9, 128
+    x = oracle.fill_normal_f16(rows * hd, 3).reshape(rows, hd)
+    pos = np.array([0, 1, 2, 17, 100, 1000, 2047, 4000, 4095], np.int32)
+    out = oracle.rope_f16(x, pos).view(np.float16).astype(np.float64)
+    xf = x.view(np.float16).astype(np.float64).reshape(rows, hd // 2, 2)
+    theta = pos[:, None].astype(np.float64) * 10000.0 ** (-2.0 * np.arange(hd // 2) / hd)
+    ref = np.stack([xf[..., 0] * np.cos(theta) - xf[..., 1] * np.sin(theta),
+                    xf[..., 0] * np.sin(theta) + xf[..., 1] * np.cos(theta)], -1).reshape(rows, hd)
+    # f32 theta at positions in the thousands is good to ~2.5e-4 rad; then one f16 rounding
+    assert np.abs(out - ref).max() < 4e-3
+    assert np.array_equal(oracle.rope_f16(x[:1], pos[:1]), x[:1])  # position 0 is the identity
+    # rotations preserve the norm of each pair
+    n_in = np.hypot(xf[..., 0], xf[..., 1])
+    o = out.reshape(rows, hd // 2, 2)
+    assert np.abs(np.hypot(o[..., 0], o[..., 1]) - n_in).max() < 4e-3

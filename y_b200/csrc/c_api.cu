@@ -165,6 +165,9 @@ KernelFamily classify_kernel(const KernelDecl& k, std::string* err) {
         if (k.params.size() == 5 && k.name.rfind("rmsnorm_residual_", 0) == 0 && gm(0, "F16") &&
             gm(1, "F16") && gm(2, "F16") && gm(3, "F16") && gm(4, "F16"))
             return KernelFamily::RmsnormResidual;
+        // rope_<head_dim>(X: F16, Positions: I32, Out: F16) (src/ptx_emitter.rs:6016-6044)
+        if (k.params.size() == 3 && k.name.rfind("rope_", 0) == 0 && gm(0, "F16") && gm(1, "I32") && gm(2, "F16"))
+            return KernelFamily::Rope;
         return KernelFamily::None;
     }
     const size_t np = k.params.size();
@@ -193,6 +196,7 @@ const char* family_name(KernelFamily f) {
         case KernelFamily::GemmF16BiasRelu: return "gemm_f16_bias_relu";
         case KernelFamily::GemmF16Swiglu: return "gemm_f16_swiglu";
         case KernelFamily::RmsnormResidual: return "rmsnorm_residual";
+        case KernelFamily::Rope: return "rope";
         default: return "none";
     }
 }
@@ -229,6 +233,8 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         out += buf;
     } else if (fam == KernelFamily::RmsnormResidual) {
         out += "// [Y RMSNORM] one 256-thread CTA per row; 128-bit loads; fixed-order reduction\n";
+    } else if (fam == KernelFamily::Rope) {
+        out += "// [Y FUSED ROPE] 1 warp (32 threads) per row | interleaved pairs, base=10000\n";
     } else {
         const uint32_t cta_k = 64;
         snprintf(buf, sizeof buf,

@@ -557,6 +557,83 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// ---- rotary position embedding (interleaved pairs), f16 in and out ---------------------------
+// A warp takes four consecutive rows (a row is one token's query or key vector of one
+// head); in each, lane L owns the contiguous pairs [L * PPT, (L + 1) * PPT), so a warp
+// reads and writes contiguous spans.
+// inv_freq comes in as a kernel parameter (the host computes base^(-2i/head_dim) in double
+// precision once per call), theta = f32(pos) * inv_freq[i], and sin/cos are taken after a
+// two-term Cody-Waite reduction to [-pi, pi] so the fast units stay accurate at positions
+// in the thousands.
+constexpr int kRopeMaxPairs = 128;  // head_dim <= 256
+struct RopeTable {
+    float inv_freq[kRopeMaxPairs];
+};
+
+__device__ __forceinline__ void sincos_reduced(float theta, float& s, float& c) {
+    const float n = rintf(__fmul_rn(theta, 0.15915494309189535f));  // theta / 2pi
+    float r = __fmaf_rn(-n, 6.28318548202514648f, theta);           // 2pi = hi + lo
+    r = __fmaf_rn(-n, -1.74845553146951715e-7f, r);
+    s = __sinf(r);
+    c = __cosf(r);
+}
+
+constexpr int kRopeRowsPerWarp = 4;  // loads of four rows are in flight before the first is rotated
+
+template <int PPT>
+__global__ void __launch_bounds__(kThreads)
+    rope_kernel(const __half* __restrict__ x, const int* __restrict__ positions, __half* __restrict__ out,
+                size_t rows, const __grid_constant__ RopeTable table) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int head_dim = PPT * 64, R = kRopeRowsPerWarp;
+    const size_t row0 = ((size_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * R;
+    if (row0 >= rows) return;
+    const int lane = threadIdx.x & 31;
+    uint32_t w[R][PPT];
+    float pos[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (row0 + r >= rows) continue;  // uniform across the warp
+        pos[r] = (float)positions[row0 + r];
+        const uint32_t* xin = reinterpret_cast<const uint32_t*>(x + (row0 + r) * head_dim) + lane * PPT;
+        if constexpr (PPT == 4) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xin);
+            w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
+        } else if constexpr (PPT == 2) {
+            const uint2 v = *reinterpret_cast<const uint2*>(xin);
+            w[r][0] = v.x; w[r][1] = v.y;
+        } else {
+            w[r][0] = xin[0];
+        }
+    }
+    float inv_freq[PPT];
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) inv_freq[j] = table.inv_freq[lane * PPT + j];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (row0 + r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < PPT; ++j) {
+            const float theta = __fmul_rn(pos[r], inv_freq[j]);
+            float s, c;
+            sincos_reduced(theta, s, c);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[r][j]));
+            const float o0 = __fsub_rn(__fmul_rn(f.x, c), __fmul_rn(f.y, s));
+            const float o1 = __fadd_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, c));
+            w[r][j] = pack_f16x2(o0, o1);
+        }
+        uint32_t* xout = reinterpret_cast<uint32_t*>(out + (row0 + r) * head_dim) + lane * PPT;
+        if constexpr (PPT == 4) {
+            *reinterpret_cast<uint4*>(xout) = make_uint4(w[r][0], w[r][1], w[r][2], w[r][3]);
+        } else if constexpr (PPT == 2) {
+            *reinterpret_cast<uint2*>(xout) = make_uint2(w[r][0], w[r][1]);
+        } else {
+            xout[0] = w[r][0];
+        }
+    }
+}
+
 // ---- input generator --------------------------------------------------------------------
 __device__ __forceinline__ uint64_t splitmix64(uint64_t index, uint64_t seed) {
     uint64_t z = index * 0x9E3779B97F4A7C15ull + seed + 0x9E3779B97F4A7C15ull;
@@ -792,6 +869,33 @@ extern "C" int y_b200_rmsnorm_residual(const void* x_f16, const void* residual_f
     else if (nvec <= 4 * kThreads) e = launch_pdl(rmsnorm_residual_kernel<4>, grid, kThreads, 0, st, xh, rh, wh, hidden, eps, oh, nh);
     else e = launch_pdl(rmsnorm_residual_kernel<0>, grid, kThreads, 0, st, xh, rh, wh, hidden, eps, oh, nh);
     return check_cuda(e, "rmsnorm_residual_kernel launch");
+}
+
+extern "C" int y_b200_rope(const void* x_f16, const int32_t* positions, void* out_f16, size_t rows, int head_dim,
+                           float base, void* stream) {
+    if (!x_f16 || !positions || !out_f16) return fail(Y_B200_ERR_INVALID, "y_b200_rope: null pointer");
+    if (head_dim != 64 && head_dim != 128 && head_dim != 256)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_rope: head_dim=%d must be 64, 128 or 256", head_dim);
+    if (!(base > 1.0f)) return fail(Y_B200_ERR_INVALID, "y_b200_rope: base must be greater than 1");
+    if (!aligned16(x_f16) || !aligned16(out_f16) || (reinterpret_cast<uintptr_t>(positions) & 3u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_rope: x and out need 16-byte, positions 4-byte alignment");
+    if (rows == 0) return Y_B200_OK;
+    RopeTable table;
+    for (int i = 0; i < head_dim / 2; ++i)
+        table.inv_freq[i] = (float)pow((double)base, -2.0 * (double)i / (double)head_dim);
+    for (int i = head_dim / 2; i < kRopeMaxPairs; ++i) table.inv_freq[i] = 0.0f;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xh = static_cast<const __half*>(x_f16);
+    __half* oh = static_cast<__half*>(out_f16);
+    const size_t rows_per_cta = (size_t)(kThreads / 32) * kRopeRowsPerWarp;
+    const size_t ctas = (rows + rows_per_cta - 1) / rows_per_cta;
+    if (ctas > 0x7fffffffu) return fail(Y_B200_ERR_SHAPE, "y_b200_rope: too many rows");
+    const unsigned grid = (unsigned)ctas;
+    cudaError_t e;
+    if (head_dim == 256) e = launch_pdl(rope_kernel<4>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
+    else if (head_dim == 128) e = launch_pdl(rope_kernel<2>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
+    else e = launch_pdl(rope_kernel<1>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
+    return check_cuda(e, "rope_kernel launch");
 }
 
 extern "C" int y_b200_fill_random_f16(void* out_f16, size_t n, uint64_t index0, uint64_t seed,

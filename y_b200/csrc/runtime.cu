@@ -23,7 +23,7 @@ struct y_buf {
     int device;
 };
 
-enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode, RmsnormResidual };
+enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode, RmsnormResidual, Rope };
 
 struct y_kernel {
     Entry entry;
@@ -167,6 +167,20 @@ int launch_once(y_kernel* k, const unsigned grid[3], const unsigned block[3], un
             return y_b200_rmsnorm_residual(reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
                                            reinterpret_cast<const void*>(a[2].v.ptr), grid[0], (size_t)k->k, 1e-5f,
                                            reinterpret_cast<void*>(a[3].v.ptr), reinterpret_cast<void*>(a[4].v.ptr), nullptr);
+        }
+        case Entry::Rope: {
+            // (X, Positions, Out); the reference launches one 32-thread CTA per row
+            // (tests/benchmark_y_rmsnorm_rope.py:156), so the grid is the number of rows.
+            static const int kinds[3] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR};
+            int rc = expect_args(a, nargs, kinds, 3, "rope_<head_dim>");
+            if (rc) return rc;
+            if (!grid || grid[0] == 0 || grid[1] != 1 || grid[2] != 1)
+                return fail(Y_B200_ERR_INVALID, "rope_<head_dim>: the launch grid must be (rows, 1, 1)");
+            if (block && (block[0] != 32 || block[1] != 1 || block[2] != 1))
+                return fail(Y_B200_ERR_INVALID, "rope_<head_dim>: launch block (%u,%u,%u) differs from the entry's (32,1,1)",
+                            block[0], block[1], block[2]);
+            return y_b200_rope(reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const int32_t*>(a[1].v.ptr),
+                               reinterpret_cast<void*>(a[2].v.ptr), grid[0], k->k, 10000.0f, nullptr);
         }
     }
     return fail(Y_B200_ERR_UNSUPPORTED, "unknown kernel entry");
@@ -335,6 +349,19 @@ extern "C" y_kernel* y_ctx_load_module(y_ctx* ctx, const char* image, const char
             }
             k.entry = Entry::RmsnormResidual;
             k.k = (int)hidden;
+            y_kernel* res = static_cast<y_kernel*>(malloc(sizeof(y_kernel)));
+            if (!res) return nullptr;
+            *res = k;
+            return res;
+        }
+        if (fam == "rope") {
+            const long long head_dim = atoll(name.c_str() + strlen("rope_"));
+            if (name.rfind("rope_", 0) != 0 || (head_dim != 64 && head_dim != 128 && head_dim != 256)) {
+                fail(Y_B200_ERR_INVALID, "y_ctx_load_module: '%s' does not name a head size of 64, 128 or 256", entry);
+                return nullptr;
+            }
+            k.entry = Entry::Rope;
+            k.k = (int)head_dim;
             y_kernel* res = static_cast<y_kernel*>(malloc(sizeof(y_kernel)));
             if (!res) return nullptr;
             *res = k;

@@ -130,6 +130,20 @@ def fused_add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Ten
     return o, nr
 
 
+def rope(x: torch.Tensor, positions: torch.Tensor, base: float = 10000.0, out: torch.Tensor | None = None):
+    """Interleaved-pair rotary embedding. x [rows, head_dim] f16 (a row is one token's query
+    or key vector of one head), positions [rows] int32; `out` may be x itself."""
+    _dev(x, "x"), _dev(positions, "positions")
+    if x.dtype != torch.float16 or positions.dtype != torch.int32:
+        raise ValueError("rope takes f16 x and int32 positions")
+    rows, head_dim = x.shape
+    if positions.shape != (rows,):
+        raise ValueError("rope: one position per row")
+    o = out if out is not None else torch.empty_like(x)
+    check(lib.y_b200_rope(x.data_ptr(), positions.data_ptr(), o.data_ptr(), rows, head_dim, float(base), _stream()))
+    return o
+
+
 # ---- FP8 GEMM -----------------------------------------------------------------
 def _scale_fields(args: GemmFp8Args, name: str, s) -> None:
     if isinstance(s, torch.Tensor):
