@@ -225,6 +225,28 @@ Y_B200_API int y_b200_rmsnorm_residual(const void* x_f16, const void* residual_f
 Y_B200_API int y_b200_rope(const void* x_f16, const int32_t* positions, void* out_f16, size_t rows, int head_dim,
                            float base, void* stream);
 
+/* ---- paged decode attention --------------------------------------------------------
+ * Replaces paged_decode_attention_<head_dim>_<q_heads>_<kv_heads>_<page_size>[_<warps>]
+ * (src/ptx_emitter.rs:6267-6760; parameters Q, KCache, VCache, PageTable, SeqLens, Out,
+ * MaxPages): one new query token per (sequence, query head) over a page-indexed f16 KV
+ * cache, softmax(q . k / sqrt(head_dim)) v with f32 accumulation, query head h reading
+ * KV head h / (q_heads / kv_heads).
+ *   q, out     [num_seqs, num_q_heads, head_dim] f16
+ *   kcache, vcache [num_pages, page_size, num_kv_heads, head_dim] f16
+ *   page_table [num_seqs, max_pages] i32 (logical -> physical page), seq_lens [num_seqs] i32
+ * A sequence of length 0 gives zeros. head_dim is 64, 128 or 256; at most 16 query heads
+ * per KV head. The head counts, page size and head size are runtime values here.
+ * workspace: y_b200_paged_decode_attention_workspace_bytes(...) bytes, 256-byte aligned.
+ * It holds partial results when a sequence is cut across CTAs; whether the call does
+ * that depends on num_seqs and num_kv_heads alone (and the SM count), not on the data. */
+Y_B200_API size_t y_b200_paged_decode_attention_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
+                                                                int head_dim);
+Y_B200_API int y_b200_paged_decode_attention(const void* q_f16, const void* kcache_f16, const void* vcache_f16,
+                                             const int32_t* page_table, const int32_t* seq_lens, void* out_f16,
+                                             int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                             int page_size, int max_pages, void* workspace, size_t workspace_bytes,
+                                             void* stream);
+
 /* ---- input generator ---------------------------------------------------------
  * random_f16_bits (src/cuda_runtime.rs:657-682): element i = f(i + index0, seed),
  * a normal binary16 with exponent in 12..14. Written on the device. */

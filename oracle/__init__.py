@@ -86,6 +86,9 @@ _q16t = _sig("orc_quantize_fp8_f16_transpose", None, _u16p, C.c_size_t, C.c_size
 _rms = _sig("orc_rmsnorm_f16", C.c_float, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float, _f32p, _f32p)
 _rmsres = _sig("orc_rmsnorm_residual_f16", None, _u16p, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float, _u16p, _u16p)
 _rope = _sig("orc_rope_f16", None, _u16p, C.POINTER(C.c_int32), C.c_size_t, C.c_int, C.c_float, _u16p)
+_i32p = C.POINTER(C.c_int32)
+_attn = _sig("orc_paged_decode_attention", None, _u16p, _u16p, _u16p, _i32p, _i32p, C.c_int, C.c_int, C.c_int,
+             C.c_int, C.c_int, C.c_int, _u16p)
 _rmsq = _sig("orc_rmsnorm_quantize_fp8", None, _u16p, _u16p, C.c_size_t, C.c_size_t, C.c_float,
              _u8p, _f32p)
 _gemm8 = _sig("orc_gemm_fp8", None, _u8p, _u8p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float,
@@ -239,6 +242,20 @@ def rope_f16(x: np.ndarray, positions: np.ndarray, base: float = 10000.0) -> np.
     rows, head_dim = x.shape
     out = np.empty((rows, head_dim), np.uint16)
     _rope(_p(x, _u16p), positions.ctypes.data_as(C.POINTER(C.c_int32)), rows, head_dim, base, _p(out, _u16p))
+    return out
+
+
+def paged_decode_attention(q: np.ndarray, kcache: np.ndarray, vcache: np.ndarray, page_table: np.ndarray,
+                           seq_lens: np.ndarray) -> np.ndarray:
+    """q [S, Hq, D], caches [pages, page, Hkv, D] as f16 bit patterns; int32 page_table [S, max_pages],
+    seq_lens [S]. Returns out [S, Hq, D] f16 bit patterns."""
+    q, kcache, vcache = _c(q, np.uint16), _c(kcache, np.uint16), _c(vcache, np.uint16)
+    page_table, seq_lens = _c(page_table, np.int32), _c(seq_lens, np.int32)
+    s, hq, d = q.shape
+    _, page, hkv, _ = kcache.shape
+    out = np.empty((s, hq, d), np.uint16)
+    _attn(_p(q, _u16p), _p(kcache, _u16p), _p(vcache, _u16p), page_table.ctypes.data_as(_i32p),
+          seq_lens.ctypes.data_as(_i32p), s, hq, hkv, d, page, page_table.shape[1], _p(out, _u16p))
     return out
 
 

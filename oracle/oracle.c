@@ -418,6 +418,60 @@ void orc_rope_f16(const uint16_t* x, const int32_t* positions, size_t rows, int 
 }
 
 /* ------------------------------------------------------------------------
+ * Paged decode attention
+ *
+ * The definition the reference kernel implements and its benchmark checks against
+ * (src/ptx_emitter.rs:6303-6345, tests/benchmark_y_paged_decode_attention.py:159-185):
+ * for sequence s and query head h, with kv head h / (q_heads / kv_heads) and tokens
+ * t < seq_lens[s] found at KCache[PageTable[s][t / page], t % page, kv head, :]:
+ *   score_t = (q . k_t) / sqrt(head_dim);  p = softmax(score);  out = sum_t p_t v_t.
+ * Evaluated in double precision and rounded once to f16; length 0 gives zeros. The
+ * device kernel accumulates in f32 with online softmax and f16 probabilities, so the
+ * comparison is by tolerance.
+ * ---------------------------------------------------------------------- */
+void orc_paged_decode_attention(const uint16_t* q, const uint16_t* kcache, const uint16_t* vcache,
+                                const int32_t* page_table, const int32_t* seq_lens, int num_seqs,
+                                int num_q_heads, int num_kv_heads, int head_dim, int page_size,
+                                int max_pages, uint16_t* out) {
+    const int group = num_q_heads / num_kv_heads;
+    const double scale = 1.0 / sqrt((double)head_dim);
+#pragma omp parallel for collapse(2) schedule(dynamic)
+    for (int s = 0; s < num_seqs; ++s)
+        for (int h = 0; h < num_q_heads; ++h) {
+            const int len = seq_lens[s], kvh = h / group;
+            uint16_t* o = out + ((size_t)s * num_q_heads + h) * head_dim;
+            if (len <= 0) {
+                for (int d = 0; d < head_dim; ++d) o[d] = 0;
+                continue;
+            }
+            const uint16_t* qv = q + ((size_t)s * num_q_heads + h) * head_dim;
+            double* score = (double*)malloc((size_t)len * sizeof(double));
+            double* acc = (double*)calloc((size_t)head_dim, sizeof(double));
+            double mx = -1e300;
+            for (int t = 0; t < len; ++t) {
+                const size_t row = (((size_t)page_table[(size_t)s * max_pages + t / page_size] * page_size +
+                                     (size_t)(t % page_size)) * num_kv_heads + kvh) * head_dim;
+                double dot = 0.0;
+                for (int d = 0; d < head_dim; ++d)
+                    dot += (double)orc_f16_bits_to_f32(qv[d]) * (double)orc_f16_bits_to_f32(kcache[row + d]);
+                score[t] = dot * scale;
+                if (score[t] > mx) mx = score[t];
+            }
+            double denom = 0.0;
+            for (int t = 0; t < len; ++t) {
+                const size_t row = (((size_t)page_table[(size_t)s * max_pages + t / page_size] * page_size +
+                                     (size_t)(t % page_size)) * num_kv_heads + kvh) * head_dim;
+                const double pexp = exp(score[t] - mx);
+                denom += pexp;
+                for (int d = 0; d < head_dim; ++d) acc[d] += pexp * (double)orc_f16_bits_to_f32(vcache[row + d]);
+            }
+            for (int d = 0; d < head_dim; ++d) o[d] = orc_f32_to_f16_bits((float)(acc[d] / denom));
+            free(score);
+            free(acc);
+        }
+}
+
+/* ------------------------------------------------------------------------
  * GEMM + epilogues
  * ---------------------------------------------------------------------- */
 

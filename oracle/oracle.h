@@ -75,6 +75,10 @@ void  orc_rmsnorm_residual_f16(const uint16_t* x, const uint16_t* residual, cons
 void  orc_rope_inv_freq(int head_dim, float base, float* inv_freq);
 void  orc_rope_f16(const uint16_t* x, const int32_t* positions, size_t rows, int head_dim, float base,
                    uint16_t* out);
+void  orc_paged_decode_attention(const uint16_t* q, const uint16_t* kcache, const uint16_t* vcache,
+                                 const int32_t* page_table, const int32_t* seq_lens, int num_seqs,
+                                 int num_q_heads, int num_kv_heads, int head_dim, int page_size,
+                                 int max_pages, uint16_t* out);
 void  orc_rmsnorm_quantize_fp8(const uint16_t* x, const uint16_t* gamma,
                                size_t rows, size_t hidden, float eps,
                                uint8_t* q, float* scale_out);

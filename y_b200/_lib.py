@@ -87,6 +87,8 @@ SIGNATURES = {
     "y_b200_gemm_int4_decode": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "y_b200_rmsnorm_residual": (_i, [_vp, _vp, _vp, _sz, _sz, C.c_float, _vp, _vp, _vp]),
     "y_b200_rope": (_i, [_vp, _vp, _vp, _sz, _i, C.c_float, _vp]),
+    "y_b200_paged_decode_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "y_b200_paged_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "y_b200_fill_random_f16": (_i, [_vp, _sz, _u64, _u64, _vp]),
     "y_compile_to_ptx": (_vp, [C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
     "y_autotune_search_space_json": (_vp, [_u32, _u32, _u32, _i]),

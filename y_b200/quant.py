@@ -144,6 +144,30 @@ def rope(x: torch.Tensor, positions: torch.Tensor, base: float = 10000.0, out: t
     return o
 
 
+def paged_decode_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, page_table: torch.Tensor,
+                           seq_lens: torch.Tensor, out: torch.Tensor | None = None,
+                           workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode attention over a paged f16 KV cache. q [S, Hq, D]; kcache, vcache
+    [pages, page_size, Hkv, D]; page_table [S, max_pages] int32; seq_lens [S] int32."""
+    for t, name in ((q, "q"), (kcache, "kcache"), (vcache, "vcache"), (page_table, "page_table"), (seq_lens, "seq_lens")):
+        _dev(t, name)
+    if q.dtype != torch.float16 or kcache.dtype != torch.float16 or vcache.dtype != torch.float16:
+        raise ValueError("paged_decode_attention takes f16 q and caches")
+    if page_table.dtype != torch.int32 or seq_lens.dtype != torch.int32:
+        raise ValueError("paged_decode_attention takes int32 page_table and seq_lens")
+    s, hq, d = q.shape
+    _, page_size, hkv, d2 = kcache.shape
+    if d2 != d or vcache.shape != kcache.shape or page_table.shape[0] != s or seq_lens.shape != (s,):
+        raise ValueError("paged_decode_attention: inconsistent shapes")
+    o = out if out is not None else torch.empty_like(q)
+    need = lib.y_b200_paged_decode_attention_workspace_bytes(s, hq, hkv, d)
+    ws = workspace if workspace is not None else torch.empty(max(need, 256), dtype=torch.uint8, device=q.device)
+    check(lib.y_b200_paged_decode_attention(q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), page_table.data_ptr(),
+                                            seq_lens.data_ptr(), o.data_ptr(), s, hq, hkv, d, page_size,
+                                            page_table.shape[1], ws.data_ptr(), ws.numel(), _stream()))
+    return o
+
+
 # ---- FP8 GEMM -----------------------------------------------------------------
 def _scale_fields(args: GemmFp8Args, name: str, s) -> None:
     if isinstance(s, torch.Tensor):
