@@ -276,6 +276,24 @@ def other_config_metrics(peaks):
     us = timeit(lambda: q.rope(xr, pos, out=orope), iters=20)
     gbs = (4.0 * xr.numel() + 4.0 * pos.numel()) / us / 1e3
     out["rope_f16_8192x32x128"] = {"us": round(us, 2), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4)}
+    # paged decode attention, the reference fixture's heads (32 query, 8 KV, head 128, page 16),
+    # 64 sequences of 4096 tokens behind a shuffled page table: K and V are each read once
+    del xr, pos, orope
+    ns, L, hq, hkv, hd, ps = 64, 4096, 32, 8, 128, 16
+    pages = ns * (L // ps)
+    kc = torch.randn(pages, ps, hkv, hd, device="cuda", dtype=torch.float16)
+    vc = torch.randn(pages, ps, hkv, hd, device="cuda", dtype=torch.float16)
+    qv = torch.randn(ns, hq, hd, device="cuda", dtype=torch.float16)
+    pt = torch.randperm(pages, device="cuda").to(torch.int32).view(ns, L // ps)
+    sl = torch.full((ns,), L, dtype=torch.int32, device="cuda")
+    oa = torch.empty_like(qv)
+    aws = torch.empty(max(int(q.lib.y_b200_paged_decode_attention_workspace_bytes(ns, hq, hkv, hd)), 256),
+                      dtype=torch.uint8, device="cuda")
+    us = timeit(lambda: q.paged_decode_attention(qv, kc, vc, pt, sl, out=oa, workspace=aws), iters=20)
+    nbytes = 2.0 * ns * L * hkv * hd * 2
+    out["paged_decode_attention_64x4096_h32_kv8_d128_p16"] = {
+        "us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
+        "bytes": "K and V of every sequence once (1.07 GB)"}
     q.device_status()
     return out
 

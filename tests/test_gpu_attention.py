@@ -74,3 +74,29 @@ def test_repeat_launches_are_bit_identical_and_pages_really_are_looked_up(q):
     pt2 = inv[pt].astype(np.int32)
     again = q.paged_decode_attention(f16_dev(qv), f16_dev(kc2), f16_dev(vc2), torch.from_numpy(pt2).cuda(), sld)
     assert torch.equal(again, first)
+
+
+def test_through_the_launch_api_with_the_reference_fixture_name(q):
+    """compile -> load_module('paged_decode_attention_128_32_8_16') -> launch with the
+    reference's grid (num_q_heads, num_seqs, 1) and seven arguments."""
+    from y_b200 import runtime as rt
+    src = ("kernel paged_decode_attention_128_32_8_16(Q: GlobalMemory<F16>, KCache: GlobalMemory<F16>, "
+           "VCache: GlobalMemory<F16>, PageTable: GlobalMemory<I32>, SeqLens: GlobalMemory<I32>, "
+           "Out: GlobalMemory<F16>, MaxPages: I32) {}")
+    image = rt.compile_to_ptx(src)
+    assert "family=paged_decode_attention" in image
+    qv, kc, vc, pt, sl = _case(128, 32, 8, 16, [40, 1000, 7], 5)
+    qd, kd, vd = f16_dev(qv), f16_dev(kc), f16_dev(vc)
+    ptd, sld = torch.from_numpy(pt).cuda(), torch.from_numpy(sl).cuda()
+    out = torch.empty_like(qd)
+    ctx = rt.CudaContext.new()
+    kern = ctx.load_module(image, "paged_decode_attention_128_32_8_16")
+    ctx.launch(kern, (32, 3, 1), None, 0, [qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ptd.data_ptr(), sld.data_ptr(),
+                                           out.data_ptr(), ("i32", pt.shape[1])])
+    ctx.synchronize()
+    assert torch.equal(out, q.paged_decode_attention(qd, kd, vd, ptd, sld))
+    with pytest.raises(rt.YB200Error):  # the grid's x must be the number of query heads
+        ctx.launch(kern, (8, 3, 1), None, 0, [qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), ptd.data_ptr(),
+                                              sld.data_ptr(), out.data_ptr(), ("i32", pt.shape[1])])
+    kern.free()
+    ctx.close()

@@ -168,6 +168,11 @@ KernelFamily classify_kernel(const KernelDecl& k, std::string* err) {
         // rope_<head_dim>(X: F16, Positions: I32, Out: F16) (src/ptx_emitter.rs:6016-6044)
         if (k.params.size() == 3 && k.name.rfind("rope_", 0) == 0 && gm(0, "F16") && gm(1, "I32") && gm(2, "F16"))
             return KernelFamily::Rope;
+        // paged_decode_attention_<d>_<qh>_<kvh>_<page>[_<warps>](Q, KCache, VCache: F16; PageTable, SeqLens: I32;
+        // Out: F16; MaxPages: I32 scalar) (src/ptx_emitter.rs:6279-6300)
+        if (k.params.size() == 7 && k.name.rfind("paged_decode_attention_", 0) == 0 && gm(0, "F16") && gm(1, "F16") &&
+            gm(2, "F16") && gm(3, "I32") && gm(4, "I32") && gm(5, "F16") && scalar(6, "I32"))
+            return KernelFamily::PagedDecodeAttention;
         return KernelFamily::None;
     }
     const size_t np = k.params.size();
@@ -197,6 +202,7 @@ const char* family_name(KernelFamily f) {
         case KernelFamily::GemmF16Swiglu: return "gemm_f16_swiglu";
         case KernelFamily::RmsnormResidual: return "rmsnorm_residual";
         case KernelFamily::Rope: return "rope";
+        case KernelFamily::PagedDecodeAttention: return "paged_decode_attention";
         default: return "none";
     }
 }
@@ -235,6 +241,9 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         out += "// [Y RMSNORM] one 256-thread CTA per row; 128-bit loads; fixed-order reduction\n";
     } else if (fam == KernelFamily::Rope) {
         out += "// [Y FUSED ROPE] 1 warp (32 threads) per row | interleaved pairs, base=10000\n";
+    } else if (fam == KernelFamily::PagedDecodeAttention) {
+        out += "// [Y PAGED DECODE ATTENTION] launch grid (num_q_heads, num_seqs, 1) as the reference entry; the library "
+               "regroups the work per KV head and splits long sequences across CTAs itself\n";
     } else {
         const uint32_t cta_k = 64;
         snprintf(buf, sizeof buf,

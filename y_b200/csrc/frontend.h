@@ -21,7 +21,7 @@ struct KernelDecl {
     std::vector<ParamDecl> params;
 };
 
-enum class KernelFamily { None, Invalid, GemmFp8, GemmF16, GemmF16BiasRelu, GemmF16Swiglu, RmsnormResidual, Rope };
+enum class KernelFamily { None, Invalid, GemmFp8, GemmF16, GemmF16BiasRelu, GemmF16Swiglu, RmsnormResidual, Rope, PagedDecodeAttention };
 
 bool parse_kernels(const std::string& src, std::vector<KernelDecl>* out, std::string* err);
 KernelFamily classify_kernel(const KernelDecl& k, std::string* err);

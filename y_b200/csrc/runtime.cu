@@ -23,7 +23,7 @@ struct y_buf {
     int device;
 };
 
-enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode, RmsnormResidual, Rope };
+enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode, RmsnormResidual, Rope, PagedDecodeAttention };
 
 struct y_kernel {
     Entry entry;
@@ -32,6 +32,7 @@ struct y_kernel {
     size_t workspace_bytes;
     unsigned max_dyn_smem;
     int device;
+    int page_size;        // paged decode attention only
 };
 
 namespace yb {
@@ -181,6 +182,29 @@ int launch_once(y_kernel* k, const unsigned grid[3], const unsigned block[3], un
                             block[0], block[1], block[2]);
             return y_b200_rope(reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const int32_t*>(a[1].v.ptr),
                                reinterpret_cast<void*>(a[2].v.ptr), grid[0], k->k, 10000.0f, nullptr);
+        }
+        case Entry::PagedDecodeAttention: {
+            // (Q, KCache, VCache, PageTable, SeqLens, Out, MaxPages); the reference's grid is
+            // (num_q_heads, num_seqs, 1) (src/ptx_emitter.rs:6321-6323): the sequence count comes from it.
+            static const int kinds[7] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 7, "paged_decode_attention_<...>");
+            if (rc) return rc;
+            if (!grid || (int)grid[0] != k->m || grid[1] == 0 || grid[2] != 1)
+                return fail(Y_B200_ERR_INVALID, "paged_decode_attention: the launch grid must be (%d, num_seqs, 1)", k->m);
+            const int num_seqs = (int)grid[1];
+            const size_t need = y_b200_paged_decode_attention_workspace_bytes(num_seqs, k->m, k->n, k->k);
+            if (need > k->workspace_bytes) {  // grown on demand, owned by the kernel object
+                if (k->workspace) cudaFree(k->workspace);
+                k->workspace = nullptr;
+                k->workspace_bytes = 0;
+                if ((rc = check_cuda(cudaMalloc(&k->workspace, need), "cudaMalloc(attention workspace)"))) return rc;
+                k->workspace_bytes = need;
+            }
+            return y_b200_paged_decode_attention(
+                reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                reinterpret_cast<const void*>(a[2].v.ptr), reinterpret_cast<const int32_t*>(a[3].v.ptr),
+                reinterpret_cast<const int32_t*>(a[4].v.ptr), reinterpret_cast<void*>(a[5].v.ptr), num_seqs, k->m, k->n,
+                k->k, k->page_size, a[6].v.i32, k->workspace, k->workspace_bytes, nullptr);
         }
     }
     return fail(Y_B200_ERR_UNSUPPORTED, "unknown kernel entry");
@@ -349,6 +373,25 @@ extern "C" y_kernel* y_ctx_load_module(y_ctx* ctx, const char* image, const char
             }
             k.entry = Entry::RmsnormResidual;
             k.k = (int)hidden;
+            y_kernel* res = static_cast<y_kernel*>(malloc(sizeof(y_kernel)));
+            if (!res) return nullptr;
+            *res = k;
+            return res;
+        }
+        if (fam == "paged_decode_attention") {
+            // paged_decode_attention_<head_dim>_<q_heads>_<kv_heads>_<page_size>[_<warps>]
+            int dims[5] = {0, 0, 0, 0, 0};
+            const int got = sscanf(name.c_str(), "paged_decode_attention_%d_%d_%d_%d_%d", &dims[0], &dims[1], &dims[2],
+                                   &dims[3], &dims[4]);
+            if (got < 4 || (dims[0] != 64 && dims[0] != 128 && dims[0] != 256) || dims[1] < 1 || dims[2] < 1 ||
+                dims[1] % dims[2] != 0 || dims[1] / dims[2] > 16 || dims[3] < 1) {
+                fail(Y_B200_ERR_INVALID, "y_ctx_load_module: '%s' does not name head_dim (64/128/256), query heads, KV heads "
+                     "(dividing the query heads, at most 16 per KV head) and page size", entry);
+                return nullptr;
+            }
+            k.entry = Entry::PagedDecodeAttention;
+            k.k = dims[0]; k.m = dims[1]; k.n = dims[2];
+            k.page_size = dims[3];
             y_kernel* res = static_cast<y_kernel*>(malloc(sizeof(y_kernel)));
             if (!res) return nullptr;
             *res = k;
