@@ -5,6 +5,8 @@ capture (a few launches, a few hundred MB on the device, inputs larger than L2).
   python -m y_b200.profile_cases gemm   [--m ... --n ... --k ... --epilogue none|bias_relu|swiglu]
   python -m y_b200.profile_cases decode [--tokens 8] [--iters 48]
   python -m y_b200.profile_cases quantize [--m 8192 --k 8192]
+  python -m y_b200.profile_cases layer_ops [--m 8192 --k 8192]     fused add+RMSNorm, RoPE
+  python -m y_b200.profile_cases attention [--seqs 16 --seq-len 4096]
 """
 from __future__ import annotations
 
@@ -17,7 +19,9 @@ from . import quant as q
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["step", "gemm", "decode", "quantize"])
+    ap.add_argument("case", choices=["step", "gemm", "decode", "quantize", "layer_ops", "attention"])
+    ap.add_argument("--seqs", type=int, default=16)
+    ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -28,9 +32,27 @@ def main() -> None:
     a = ap.parse_args()
     torch.manual_seed(0)
     dev = "cuda"
-    if a.case in ("step", "gemm", "quantize"):
+    if a.case in ("step", "gemm", "quantize", "layer_ops"):
         x = torch.randn(a.m, a.k, device=dev, dtype=torch.float16)
-    if a.case == "quantize":
+    if a.case == "layer_ops":
+        r = torch.randn_like(x)
+        g = (torch.rand(a.k, device=dev) + 0.5).to(torch.float16)
+        heads = x.view(-1, 128)  # rows of one head each
+        pos = torch.randint(0, 4096, (heads.shape[0],), dtype=torch.int32, device=dev)
+        for _ in range(a.iters):
+            q.fused_add_rmsnorm(x, r, g, 1e-5)
+            q.rope(heads, pos)
+    elif a.case == "attention":
+        hq, hkv, hd, ps = 32, 8, 128, 16
+        pages = a.seqs * (a.seq_len // ps)
+        kc = torch.randn(pages, ps, hkv, hd, device=dev, dtype=torch.float16)
+        vc = torch.randn(pages, ps, hkv, hd, device=dev, dtype=torch.float16)
+        qv = torch.randn(a.seqs, hq, hd, device=dev, dtype=torch.float16)
+        pt = torch.randperm(pages, device=dev).to(torch.int32).view(a.seqs, a.seq_len // ps)
+        sl = torch.full((a.seqs,), a.seq_len, dtype=torch.int32, device=dev)
+        for _ in range(a.iters):
+            q.paged_decode_attention(qv, kc, vc, pt, sl)
+    elif a.case == "quantize":
         for _ in range(a.iters):
             q.quantize_fp8_dynamic(x)
             q.quantize_fp8_dynamic(x, transpose=True)
