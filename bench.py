@@ -179,7 +179,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over e4m3 (CPU)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": {"workload": WORKLOAD, "m": M, "k": K, "n_per_gpu": N_SHARD, "n_total": N_SHARD * max(args.gpus, 1),
+                   "parallelism": "host cores of rank 0 only", "sample": sample,
+                   "step": "rmsnorm_stats + rmsnorm_quantize_fp8 + gemm_fp8 (weights pre-quantised), oracle port"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
