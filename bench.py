@@ -454,7 +454,9 @@ def run_ours(args):
     clocks["e2e_region"] = clk.summary("e2e")
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
 
-    # ---- the exchange step, reported separately
+    # ---- the exchange step, reported separately: the same step followed by NCCL's all-gather,
+    # and the step whose GEMM epilogue stores its shard straight into every peer's gathered
+    # buffer over NVLink (no separate collective; a one-element all-reduce orders the ranks)
     gather = None
     if world > 1:
         def gather_step():
@@ -464,8 +466,33 @@ def run_ours(args):
         for _ in range(2):
             gather_step()
         g_ms = timed(gather_step, args.steps) / args.steps
-        gather = {"ms_per_step_with_gather": g_ms, "tflops_with_gather": flops_step / (g_ms * 1e-3) / 1e12,
+        gather = {"nccl": {"ms_per_step": g_ms, "tflops": flops_step / (g_ms * 1e-3) / 1e12},
                   "gathered_layout": "[rank, M, N_shard] bf16", "recv_bytes_per_gpu": (world - 1) * M * N_SHARD * 2}
+        fused, why = None, ""
+        try:
+            fused = colpar.GatheredOutput(M, N_SHARD)
+        except Exception as e:  # peer mapping refused (e.g. no IPC between the ranks' containers)
+            why = str(e)[:200]
+        ok = torch.tensor([1.0 if fused is not None else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() > 0:
+            def fused_step():
+                layer.forward(x, gathered=fused)
+                fused.barrier()
+
+            for _ in range(2):
+                fused_step()
+            f_ms = timed(fused_step, args.steps) / args.steps
+            same = torch.equal(fused.to_host(), gathered.cpu())  # against NCCL's result, every rank
+            agree = torch.tensor([1.0 if same else 0.0], device=dev)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+            gather["fused_epilogue_stores"] = {"ms_per_step": f_ms, "tflops": flops_step / (f_ms * 1e-3) / 1e12,
+                                               "equals_nccl_result_on_every_rank": bool(agree.item() > 0)}
+            fused.close()
+        else:
+            gather["fused_epilogue_stores"] = {"unavailable": why or "another rank could not map its peers"}
+            if fused is not None:
+                fused.close()
     q.device_status()
 
     line = None

@@ -95,6 +95,7 @@ Y_B200_API int y_b200_rmsnorm_quantize_fp8(const void* x_f16, const void* gamma_
  * EPI_SWIGLU: the N columns are gate|up interleaved (2j gate, 2j+1 up); c is
  * [M, N/2] bf16 and amax_out (device float, must be zeroed by the caller or
  * by y_b200_gemm_fp8_swiglu_requant) receives max|c|. */
+#define Y_B200_MAX_REPLICAS 7
 typedef struct y_b200_gemm_fp8_args {
     const void* a;
     const void* bt;
@@ -112,6 +113,14 @@ typedef struct y_b200_gemm_fp8_args {
     int max_ctas;      /* 0 = one persistent CTA per SM */
     int cta_m;         /* 0 = pick from the tile table; 128 = one CTA per tile; 256 = a pair of
                           CTAs (cluster of 2) shares each 256 x 256 tile (needs cta_n 0 or 256) */
+    /* Fused all-gather of the output: besides c, the epilogue stores every element to
+     * c_replicas[0 .. c_replica_count) at the same offset. The replicas are this rank's slot
+     * in the other GPUs' gathered buffers (peer memory opened with y_b200_peer_open; plain
+     * stores over NVLink, no multicast), so the transfer overlaps the GEMM tile by tile and
+     * no separate collective runs. The caller orders the ranks afterwards (a barrier on the
+     * stream) before anyone reads a gathered buffer. Not with EPI_SWIGLU. */
+    void* c_replicas[Y_B200_MAX_REPLICAS];
+    int c_replica_count;
 } y_b200_gemm_fp8_args;
 
 Y_B200_API int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* args, void* stream);
@@ -246,6 +255,21 @@ Y_B200_API int y_b200_paged_decode_attention(const void* q_f16, const void* kcac
                                              int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                                              int page_size, int max_pages, void* workspace, size_t workspace_bytes,
                                              void* stream);
+
+/* ---- peer memory for the fused all-gather ------------------------------------------
+ * One process per GPU. y_b200_peer_alloc gives device memory that other processes of the
+ * node can map: y_b200_peer_export writes an opaque 64-byte handle to send to them (any
+ * host channel), y_b200_peer_open maps a received handle and returns a device pointer
+ * valid in this process (stores to it travel over NVLink), y_b200_peer_close unmaps it.
+ * Free with y_b200_peer_free after every peer has closed its mapping. */
+#define Y_B200_PEER_HANDLE_BYTES 64
+Y_B200_API int y_b200_peer_alloc(size_t bytes, void** ptr);
+Y_B200_API int y_b200_peer_free(void* ptr);
+Y_B200_API int y_b200_peer_export(const void* ptr, unsigned char handle[Y_B200_PEER_HANDLE_BYTES]);
+Y_B200_API int y_b200_peer_open(const unsigned char handle[Y_B200_PEER_HANDLE_BYTES], void** peer_ptr);
+Y_B200_API int y_b200_peer_close(void* peer_ptr);
+/* Synchronous copy of a peer buffer (or any device memory) to the host, for checks. */
+Y_B200_API int y_b200_peer_read(void* host_dst, const void* device_src, size_t bytes);
 
 /* ---- input generator ---------------------------------------------------------
  * random_f16_bits (src/cuda_runtime.rs:657-682): element i = f(i + index0, seed),

@@ -71,10 +71,10 @@ def test_compile_returns_a_launch_descriptor_for_tile_kernels():
     assert "Dynamic shared memory required:" in text and "Launch grid required:" in text
     out = (C.c_uint32 * 4)()
     fake = "// [Y TENSOR CORE GEMM] M=1024 N=1024 K=1024 | CTA 64x128x32 | 2x2 warps | x\n" \
-           "// Dynamic shared memory required: 45568 bytes.\n"
+           "// Dynamic shared memory required: 61952 bytes.\n"
     # src/empirical_autotune.rs:1003-1019
     assert lib.y_parse_launch_config(fake.encode(), 1024, 1024, out) == 0
-    assert list(out) == [8, 16, 128, 45568]
+    assert list(out) == [8, 16, 128, 61952]
     # the synchronous fallback prints no byte count: 0 is the answer (:1021-1030)
     fake2 = "    // [Y TENSOR CORE GEMM] M=64 N=64 K=32 | CTA 32x32x32 | 2x1 warps | wmma\n"
     assert lib.y_parse_launch_config(fake2.encode(), 64, 64, out) == 0

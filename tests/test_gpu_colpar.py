@@ -50,3 +50,34 @@ def test_host_pipeline_equals_device_path_step_by_step(layer_and_inputs):
         q.device_status()
         for ch, w in zip(c_host, want):
             assert torch.equal(ch, w.cpu())
+
+
+def test_epilogue_replicas_receive_the_same_bits(layer_and_inputs):
+    """The fused all-gather's mechanism on one GPU: the replicas are local buffers here, peer
+    memory on a multi-GPU node; vector-store and ragged (scalar-store) shapes."""
+    layer, xs, g, bqt_h, sb, q = layer_and_inputs
+    for (m, n, k) in ((320, 384, 512), (100, 72, 128)):
+        aq = torch.randint(0, 0x78, (m, k), dtype=torch.uint8, device="cuda")
+        bq = torch.randint(0, 0x78, (n, k), dtype=torch.uint8, device="cuda")
+        for cta_m, dt in ((128, torch.bfloat16), (256, torch.bfloat16), (256, torch.float16), (128, torch.float32)):
+            want = q.gemm_fp8_codes(aq, bq, 0.5, 0.25, out_dtype=dt, cta_m=cta_m)
+            reps = [torch.zeros_like(want) for _ in range(7)]
+            got = q.gemm_fp8_codes(aq, bq, 0.5, 0.25, out_dtype=dt, cta_m=cta_m, replicas=reps)
+            q.device_status()
+            assert torch.equal(got, want)
+            for r in reps:
+                assert torch.equal(r, want)
+
+
+def test_gathered_output_on_one_rank(layer_and_inputs):
+    """World size 1: the gathered buffer has one slot, filled by the GEMM, read back through the library."""
+    from y_b200 import colpar
+    layer, xs, g, bqt_h, sb, q = layer_and_inputs
+    gathered = colpar.GatheredOutput(layer.m, layer.n_shard)
+    try:
+        want = layer.forward(f16_dev(xs[1]))
+        layer.forward(f16_dev(xs[1]), gathered=gathered)
+        gathered.barrier()
+        assert torch.equal(gathered.to_host()[0], want.cpu())
+    finally:
+        gathered.close()

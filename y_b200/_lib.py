@@ -36,6 +36,7 @@ class GemmFp8Args(C.Structure):
         ("epilogue", C.c_int), ("out_kind", C.c_int),
         ("amax_out", C.c_void_p),
         ("cta_n", C.c_int), ("max_ctas", C.c_int), ("cta_m", C.c_int),
+        ("c_replicas", C.c_void_p * 7), ("c_replica_count", C.c_int),
     ]
 
 
@@ -89,6 +90,12 @@ SIGNATURES = {
     "y_b200_rope": (_i, [_vp, _vp, _vp, _sz, _i, C.c_float, _vp]),
     "y_b200_paged_decode_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "y_b200_paged_decode_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "y_b200_peer_alloc": (_i, [_sz, C.POINTER(_vp)]),
+    "y_b200_peer_free": (_i, [_vp]),
+    "y_b200_peer_export": (_i, [_vp, C.c_char_p]),
+    "y_b200_peer_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
+    "y_b200_peer_close": (_i, [_vp]),
+    "y_b200_peer_read": (_i, [_vp, _vp, _sz]),
     "y_b200_fill_random_f16": (_i, [_vp, _sz, _u64, _u64, _vp]),
     "y_compile_to_ptx": (_vp, [C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
     "y_autotune_search_space_json": (_vp, [_u32, _u32, _u32, _i]),

@@ -56,6 +56,84 @@ def assemble(gathered: torch.Tensor) -> torch.Tensor:
     return gathered.permute(1, 0, 2).reshape(m, world * n_s)
 
 
+class _RawOut:
+    """A device address with a shape and dtype, accepted where the operator layer takes `out`."""
+
+    def __init__(self, ptr: int, shape, dtype, device):
+        self._ptr, self.shape, self.dtype, self.device = ptr, tuple(shape), dtype, device
+
+    def data_ptr(self) -> int:
+        return self._ptr
+
+
+class GatheredOutput:
+    """The gathered output [world, M, N_s] of a column-parallel GEMM, filled by the GEMM's own
+    epilogue instead of a collective: every rank allocates the whole buffer in memory its
+    peers can map (CUDA IPC through the library), and each rank's GEMM stores its shard into
+    slot `rank` of every rank's buffer with plain NVLink stores. `barrier()` orders the ranks
+    on the current stream; after it every rank may read its `tensor_bytes()`.
+    """
+
+    def __init__(self, m: int, n_shard: int, dtype=torch.bfloat16, group=None):
+        import ctypes as C
+
+        from ._lib import check, lib
+
+        self._lib, self._check, self._C = lib, check, C
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.m, self.n_shard, self.dtype = m, n_shard, dtype
+        self.slot_bytes = m * n_shard * torch.empty((), dtype=dtype).element_size()
+        base = C.c_void_p()
+        check(lib.y_b200_peer_alloc(self.slot_bytes * self.world, C.byref(base)))
+        self.base = base.value
+        handle = C.create_string_buffer(64)
+        check(lib.y_b200_peer_export(self.base, handle))
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, handle.raw, group=group)
+        self.peer_bases = {}
+        for r, h in enumerate(handles):
+            if r == self.rank or h is None:
+                continue
+            ptr = C.c_void_p()
+            check(lib.y_b200_peer_open(h, C.byref(ptr)))
+            self.peer_bases[r] = ptr.value
+        self._token = torch.zeros(1, device="cuda")
+
+    def local_slot(self) -> int:
+        """Device address of this rank's slot in its own buffer (the GEMM's `c`)."""
+        return self.base + self.rank * self.slot_bytes
+
+    def replica_slots(self) -> list[int]:
+        """Device addresses of this rank's slot in every peer's buffer (the GEMM's replicas)."""
+        return [b + self.rank * self.slot_bytes for _, b in sorted(self.peer_bases.items())]
+
+    def barrier(self) -> None:
+        if self.world > 1:
+            dist.all_reduce(self._token, group=self.group)  # stream-ordered on every rank
+
+    def to_host(self) -> torch.Tensor:
+        """Copy of the whole gathered buffer as a CPU tensor [world, M, N_s] (for checks)."""
+        out = torch.empty((self.world, self.m, self.n_shard), dtype=self.dtype)
+        torch.cuda.synchronize()
+        self._check(self._lib.y_b200_peer_read(out.data_ptr(), self.base, self.slot_bytes * self.world))
+        return out
+
+    def close(self) -> None:
+        """Unmap the peers' buffers, wait for every rank to have done so, then free this one."""
+        for b in self.peer_bases.values():
+            self._check(self._lib.y_b200_peer_close(b))
+        self.peer_bases = {}
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        if self.base:
+            self._check(self._lib.y_b200_peer_free(self.base))
+            self.base = 0
+
+
 class ColumnParallelFp8Linear:
     """One rank's shard of `C = rmsnorm(X; gamma, eps) -> e4m3, then FP8 GEMM with the
     pre-quantised weight shard -> bf16`, with a device path and a pipelined host path.
@@ -92,10 +170,17 @@ class ColumnParallelFp8Linear:
         self._streams = None
         self._count = 0
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, slot: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, slot: int = 0,
+                gathered: "GatheredOutput | None" = None) -> torch.Tensor:
+        """With `gathered`, the GEMM's epilogue also stores the shard into this rank's slot on
+        every peer (call `gathered.barrier()` before reading); `out` is then ignored."""
         q = self._q
         aq, sa = q.rmsnorm_quantize_fp8(x, self.gamma, self.eps, workspace=self._ws[slot], out=self._aq[slot])
-        return q.gemm_fp8_codes(aq, self.bqt, sa, self.scale_b, out_dtype=torch.bfloat16, out=out)
+        if gathered is None:
+            return q.gemm_fp8_codes(aq, self.bqt, sa, self.scale_b, out_dtype=torch.bfloat16, out=out)
+        return q.gemm_fp8_codes(aq, self.bqt, sa, self.scale_b, out_dtype=torch.bfloat16,
+                                out=_RawOut(gathered.local_slot(), (self.m, self.n_shard), torch.bfloat16, x.device),
+                                replicas=gathered.replica_slots())
 
     def _host_state(self):
         if self._streams is None:

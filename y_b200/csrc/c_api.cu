@@ -225,7 +225,7 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         const long long grid = ctas < cap ? ctas : cap;
         // Per CTA and stage: 128 rows of A, and of B either the whole N tile or half of the pair's.
         const unsigned b_rows = pair ? 128u : c.cta_n;
-        const unsigned smem = c.num_stages * (128u * 128u + b_rows * 128u) + (2 * c.num_stages + 4) * 8 + 16 + 4096 + 1024;
+        const unsigned smem = c.num_stages * (128u * 128u + b_rows * 128u) + (2 * c.num_stages + 4) * 8 + 16 + 4096 + 8 * 2048 + 1024;
         snprintf(buf, sizeof buf,
                  "// [Y FP8 TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %ux%ux%u | %ux%u warps | "
                  "tcgen05.mma.cta_group::%d.kind::f8f6f4 e4m3 x e4m3 -> f32 (TMEM)\n"

@@ -98,3 +98,44 @@ extern "C" int y_b200_device_status(void* stream) {
                 "device wait ran out: code %u at role/barrier 0x%x, CTA %u, detail %u", h.code,
                 h.where, h.block, h.extra);
 }
+
+// ---- peer memory (CUDA IPC) -----------------------------------------------------------------
+static_assert(sizeof(cudaIpcMemHandle_t) == Y_B200_PEER_HANDLE_BYTES, "the exported handle is a cudaIpcMemHandle_t");
+
+extern "C" int y_b200_peer_alloc(size_t bytes, void** ptr) {
+    if (!ptr || bytes == 0) return yb::fail(Y_B200_ERR_INVALID, "y_b200_peer_alloc: null output or zero size");
+    *ptr = nullptr;
+    return yb::check_cuda(cudaMalloc(ptr, bytes), "cudaMalloc(peer buffer)");
+}
+
+extern "C" int y_b200_peer_free(void* ptr) {
+    if (!ptr) return 0;
+    return yb::check_cuda(cudaFree(ptr), "cudaFree(peer buffer)");
+}
+
+extern "C" int y_b200_peer_export(const void* ptr, unsigned char handle[Y_B200_PEER_HANDLE_BYTES]) {
+    if (!ptr || !handle) return yb::fail(Y_B200_ERR_INVALID, "y_b200_peer_export: null argument");
+    cudaIpcMemHandle_t h;
+    int rc = yb::check_cuda(cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)), "cudaIpcGetMemHandle");
+    if (rc) return rc;
+    memcpy(handle, &h, sizeof h);
+    return 0;
+}
+
+extern "C" int y_b200_peer_open(const unsigned char handle[Y_B200_PEER_HANDLE_BYTES], void** peer_ptr) {
+    if (!handle || !peer_ptr) return yb::fail(Y_B200_ERR_INVALID, "y_b200_peer_open: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    *peer_ptr = nullptr;
+    return yb::check_cuda(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+}
+
+extern "C" int y_b200_peer_close(void* peer_ptr) {
+    if (!peer_ptr) return 0;
+    return yb::check_cuda(cudaIpcCloseMemHandle(peer_ptr), "cudaIpcCloseMemHandle");
+}
+
+extern "C" int y_b200_peer_read(void* host_dst, const void* device_src, size_t bytes) {
+    if (!host_dst || !device_src) return yb::fail(Y_B200_ERR_INVALID, "y_b200_peer_read: null pointer");
+    return yb::check_cuda(cudaMemcpy(host_dst, device_src, bytes, cudaMemcpyDeviceToHost), "cudaMemcpy(device to host)");
+}

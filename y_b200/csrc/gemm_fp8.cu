@@ -45,6 +45,11 @@ constexpr int kUmmaK = 32;  // K per tcgen05.mma for 8-bit operands
 constexpr int kGemmThreads = 320;
 constexpr int kEpiWarps = 8;
 constexpr int kBiasBytes = kEpiWarps * 128 * 4;  // per epilogue warp: its column half's bias as f32
+// Per epilogue warp: 32 rows x 32 columns of packed output, re-read row-contiguously for the
+// stores to peer memory (a lane's own 16-byte stores land in 32 different rows; over NVLink
+// that is 32 quarter-filled transactions, the staged form writes whole 64- or 128-byte runs).
+constexpr int kRepStageBytes = 32 * 32 * 2;  // 16-bit outputs; f32 outputs store to the peers directly
+constexpr int kEpiSmemBytes = kBiasBytes + kEpiWarps * kRepStageBytes;
 constexpr int kSwizzleGroup = 8;  // M-tiles per raster group
 
 struct GemmParams {
@@ -58,6 +63,8 @@ struct GemmParams {
     unsigned int* amax_out;
     DeviceStatus* status;
     int m_tiles, n_tiles;
+    void* c_rep[Y_B200_MAX_REPLICAS];  // further destinations of every output element (peer memory)
+    int n_rep;
 };
 
 template <int BN>
@@ -67,7 +74,7 @@ struct GemmCfg {
     static constexpr int stage_bytes = a_bytes + b_bytes;
     static constexpr int stages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
     static constexpr int tmem_cols = 2 * BN;  // 128, 256 or 512: powers of two >= 32
-    static constexpr int bar_bytes = (2 * stages + 4) * 8 + 16 + kBiasBytes;
+    static constexpr int bar_bytes = (2 * stages + 4) * 8 + 16 + kEpiSmemBytes;
     // +1024 so the ring can be aligned to the swizzle-atom size at run time.
     static constexpr int smem_bytes = stages * stage_bytes + bar_bytes + 1024;
 };
@@ -156,7 +163,7 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* bias_s, i
 template <int BN, int EPI, int OUT>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_addr, int row, int col_base,
                                                   float scale, bool rows_aligned, int n_out,
-                                                  const float* bias_s, uint32_t& amax_bits) {
+                                                  const float* bias_s, uint8_t* rep_stage, uint32_t& amax_bits) {
     constexpr int esize = OUT == Y_B200_F32 ? 4 : 2;
 #pragma unroll 1
     for (int ch = 0; ch < BN / 64; ++ch) {
@@ -210,12 +217,37 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
             }
         } else if (row < p.m) {
             if (rows_aligned && col0 + 32 <= p.n) {
-                store_vec<OUT, 32>(static_cast<char*>(p.c) + ((size_t)row * p.n + col0) * esize, v);
+                const size_t off = ((size_t)row * p.n + col0) * esize;
+                store_vec<OUT, 32>(static_cast<char*>(p.c) + off, v);
+                if (esize == 4)
+                    for (int d = 0; d < p.n_rep; ++d) store_vec<OUT, 32>(static_cast<char*>(p.c_rep[d]) + off, v);
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
-                    if (col0 + j < p.n) store_scalar<OUT>(p.c, (size_t)row * p.n + col0 + j, v[j]);
+                    if (col0 + j < p.n) {
+                        store_scalar<OUT>(p.c, (size_t)row * p.n + col0 + j, v[j]);
+                        for (int d = 0; d < p.n_rep; ++d) store_scalar<OUT>(p.c_rep[d], (size_t)row * p.n + col0 + j, v[j]);
+                    }
             }
+        }
+        // Fused all-gather, full 32-column chunks: the warp's 32 x 32 block goes through shared
+        // memory so that each store instruction covers whole rows' runs (uniform branch).
+        if (EPI != Y_B200_EPI_SWIGLU && esize == 2 && p.n_rep > 0 && rows_aligned && col0 + 32 <= p.n) {
+            constexpr int row_bytes = 32 * esize, units = row_bytes / 16;  // 16-byte units per row
+            const int lane = threadIdx.x & 31;
+            store_vec<OUT, 32>(rep_stage + lane * row_bytes, v);
+            __syncwarp();
+            const int row_base = row - lane;
+#pragma unroll
+            for (int it = 0; it < units; ++it) {
+                const int u = it * 32 + lane, r = u / units, cu = u % units;
+                const uint4 val = *reinterpret_cast<const uint4*>(rep_stage + r * row_bytes + cu * 16);
+                if (row_base + r < p.m) {
+                    const size_t off = ((size_t)(row_base + r) * p.n + col0) * esize + (size_t)cu * 16;
+                    for (int d = 0; d < p.n_rep; ++d) *reinterpret_cast<uint4*>(static_cast<char*>(p.c_rep[d]) + off) = val;
+                }
+            }
+            __syncwarp();
         }
     }
 }
@@ -338,6 +370,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int quarter = warp & 3;  // TMEM lanes this warp may touch
         const int half = (warp - 2) >> 2;  // column half of the tile this warp drains
         float* bias_s = bias_all + (warp - 2) * 128;
+        uint8_t* rep_stage = reinterpret_cast<uint8_t*>(bias_all) + kBiasBytes + (warp - 2) * kRepStageBytes;
         const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
                             (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
         constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
@@ -362,7 +395,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tc_fence_after();
             const int row = tm * kCtaM + quarter * 32 + lane;
             const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + half * (BN / 2);
-            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, amax_bits);
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, rep_stage, amax_bits);
             // The warp's TMEM reads are complete (wait::ld above): hand its part of the
             // accumulator buffer back to the MMA warp.
             tc_fence_before();
@@ -396,7 +429,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 // issues; completion is signalled to both CTAs' barriers. No load is shared between CTAs.
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kCtaM * kCtaK;  // 16 KB of A + 16 KB of B per CTA
-constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16 + kBiasBytes;
+constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16 + kEpiSmemBytes;
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairBarBytes + 1024;
 
 template <int EPI, int OUT>
@@ -513,6 +546,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
         float* bias_s = bias_all + (warp - 2) * 128;
+        uint8_t* rep_stage = reinterpret_cast<uint8_t*>(bias_all) + kBiasBytes + (warp - 2) * kRepStageBytes;
         const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
                             (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
         constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
@@ -538,7 +572,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             tc_fence_after();
             const int row = tm * 256 + (int)rank * kCtaM + quarter * 32 + lane;
             const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + half * (BN / 2);
-            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, amax_bits);
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, rep_stage, amax_bits);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * as);
@@ -724,6 +758,16 @@ int validate(const y_b200_gemm_fp8_args* a) {
         return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: cta_m must be 0, 128 or 256");
     if (a->cta_m == 256 && a->cta_n != 0 && a->cta_n != 256)
         return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: cta_m 256 (CTA pair) needs cta_n 0 or 256");
+    if (a->c_replica_count < 0 || a->c_replica_count > Y_B200_MAX_REPLICAS)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: c_replica_count must be 0..%d", Y_B200_MAX_REPLICAS);
+    if (a->c_replica_count > 0 && a->epilogue == Y_B200_EPI_SWIGLU)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: output replicas are not available with the SwiGLU epilogue");
+    for (int d = 0; d < a->c_replica_count; ++d) {
+        if (!a->c_replicas[d]) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: null output replica %d", d);
+        // the vector-store path is chosen from c's alignment: the replicas must not be less aligned
+        if ((reinterpret_cast<uintptr_t>(a->c_replicas[d]) & 15u) != (reinterpret_cast<uintptr_t>(a->c) & 15u))
+            return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_fp8: output replica %d must have the 16-byte alignment of c", d);
+    }
     return 0;
 }
 
@@ -781,6 +825,8 @@ extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
     p.bias = a->bias; p.bias_kind = a->bias_kind;
     p.amax_out = reinterpret_cast<unsigned int*>(a->amax_out);
     p.status = device_status_ptr();
+    p.n_rep = a->c_replica_count;
+    for (int d = 0; d < p.n_rep; ++d) p.c_rep[d] = a->c_replicas[d];
     return launch_tiled(a->a, a->bt, p, tile, a->epilogue, a->out_kind, a->max_ctas, st);
 }
 

@@ -191,7 +191,7 @@ def gemm_fp8_launch_info(m: int, n: int, k: int, cta_n: int = 0) -> LaunchInfo:
 def gemm_fp8_codes(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b, *, bias=None,
                    epilogue: int = EPI_NONE, out_dtype=torch.float32, out: torch.Tensor | None = None,
                    amax_out: torch.Tensor | None = None, cta_n: int = 0, max_ctas: int = 0,
-                   cta_m: int = 0):
+                   cta_m: int = 0, replicas=()):
     """C = epilogue((sa*sb) * aq @ bqt^T). aq [M, K], bqt [N, K] e4m3 codes
     (uint8 or float8_e4m3fn). Scales are floats or 1-element f32 device tensors.
     cta_m / cta_n force a tile (cta_m 256 = the CTA-pair kernel); 0 asks the tile table."""
@@ -213,6 +213,10 @@ def gemm_fp8_codes(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b, *, bia
     args.epilogue, args.out_kind = epilogue, out_kind
     args.amax_out = amax_out.data_ptr() if amax_out is not None else None
     args.cta_n, args.max_ctas, args.cta_m = cta_n, max_ctas, cta_m
+    # replicas: device addresses (ints) or tensors laid out like c; every output element is also stored there
+    args.c_replica_count = len(replicas)
+    for i, r in enumerate(replicas):
+        args.c_replicas[i] = r.data_ptr() if isinstance(r, torch.Tensor) else int(r)
     check(lib.y_b200_gemm_fp8(C.byref(args), _stream()))
     return c
 
