@@ -143,3 +143,24 @@ def test_context_creation_never_aborts_without_a_device():
     if torch.cuda.is_available():
         pytest.skip("a device is present")
     assert runtime.CudaContext.new() is None  # src/cuda_runtime.rs:330-364
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/tests"), reason="the reference checkout is not on this machine")
+def test_the_references_own_kernel_fixtures_compile_to_the_right_family():
+    """Every .ysu kernel fixture of the reference goes through y_compile_to_ptx verbatim and
+    lands in the family its name says (a CPU-side check: the GPU box has no reference tree)."""
+    import glob
+    expect = (("gemm_fp8_", "gemm_fp8"), ("gemm_f16_bias_relu_", "gemm_f16_bias_relu"),
+              ("gemm_f16_swiglu_", "gemm_f16_swiglu"), ("gemm_f16_", "gemm_f16"),
+              ("rmsnorm_residual_", "rmsnorm_residual"), ("rope_", "rope"),
+              ("paged_decode_attention_", "paged_decode_attention"))
+    seen = 0
+    for path in sorted(glob.glob("/root/reference/tests/*.ysu")):
+        stem = os.path.basename(path)[:-4]
+        fam = next((f for prefix, f in expect if stem.startswith(prefix)), None)
+        if fam is None:
+            continue
+        image = runtime.compile_to_ptx(open(path).read())
+        assert f" family={fam} " in image and "entry=" + stem.rsplit("_", 1)[0] in image, stem
+        seen += 1
+    assert seen >= 30
