@@ -56,7 +56,7 @@ def test_epilogue_replicas_receive_the_same_bits(layer_and_inputs):
     """The fused all-gather's mechanism on one GPU: the replicas are local buffers here, peer
     memory on a multi-GPU node; vector-store and ragged (scalar-store) shapes."""
     layer, xs, g, bqt_h, sb, q = layer_and_inputs
-    for (m, n, k) in ((320, 384, 512), (100, 72, 128)):
+    for (m, n, k) in ((320, 384, 512), (100, 72, 128), (320, 96, 256), (257, 160, 128), (512, 8192, 128)):
         aq = torch.randint(0, 0x78, (m, k), dtype=torch.uint8, device="cuda")
         bq = torch.randint(0, 0x78, (n, k), dtype=torch.uint8, device="cuda")
         for cta_m, dt in ((128, torch.bfloat16), (256, torch.bfloat16), (256, torch.float16), (128, torch.float32)):

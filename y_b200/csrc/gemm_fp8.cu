@@ -50,6 +50,10 @@ constexpr int kBiasBytes = kEpiWarps * 128 * 4;  // per epilogue warp: its colum
 // that is 32 quarter-filled transactions, the staged form writes whole 64- or 128-byte runs).
 constexpr int kRepStageBytes = 32 * 32 * 2;  // 16-bit outputs; f32 outputs store to the peers directly
 constexpr int kEpiSmemBytes = kBiasBytes + kEpiWarps * kRepStageBytes;
+// The CTA-pair kernel gives up one ring stage when it has replicas to write and stages two
+// chunks per flush instead, so that every store instruction to peer memory writes whole
+// 128-byte lines (64-byte runs reached 0.43 TB/s of NVLink egress with seven peers).
+constexpr int kRepStageBytesWide = 2 * kRepStageBytes;
 constexpr int kSwizzleGroup = 8;  // M-tiles per raster group
 
 struct GemmParams {
@@ -65,6 +69,8 @@ struct GemmParams {
     int m_tiles, n_tiles;
     void* c_rep[Y_B200_MAX_REPLICAS];  // further destinations of every output element (peer memory)
     int n_rep;
+    int stages;      // CTA-pair kernel: ring stages of this launch (one fewer when replicas are staged wide)
+    int rep_chunks;  // 32-column chunks staged per replica flush: 1 (64-byte runs) or 2 (128-byte runs)
 };
 
 template <int BN>
@@ -230,24 +236,33 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
                     }
             }
         }
-        // Fused all-gather, full 32-column chunks: the warp's 32 x 32 block goes through shared
-        // memory so that each store instruction covers whole rows' runs (uniform branch).
+        // Fused all-gather, full 32-column chunks: the warp's 32-row block goes through shared
+        // memory so that each store instruction covers whole rows' runs (uniform branches).
         if (EPI != Y_B200_EPI_SWIGLU && esize == 2 && p.n_rep > 0 && rows_aligned && col0 + 32 <= p.n) {
-            constexpr int row_bytes = 32 * esize, units = row_bytes / 16;  // 16-byte units per row
             const int lane = threadIdx.x & 31;
-            store_vec<OUT, 32>(rep_stage + lane * row_bytes, v);
-            __syncwarp();
-            const int row_base = row - lane;
-#pragma unroll
-            for (int it = 0; it < units; ++it) {
-                const int u = it * 32 + lane, r = u / units, cu = u % units;
-                const uint4 val = *reinterpret_cast<const uint4*>(rep_stage + r * row_bytes + cu * 16);
-                if (row_base + r < p.m) {
-                    const size_t off = ((size_t)(row_base + r) * p.n + col0) * esize + (size_t)cu * 16;
-                    for (int d = 0; d < p.n_rep; ++d) *reinterpret_cast<uint4*>(static_cast<char*>(p.c_rep[d]) + off) = val;
+            const int wide = p.rep_chunks == 2;
+            const int stride = wide ? 128 : 64;               // staged bytes per row
+            const int slot = wide ? (ch & 1) : 0;              // which half of the row this chunk fills
+            store_vec<OUT, 32>(rep_stage + lane * stride + slot * 64, v);
+            // flush when the row is full, or when no further full chunk will come to fill it
+            const bool flush = !wide || slot == 1 || ch + 1 == BN / 64 || col0 + 64 > p.n;
+            if (flush) {
+                __syncwarp();
+                const int run = 64 * (slot + 1);               // bytes per row in this flush
+                const int units = run / 16;
+                const int first_col = col0 - 32 * slot;
+                const int row_base = row - lane;
+                for (int u = lane; u < 32 * units; u += 32) {
+                    const int r = u / units, cu = u % units;
+                    const uint4 val = *reinterpret_cast<const uint4*>(rep_stage + r * stride + cu * 16);
+                    if (row_base + r < p.m) {
+                        const size_t off = ((size_t)(row_base + r) * p.n + first_col) * esize + (size_t)cu * 16;
+                        for (int d = 0; d < p.n_rep; ++d)
+                            *reinterpret_cast<uint4*>(static_cast<char*>(p.c_rep[d]) + off) = val;
+                    }
                 }
+                __syncwarp();
             }
-            __syncwarp();
         }
     }
 }
@@ -431,6 +446,12 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kCtaM * kCtaK;  // 16 KB of A + 16 KB of B per CTA
 constexpr int kPairBarBytes = (2 * kPairStages + 4) * 8 + 16 + kEpiSmemBytes;
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kPairBarBytes + 1024;
+constexpr int pair_smem_bytes(int stages, bool wide_replicas) {
+    return stages * kPairStageBytes + (2 * stages + 4) * 8 + 16 + kBiasBytes +
+           kEpiWarps * (wide_replicas ? kRepStageBytesWide : kRepStageBytes) + 1024;
+}
+static_assert(pair_smem_bytes(kPairStages, false) == kPairSmemBytes, "layout of the default launch");
+static_assert(pair_smem_bytes(kPairStages - 1, true) <= kPairSmemBytes, "the wide-replica launch fits the same opt-in");
 
 template <int EPI, int OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
@@ -441,12 +462,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t ring0 = (raw_addr + 1023u) & ~1023u;
     uint8_t* ring_ptr = smem_raw + (ring0 - raw_addr);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + kPairStages * kPairStageBytes);
+    const int stages = p.stages;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + stages * kPairStageBytes);
     const uint32_t full0 = smem_u32(bars);
-    const uint32_t empty0 = full0 + 8 * kPairStages;
-    const uint32_t tfull0 = empty0 + 8 * kPairStages;
+    const uint32_t empty0 = full0 + 8 * stages;
+    const uint32_t tfull0 = empty0 + 8 * stages;
     const uint32_t tempty0 = tfull0 + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kPairStages + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * stages + 4);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     float* bias_all = reinterpret_cast<float*>(tmem_slot + 4);
 
@@ -458,7 +480,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPairStages; ++s) {
+        for (int s = 0; s < stages; ++s) {
             mbar_init(full0 + 8 * s, 1);   // the even CTA's producer arrives; bytes come from both CTAs
             mbar_init(empty0 + 8 * s, 1);  // one commit per use
         }
@@ -501,7 +523,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     tma_load_2d_pair(dst, &tmap_a, full0 + 8 * stage, kb * kCtaK, tm * 256 + (int)rank * kCtaM);
                     tma_load_2d_pair(dst + kCtaM * kCtaK, &tmap_b, full0 + 8 * stage, kb * kCtaK,
                                      tn * BN + (int)rank * 128);
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -536,7 +558,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         umma_f8f6f4_pair(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
                                          b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc, (uint32_t)((kb | k) != 0));
                     tc_commit_pair(empty0 + 8 * stage, 3);  // both CTAs' stages are free again
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
                 }
                 if (ok) tc_commit_pair(tfull0 + 8 * as, 3);  // accumulator complete in both CTAs
             }
@@ -546,7 +568,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
         float* bias_s = bias_all + (warp - 2) * 128;
-        uint8_t* rep_stage = reinterpret_cast<uint8_t*>(bias_all) + kBiasBytes + (warp - 2) * kRepStageBytes;
+        uint8_t* rep_stage = reinterpret_cast<uint8_t*>(bias_all) + kBiasBytes +
+                             (warp - 2) * (p.rep_chunks == 2 ? kRepStageBytesWide : kRepStageBytes);
         const float scale = (p.scale_a_dev ? p.scale_a_dev[0] : p.scale_a) *
                             (p.scale_b_dev ? p.scale_b_dev[0] : p.scale_b);
         constexpr int out_div = EPI == Y_B200_EPI_SWIGLU ? 2 : 1;
@@ -707,7 +730,8 @@ int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPara
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
         configured[dev] = true;
     }
-    return check_cuda(launch_pdl(gemm_fp8_pair_kernel<EPI, OUT>, grid, kGemmThreads, kPairSmemBytes, st, ta, tb, p),
+    const int smem = pair_smem_bytes(p.stages, p.rep_chunks == 2);
+    return check_cuda(launch_pdl(gemm_fp8_pair_kernel<EPI, OUT>, grid, kGemmThreads, smem, st, ta, tb, p),
                       "gemm_fp8_pair_kernel launch");
 }
 
@@ -786,7 +810,13 @@ int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, in
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles > 0x3fffffffLL) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: too many tiles");
     int cap = max_ctas > 0 ? max_ctas : sm_count();
+    p.stages = kPairStages;
+    p.rep_chunks = 1;
     if (tile.cta_m == 256) {
+        if (p.n_rep > 0 && out_kind != Y_B200_F32) {  // wide replica staging, one ring stage fewer
+            p.stages = kPairStages - 1;
+            p.rep_chunks = 2;
+        }
         cap &= ~1;
         if (cap < 2) cap = 2;
         const int grid = (int)(2 * tiles < cap ? 2 * tiles : cap);
