@@ -96,8 +96,19 @@ __global__ void __launch_bounds__(kThreads) amax_kernel(const void* __restrict__
     pdl_wait();
     const size_t n8 = n / 8;
     float m = 0.0f;
-    for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n8;
-         v += (size_t)gridDim.x * kThreads) {
+    // four independent vectors per trip, so a thread has 64 bytes (128 for f32) in flight
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    for (; v + 3 * stride < n8; v += 4 * stride) {
+        float f[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) Elem<KIND>::load8(x, (v + u * stride) * 8, f[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(f[u][j]));
+    }
+    for (; v < n8; v += stride) {
         float f[8];
         Elem<KIND>::load8(x, v * 8, f);
 #pragma unroll
@@ -558,9 +569,7 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 // ---- rotary position embedding (interleaved pairs), f16 in and out ---------------------------
-// A warp takes four consecutive rows (a row is one token's query or key vector of one
-// head); in each, lane L owns the contiguous pairs [L * PPT, (L + 1) * PPT), so a warp
-// reads and writes contiguous spans.
+// A row is one token's query or key vector of one head.
 // inv_freq comes in as a kernel parameter (the host computes base^(-2i/head_dim) in double
 // precision once per call), theta = f32(pos) * inv_freq[i], and sin/cos are taken after a
 // two-term Cody-Waite reduction to [-pi, pi] so the fast units stay accurate at positions
@@ -578,59 +587,60 @@ __device__ __forceinline__ void sincos_reduced(float theta, float& s, float& c) 
     c = __cosf(r);
 }
 
-constexpr int kRopeRowsPerWarp = 4;  // loads of four rows are in flight before the first is rotated
+// A warp works on spans of 128 consecutive pairs (512 bytes: one row of head 256, two of
+// head 128, four of head 64), lane L on the four pairs [4L, 4L + 3] of the span, so every
+// load and store is 16 bytes whatever the head size. Four spans are loaded before the first
+// is rotated, which keeps 64 bytes per lane in flight.
+constexpr int kRopeSpansPerWarp = 4;
 
-template <int PPT>
+template <int HEAD_DIM>
 __global__ void __launch_bounds__(kThreads)
     rope_kernel(const __half* __restrict__ x, const int* __restrict__ positions, __half* __restrict__ out,
                 size_t rows, const __grid_constant__ RopeTable table) {
     pdl_wait();
     pdl_launch_dependents();
-    constexpr int head_dim = PPT * 64, R = kRopeRowsPerWarp;
-    const size_t row0 = ((size_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * R;
-    if (row0 >= rows) return;
+    constexpr int pairs_per_row = HEAD_DIM / 2, rows_per_span = 128 / pairs_per_row, S = kRopeSpansPerWarp;
+    // The table goes to shared memory once per CTA: lanes index it differently, and a
+    // constant-bank load with 16 distinct addresses per warp is replayed 16 times (the
+    // MIO-throttle stalls ncu showed at head 128).
+    __shared__ __align__(16) float s_inv[kRopeMaxPairs];
+    if (threadIdx.x < pairs_per_row) s_inv[threadIdx.x] = table.inv_freq[threadIdx.x];
+    __syncthreads();
+    const size_t spans = (rows + rows_per_span - 1) / rows_per_span;
+    const size_t span0 = ((size_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5)) * S;
+    if (span0 >= spans) return;
     const int lane = threadIdx.x & 31;
-    uint32_t w[R][PPT];
-    float pos[R];
+    const int row_in_span = (lane * 4) / pairs_per_row, pair0 = (lane * 4) % pairs_per_row;
+    uint4 w[S];
+    float pos[S];
+    bool live[S];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        if (row0 + r >= rows) continue;  // uniform across the warp
-        pos[r] = (float)positions[row0 + r];
-        const uint32_t* xin = reinterpret_cast<const uint32_t*>(x + (row0 + r) * head_dim) + lane * PPT;
-        if constexpr (PPT == 4) {
-            const uint4 v = *reinterpret_cast<const uint4*>(xin);
-            w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
-        } else if constexpr (PPT == 2) {
-            const uint2 v = *reinterpret_cast<const uint2*>(xin);
-            w[r][0] = v.x; w[r][1] = v.y;
-        } else {
-            w[r][0] = xin[0];
+    for (int s = 0; s < S; ++s) {
+        const size_t row = (span0 + s) * rows_per_span + row_in_span;
+        live[s] = row < rows;
+        if (live[s]) {
+            pos[s] = (float)positions[row];
+            w[s] = *reinterpret_cast<const uint4*>(x + row * HEAD_DIM + pair0 * 2);
         }
     }
-    float inv_freq[PPT];
+    const float4 fr = *reinterpret_cast<const float4*>(s_inv + pair0);
+    const float inv_freq[4] = {fr.x, fr.y, fr.z, fr.w};
 #pragma unroll
-    for (int j = 0; j < PPT; ++j) inv_freq[j] = table.inv_freq[lane * PPT + j];
+    for (int s = 0; s < S; ++s) {
+        if (!live[s]) continue;
+        uint32_t v[4] = {w[s].x, w[s].y, w[s].z, w[s].w};
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        if (row0 + r >= rows) continue;
-#pragma unroll
-        for (int j = 0; j < PPT; ++j) {
-            const float theta = __fmul_rn(pos[r], inv_freq[j]);
-            float s, c;
-            sincos_reduced(theta, s, c);
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[r][j]));
-            const float o0 = __fsub_rn(__fmul_rn(f.x, c), __fmul_rn(f.y, s));
-            const float o1 = __fadd_rn(__fmul_rn(f.x, s), __fmul_rn(f.y, c));
-            w[r][j] = pack_f16x2(o0, o1);
+        for (int j = 0; j < 4; ++j) {
+            const float theta = __fmul_rn(pos[s], inv_freq[j]);
+            float sn, cs;
+            sincos_reduced(theta, sn, cs);
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v[j]));
+            const float o0 = __fsub_rn(__fmul_rn(f.x, cs), __fmul_rn(f.y, sn));
+            const float o1 = __fadd_rn(__fmul_rn(f.x, sn), __fmul_rn(f.y, cs));
+            v[j] = pack_f16x2(o0, o1);
         }
-        uint32_t* xout = reinterpret_cast<uint32_t*>(out + (row0 + r) * head_dim) + lane * PPT;
-        if constexpr (PPT == 4) {
-            *reinterpret_cast<uint4*>(xout) = make_uint4(w[r][0], w[r][1], w[r][2], w[r][3]);
-        } else if constexpr (PPT == 2) {
-            *reinterpret_cast<uint2*>(xout) = make_uint2(w[r][0], w[r][1]);
-        } else {
-            xout[0] = w[r][0];
-        }
+        const size_t row = (span0 + s) * rows_per_span + row_in_span;
+        *reinterpret_cast<uint4*>(out + row * HEAD_DIM + pair0 * 2) = make_uint4(v[0], v[1], v[2], v[3]);
     }
 }
 
@@ -887,14 +897,16 @@ extern "C" int y_b200_rope(const void* x_f16, const int32_t* positions, void* ou
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __half* xh = static_cast<const __half*>(x_f16);
     __half* oh = static_cast<__half*>(out_f16);
-    const size_t rows_per_cta = (size_t)(kThreads / 32) * kRopeRowsPerWarp;
-    const size_t ctas = (rows + rows_per_cta - 1) / rows_per_cta;
+    const size_t rows_per_span = 128 / (size_t)(head_dim / 2);
+    const size_t spans = (rows + rows_per_span - 1) / rows_per_span;
+    const size_t spans_per_cta = (size_t)(kThreads / 32) * kRopeSpansPerWarp;
+    const size_t ctas = (spans + spans_per_cta - 1) / spans_per_cta;
     if (ctas > 0x7fffffffu) return fail(Y_B200_ERR_SHAPE, "y_b200_rope: too many rows");
     const unsigned grid = (unsigned)ctas;
     cudaError_t e;
-    if (head_dim == 256) e = launch_pdl(rope_kernel<4>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
-    else if (head_dim == 128) e = launch_pdl(rope_kernel<2>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
-    else e = launch_pdl(rope_kernel<1>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
+    if (head_dim == 256) e = launch_pdl(rope_kernel<256>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
+    else if (head_dim == 128) e = launch_pdl(rope_kernel<128>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
+    else e = launch_pdl(rope_kernel<64>, grid, kThreads, 0, st, xh, positions, oh, rows, table);
     return check_cuda(e, "rope_kernel launch");
 }
 
