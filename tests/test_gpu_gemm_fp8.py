@@ -46,6 +46,8 @@ def test_exact_integer_gemm(q, m, n, k, cta_n):
     (256, 256, 128), (256, 256, 512), (512, 768, 512),       # whole 256 x 256 tiles
     (300, 500, 384), (513, 257, 256), (17, 9, 64), (130, 130, 192), (200, 72, 80),  # ragged, K tail
     (2048, 2304, 1024), (4864, 4864, 256),                   # several tiles per CTA pair; 19 x 19 tiles
+    # 80, 75 and 90 tiles on 74 pairs: the last wave is cut into 256 x 128 half tiles
+    (2048, 2560, 256), (3840, 1280, 128), (2088, 2536, 192),
 ])
 def test_exact_integer_gemm_cta_pair(q, m, n, k):
     """The cta_group::2 kernel: two CTAs of a cluster share each 256 x 256 tile."""
@@ -97,7 +99,7 @@ def test_scale_epilogue_and_output_types(q, m, n, k, out):
         assert_gemm_close(to_f64(got, kind), to_f64(ref, kind), out)
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (130, 72, 192)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (130, 72, 192), (2048, 2560, 128)])
 @pytest.mark.parametrize("bias_dtype", ["f16", "f32"])
 @pytest.mark.parametrize("cta_m", [128, 256])
 def test_bias_relu_epilogue(q, m, n, k, bias_dtype, cta_m):
@@ -119,7 +121,7 @@ def test_bias_relu_epilogue(q, m, n, k, bias_dtype, cta_m):
             assert got.min() >= 0.0
 
 
-@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (100, 88, 128)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (100, 88, 128), (2048, 2560, 128)])
 @pytest.mark.parametrize("cta_m", [128, 256])
 def test_swiglu_requant(q, m, n, k, cta_m):
     a, b, sa, sb, aq, bqt = quantised_operands(m, n, k)

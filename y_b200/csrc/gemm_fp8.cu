@@ -69,6 +69,8 @@ struct GemmParams {
     int m_tiles, n_tiles;
     void* c_rep[Y_B200_MAX_REPLICAS];  // further destinations of every output element (peer memory)
     int n_rep;
+    int full_units;  // CTA-pair kernel: work units below this index are whole 256 x 256 tiles, the rest half tiles
+    int units;       // CTA-pair kernel: number of work units (see pair_unit)
     int stages;      // CTA-pair kernel: ring stages of this launch (one fewer when replicas are staged wide)
     int rep_chunks;  // 32-column chunks staged per replica flush: 1 (64-byte runs) or 2 (128-byte runs)
 };
@@ -149,9 +151,10 @@ __device__ __forceinline__ void store_vec(void* dst, const float* v) {
 // memory as f32 (zero beyond N). Only the warp itself reads the slice, so a warp-level
 // sync on either side is all the ordering it needs.
 template <int BN>
-__device__ __forceinline__ void stage_bias(const GemmParams& p, float* bias_s, int col_base, int lane) {
+__device__ __forceinline__ void stage_bias(const GemmParams& p, float* bias_s, int col_base, int lane,
+                                           int count = BN / 2) {
     __syncwarp();  // the previous tile's reads are done
-    for (int i = lane; i < BN / 2; i += 32) {
+    for (int i = lane; i < count; i += 32) {
         const int col = col_base + i;
         float b = 0.0f;
         if (col < p.n)
@@ -169,10 +172,11 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* bias_s, i
 template <int BN, int EPI, int OUT>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t t_addr, int row, int col_base,
                                                   float scale, bool rows_aligned, int n_out,
-                                                  const float* bias_s, uint8_t* rep_stage, uint32_t& amax_bits) {
+                                                  const float* bias_s, uint8_t* rep_stage, uint32_t& amax_bits,
+                                                  int nchunks = BN / 64) {
     constexpr int esize = OUT == Y_B200_F32 ? 4 : 2;
 #pragma unroll 1
-    for (int ch = 0; ch < BN / 64; ++ch) {
+    for (int ch = 0; ch < nchunks; ++ch) {
         const int col0 = col_base + ch * 32;
         if (col0 >= p.n) break;  // uniform across the warp
         uint32_t r[32];
@@ -245,7 +249,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
             const int slot = wide ? (ch & 1) : 0;              // which half of the row this chunk fills
             store_vec<OUT, 32>(rep_stage + lane * stride + slot * 64, v);
             // flush when the row is full, or when no further full chunk will come to fill it
-            const bool flush = !wide || slot == 1 || ch + 1 == BN / 64 || col0 + 64 > p.n;
+            const bool flush = !wide || slot == 1 || ch + 1 == nchunks || col0 + 64 > p.n;
             if (flush) {
                 __syncwarp();
                 const int run = 64 * (slot + 1);               // bytes per row in this flush
@@ -453,10 +457,27 @@ constexpr int pair_smem_bytes(int stages, bool wide_replicas) {
 static_assert(pair_smem_bytes(kPairStages, false) == kPairSmemBytes, "layout of the default launch");
 static_assert(pair_smem_bytes(kPairStages - 1, true) <= kPairSmemBytes, "the wide-replica launch fits the same opt-in");
 
+// Work units of the CTA-pair kernel. A launch whose last wave would leave more than half of
+// the pairs idle cuts the tiles of that wave into 256 x 128 halves, one unit each, so the
+// wave takes half as long with twice as many pairs busy (4096^3 on 74 pairs: 3 full waves
+// and 34 tiles become 3 waves and 68 half tiles). Units below p.full_units are whole tiles.
+__device__ __forceinline__ void pair_unit(const GemmParams& p, int u, int& tm, int& tn, int& bn, int& col0) {
+    int tile = u, half = 0;
+    bn = 256;
+    if (u >= p.full_units) {
+        tile = p.full_units + ((u - p.full_units) >> 1);
+        half = (u - p.full_units) & 1;
+        bn = 128;
+    }
+    tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+    col0 = tn * 256 + half * 128;
+}
+
 template <int EPI, int OUT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                         const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_b_half, const GemmParams p) {
     constexpr int BN = 256;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -475,7 +496,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
-    const int num_tiles = p.m_tiles * p.n_tiles;  // tiles of 256 x 256
+    const int num_units = p.units;
     const int num_kb = (p.k + kCtaK - 1) / kCtaK;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
@@ -492,6 +513,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         mbar_fence_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_b_half);
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(tmem_slot), 512);
@@ -509,9 +531,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (elect_one()) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-                int tm, tn;
-                tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+            for (int u = pair; u < num_units && ok; u += num_pairs) {
+                int tm, tn, bn, col0;
+                pair_unit(p, u, tm, tn, bn, col0);
+                const uint32_t b_bytes = (uint32_t)(bn / 2) * kCtaK;  // this CTA's half of the B tile
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) {
                         report_timeout(p.status, abort_flag, 0x10u, (unsigned)kb);
@@ -519,10 +542,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         break;
                     }
                     const uint32_t dst = ring0 + stage * kPairStageBytes;
-                    if (leader) mbar_expect_tx(full0 + 8 * stage, 2 * kPairStageBytes);
+                    if (leader) mbar_expect_tx(full0 + 8 * stage, 2 * (kCtaM * kCtaK + b_bytes));
                     tma_load_2d_pair(dst, &tmap_a, full0 + 8 * stage, kb * kCtaK, tm * 256 + (int)rank * kCtaM);
-                    tma_load_2d_pair(dst + kCtaM * kCtaK, &tmap_b, full0 + 8 * stage, kb * kCtaK,
-                                     tn * BN + (int)rank * 128);
+                    tma_load_2d_pair(dst + kCtaM * kCtaK, bn == 256 ? &tmap_b : &tmap_b_half, full0 + 8 * stage,
+                                     kb * kCtaK, col0 + (int)rank * (bn / 2));
                     if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -530,11 +553,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     } else if (warp == 1) {
         // ------------------------------ MMA issuer (even CTA only) ------------------
         if (leader && elect_one()) {
-            constexpr uint32_t idesc = make_idesc(256, BN, 0u, 0u);
+            constexpr uint32_t idesc_full = make_idesc(256, 256, 0u, 0u), idesc_half = make_idesc(256, 128, 0u, 0u);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int it = 0;
-            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+            for (int u = pair; u < num_units && ok; u += num_pairs, ++it) {
+                const uint32_t idesc = u < p.full_units ? idesc_full : idesc_half;
                 const uint32_t as = it & 1, aphase = (it >> 1) & 1;
                 if (!mbar_wait(tempty0 + 8 * as, aphase ^ 1u, abort_flag)) {
                     report_timeout(p.status, abort_flag, 0x20u, (unsigned)it);
@@ -581,12 +605,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         uint32_t amax_bits = 0;
         bool dead = false;
         int it = 0;
-        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
-            int tm, tn;
-            tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+        for (int u = pair; u < num_units; u += num_pairs, ++it) {
+            int tm, tn, bn, col0;
+            pair_unit(p, u, tm, tn, bn, col0);
             const uint32_t as = it & 1, aphase = (it >> 1) & 1;
-            const int col_base = tn * BN + half * (BN / 2);
-            if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane);
+            const int col_base = col0 + half * (bn / 2);
+            if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane, bn / 2);
             if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
                 report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
                 dead = true;
@@ -594,8 +618,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             if (dead) break;
             tc_fence_after();
             const int row = tm * 256 + (int)rank * kCtaM + quarter * 32 + lane;
-            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + half * (BN / 2);
-            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, rep_stage, amax_bits);
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + as * BN + half * (bn / 2);
+            drain_accumulator<BN, EPI, OUT>(p, t_addr, row, col_base, scale, rows_aligned, n_out, bias_s, rep_stage,
+                                            amax_bits, bn / 64);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * as);
@@ -720,8 +745,8 @@ int launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
 }
 
 template <int EPI, int OUT>
-int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                    cudaStream_t st) {
+int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh, const GemmParams& p,
+                    int grid, cudaStream_t st) {
     static bool configured[64] = {};
     int dev = 0;
     YB_CUDA(cudaGetDevice(&dev));
@@ -731,31 +756,31 @@ int launch_pair_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPara
         configured[dev] = true;
     }
     const int smem = pair_smem_bytes(p.stages, p.rep_chunks == 2);
-    return check_cuda(launch_pdl(gemm_fp8_pair_kernel<EPI, OUT>, grid, kGemmThreads, smem, st, ta, tb, p),
+    return check_cuda(launch_pdl(gemm_fp8_pair_kernel<EPI, OUT>, grid, kGemmThreads, smem, st, ta, tb, tbh, p),
                       "gemm_fp8_pair_kernel launch");
 }
 
 template <int EPI>
-int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int out_kind,
-                    int grid, cudaStream_t st) {
+int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh, const GemmParams& p,
+                    int out_kind, int grid, cudaStream_t st) {
     switch (out_kind) {
-        case Y_B200_F32: return launch_pair_one<EPI, Y_B200_F32>(ta, tb, p, grid, st);
-        case Y_B200_F16: return launch_pair_one<EPI, Y_B200_F16>(ta, tb, p, grid, st);
-        case Y_B200_BF16: return launch_pair_one<EPI, Y_B200_BF16>(ta, tb, p, grid, st);
+        case Y_B200_F32: return launch_pair_one<EPI, Y_B200_F32>(ta, tb, tbh, p, grid, st);
+        case Y_B200_F16: return launch_pair_one<EPI, Y_B200_F16>(ta, tb, tbh, p, grid, st);
+        case Y_B200_BF16: return launch_pair_one<EPI, Y_B200_BF16>(ta, tb, tbh, p, grid, st);
     }
     return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad out_kind %d", out_kind);
 }
 
-int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int epi, int out_kind,
-                int grid, cudaStream_t st) {
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tbh, const GemmParams& p, int epi,
+                int out_kind, int grid, cudaStream_t st) {
     switch (epi) {
-        case Y_B200_EPI_NONE: return launch_pair_out<Y_B200_EPI_NONE>(ta, tb, p, out_kind, grid, st);
-        case Y_B200_EPI_BIAS: return launch_pair_out<Y_B200_EPI_BIAS>(ta, tb, p, out_kind, grid, st);
-        case Y_B200_EPI_BIAS_RELU: return launch_pair_out<Y_B200_EPI_BIAS_RELU>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_NONE: return launch_pair_out<Y_B200_EPI_NONE>(ta, tb, tbh, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS: return launch_pair_out<Y_B200_EPI_BIAS>(ta, tb, tbh, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_RELU: return launch_pair_out<Y_B200_EPI_BIAS_RELU>(ta, tb, tbh, p, out_kind, grid, st);
         case Y_B200_EPI_SWIGLU:
             if (out_kind != Y_B200_BF16)
                 return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: the SwiGLU epilogue writes bf16");
-            return launch_pair_one<Y_B200_EPI_SWIGLU, Y_B200_BF16>(ta, tb, p, grid, st);
+            return launch_pair_one<Y_B200_EPI_SWIGLU, Y_B200_BF16>(ta, tb, tbh, p, grid, st);
     }
     return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad epilogue %d", epi);
 }
@@ -795,6 +820,17 @@ int validate(const y_b200_gemm_fp8_args* a) {
     return 0;
 }
 
+// Work units of a CTA-pair launch on `pairs` pairs (see pair_unit in the kernel): when the
+// last wave would fill at most half of the pairs, its tiles become two half tiles each.
+struct PairUnits {
+    int full_units, units;
+};
+PairUnits pair_units(long long tiles, int pairs) {
+    const long long rem = tiles % pairs;
+    if (tiles > pairs && rem > 0 && 2 * rem <= pairs) return {(int)(tiles - rem), (int)(tiles + rem)};
+    return {(int)tiles, (int)tiles};
+}
+
 // Builds the tensor maps for `tile`, sizes the persistent grid and launches.
 // `p` arrives with everything but m_tiles / n_tiles filled in.
 int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, int epi, int out_kind,
@@ -819,8 +855,13 @@ int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, in
         }
         cap &= ~1;
         if (cap < 2) cap = 2;
-        const int grid = (int)(2 * tiles < cap ? 2 * tiles : cap);
-        return launch_pair(ta, tb, p, epi, out_kind, grid, st);
+        const PairUnits pu = pair_units(tiles, cap / 2);
+        p.full_units = pu.full_units;
+        p.units = pu.units;
+        CUtensorMap tbh;  // 64-row B boxes for half tiles
+        if ((rc = make_operand_map(&tbh, bt, p.n, p.k, 64))) return rc;
+        const int grid = (int)(2LL * p.units < cap ? 2LL * p.units : cap);
+        return launch_pair(ta, tb, tbh, p, epi, out_kind, grid, st);
     }
     const int grid = (int)(tiles < cap ? tiles : cap);
     switch (tile.cta_n) {
@@ -870,8 +911,8 @@ extern "C" int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b20
     const long long tiles = (long long)((m + tile.cta_m - 1) / tile.cta_m) * ((n + tile.cta_n - 1) / tile.cta_n);
     const int sms = sm_count();
     const bool pair = tile.cta_m == 256;
-    const long long ctas = pair ? 2 * tiles : tiles;
     const int cap = pair ? (sms & ~1) : sms;
+    const long long ctas = pair ? 2LL * pair_units(tiles, cap / 2).units : tiles;
     out->grid[0] = (unsigned)(ctas < cap ? ctas : cap);
     out->grid[1] = out->grid[2] = 1;
     out->block[0] = kGemmThreads;
