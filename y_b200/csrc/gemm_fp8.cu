@@ -21,6 +21,15 @@
 // expects. Out-of-range rows and K are zero-filled by TMA, so any M, N >= 1 and
 // any K % 16 == 0 work; the epilogue masks the ragged edge. No multicast.
 //
+// Two kernels share the roles above. gemm_fp8_kernel<CTA_N>: one CTA per 128 x CTA_N
+// tile (M <= 128, or forced). gemm_fp8_pair_kernel (the default for M > 128): a cluster
+// of two CTAs per 256 x 256 tile on tcgen05.mma.cta_group::2, each CTA holding half of
+// both operands and half of the accumulator rows; see the comment above it.
+//
+// The output can also be stored to up to seven further buffers laid out like C (the
+// caller's slots in its peers' gathered buffers, mapped peer memory): the fused
+// all-gather of a column-parallel GEMM. Those stores are plain st.global.
+//
 // Every mbarrier wait is bounded; a wait that runs out raises the device
 // status word and the CTA unwinds through the common teardown.
 #include <cuda.h>
