@@ -1,0 +1,127 @@
+"""Pure-integer models of the kernels' address arithmetic (no GPU): each restates an index
+formula of a kernel source file and checks the property the kernel relies on, the way the
+reference checks its grid swizzle and ldmatrix bank mapping with integer models
+(src/ptx_emitter.rs:7449-7513, 8265-8365)."""
+import itertools
+
+import pytest
+
+
+def _banks(byte_addr: int, nbytes: int):
+    return [((byte_addr + 4 * i) // 4) % 32 for i in range(nbytes // 4)]
+
+
+@pytest.mark.parametrize("head_dim", [64, 128, 256])
+def test_attention_staging_swizzle_is_conflict_free_for_ldmatrix(head_dim):
+    """attention.cu: K/V rows of head_dim f16 sit row_bytes apart; the 16-byte chunk c of row r
+    is stored at chunk c ^ (r & 7). Every 8x8 block one ldmatrix phase reads (8 consecutive
+    rows, one logical chunk) must touch each of the 32 banks exactly once, for K (plain) and
+    V (transposed) alike, and the mapping must be a permutation of the row's chunks."""
+    row_bytes, chunks = head_dim * 2, head_dim // 8
+    for r in range(16):
+        assert sorted(c ^ (r & 7) for c in range(chunks)) == list(range(chunks))
+    for r0 in (0, 8):
+        for c in range(chunks):
+            hit = []
+            for r in range(r0, r0 + 8):
+                hit += _banks(r * row_bytes + ((c ^ (r & 7)) * 16), 16)
+            assert sorted(hit) == list(range(32))
+
+
+def test_transposed_quantise_tile_swizzle():
+    """quantize.cu: thread t = 8*rq + cv (rq 0..31, cv 0..7) stores, for j in 0..7, the word
+    of column cv*8+j at word index rq ^ (cv*4) of that column's 32-word row; a warp's 32
+    stores of one j must hit 32 different banks. The write-out reads 16-byte groups
+    (rv ^ (c // 8)) * 4 of row c: together they must return every row quad once."""
+    for warp in range(8):
+        for j in range(8):
+            banks = set()
+            for lane in range(32):
+                t = warp * 32 + lane
+                rq, cv = t // 8, t % 8
+                word = (cv * 8 + j) * 32 + (rq ^ (cv * 4))
+                banks.add(word % 32)
+            assert len(banks) == 32
+    for c in range(64):
+        cv = c // 8
+        stored = {rq: rq ^ (cv * 4) for rq in range(32)}           # row quad -> word index
+        read_back = {}
+        for rv in range(8):
+            g = (rv ^ cv) * 4
+            for i in range(4):
+                read_back[g + i] = rv * 4 + i                       # word index -> row quad it is taken for
+        assert all(read_back[w] == rq for rq, w in stored.items())
+
+
+@pytest.mark.parametrize("head_dim", [64, 128, 256])
+def test_rope_span_mapping_covers_every_pair_once(head_dim):
+    """quantize.cu rope_kernel: a warp works on a span of 128 pairs; lane L takes pairs
+    [4L, 4L+3] of the span: row (4L) // pairs_per_row of the span, pair (4L) % pairs_per_row."""
+    ppr = head_dim // 2
+    rows_per_span = 128 // ppr
+    seen = set()
+    for lane in range(32):
+        row, p0 = (lane * 4) // ppr, (lane * 4) % ppr
+        assert row < rows_per_span and p0 + 3 < ppr
+        for j in range(4):
+            seen.add((row, p0 + j))
+    assert len(seen) == 128 == rows_per_span * ppr
+
+
+def _pair_units(tiles: int, pairs: int):
+    rem = tiles % pairs
+    if tiles > pairs and rem > 0 and 2 * rem <= pairs:
+        return tiles - rem, tiles + rem
+    return tiles, tiles
+
+
+@pytest.mark.parametrize("pairs", [1, 2, 37, 74])
+def test_pair_units_cover_every_tile_once(pairs):
+    """gemm_fp8.cu pair_units / pair_unit: units below full_units are whole tiles; the rest
+    are (tile, half) with tile = full + (u - full) // 2. Every tile must be produced exactly
+    once, whole or as both halves, and the split must only happen for a thin last wave."""
+    for tiles in itertools.chain(range(1, 400), (1024, 1376, 4096)):
+        full, units = _pair_units(tiles, pairs)
+        got = {}
+        for u in range(units):
+            if u < full:
+                got.setdefault(u, []).append("whole")
+            else:
+                got.setdefault(full + (u - full) // 2, []).append((u - full) & 1)
+        assert sorted(got) == list(range(tiles))
+        for t, parts in got.items():
+            assert parts == ["whole"] or sorted(parts) == [0, 1]
+        if units != tiles:
+            waves_before = -(-tiles // pairs)
+            assert units - full <= pairs and -(-full // pairs) + 1 == waves_before
+
+
+def test_decode_warp_block_sequence_matches_its_consumption_order():
+    """int4.cu: a warp requests blocks in the order (round, phase, tile) with a running source
+    pointer; model the pointer and check it against the closed form
+    ((r0 + t) * ngroups + p * warps + warp) * 1056 for several shapes."""
+    blk, warps, round_tiles = 1056, 16, 5
+    for (ngroups, t_begin, t_end, warp) in [(32, 0, 5, 3), (32, 4, 9, 15), (8, 0, 13, 7), (2, 10, 23, 1), (40, 7, 8, 9)]:
+        my_phases = (ngroups - warp + warps - 1) // warps if warp < ngroups else 0
+        tile_stride = ngroups * blk
+        wmine = warp * blk
+        r0, rt, p, t = t_begin, min(round_tiles, t_end - t_begin), 0, 0
+        src = wmine + t_begin * tile_stride
+        seq = []
+        while my_phases > 0 and r0 < t_end:
+            seq.append(src)
+            src += tile_stride
+            t += 1
+            if t == rt:
+                t = 0
+                p += 1
+                if p == my_phases:
+                    p = 0
+                    r0 += round_tiles
+                    rt = min(round_tiles, t_end - r0)
+                src = wmine + r0 * tile_stride + p * warps * blk
+        want = [((rr + tt) * ngroups + pp * warps + warp) * blk
+                for rr in range(t_begin, t_end, round_tiles)
+                for pp in range(my_phases)
+                for tt in range(min(round_tiles, t_end - rr))]
+        assert seq == want
