@@ -44,6 +44,11 @@ Y_B200_API const char* y_b200_version(void);
  * write when a wait runs out. Returns 0 when clean, else Y_B200_ERR_DEVICE
  * with details in y_b200_last_error(). Synchronises `stream`. */
 Y_B200_API int y_b200_device_status(void* stream);
+/* Exercises that path without any fault: launches one small CTA that waits, for at most
+ * `cycles` SM cycles, on a barrier nothing completes, lets the wait run out and records it
+ * like a GEMM role would. The kernel returns normally; the next y_b200_device_status
+ * reports Y_B200_ERR_DEVICE (role 0x7e57) and clears the word. */
+Y_B200_API int y_b200_selftest_bounded_wait(unsigned long long cycles, void* stream);
 
 /* ---- element kinds ---------------------------------------------------------- */
 enum { Y_B200_F32 = 0, Y_B200_F16 = 1, Y_B200_BF16 = 2, Y_B200_E4M3 = 3 };

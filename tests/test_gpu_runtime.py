@@ -111,3 +111,23 @@ def test_measured_autotune_ranks_persists_and_is_reused(rt, tmp_path):
     finally:
         lib.y_autotune_set_profile_path(b"")
         lib.y_autotune_clear_cache()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(cuda):
+    """Failure detection without a fault: a barrier nothing completes, a wait budget of about
+    0.1 ms, an error status the host reads; afterwards the GPU computes as before."""
+    import torch
+
+    from y_b200 import quant as q
+    from y_b200._lib import ERR_DEVICE, YB200Error, check, lib
+    q.device_status()                                   # clean to begin with
+    check(lib.y_b200_selftest_bounded_wait(200_000, None))
+    with pytest.raises(YB200Error) as e:
+        q.device_status()
+    assert e.value.code == ERR_DEVICE and "0x7e57" in e.value.message
+    q.device_status()                                   # reading cleared it
+    a = torch.randint(0, 0x78, (256, 256), dtype=torch.uint8, device="cuda")
+    c1 = q.gemm_fp8_codes(a, a, 1.0, 1.0)
+    c2 = q.gemm_fp8_codes(a, a, 1.0, 1.0)
+    q.device_status()
+    assert torch.equal(c1, c2) and torch.isfinite(c1).all()

@@ -65,6 +65,7 @@ SIGNATURES = {
     "y_b200_last_error": (C.c_char_p, []),
     "y_b200_version": (C.c_char_p, []),
     "y_b200_device_status": (_i, [_vp]),
+    "y_b200_selftest_bounded_wait": (_i, [_u64, _vp]),
     "y_b200_amax": (_i, [_vp, _i, _sz, _vp, _vp]),
     "y_b200_scale_from_amax": (_i, [_vp, _vp, _vp]),
     "y_b200_quantize_fp8": (_i, [_vp, _i, _sz, _vp, _vp, _vp]),

@@ -85,14 +85,14 @@ constexpr long long kWaitCycles = 4000000000LL;
 // Bounded wait. Returns false when the budget ran out or when another role of
 // this CTA already raised `abort_flag` (a word in shared memory).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+                                          volatile uint32_t* abort_flag, long long budget = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag != 0) return false;
-            if (clock64() - t0 > kWaitCycles) return false;
+            if (clock64() - t0 > budget) return false;
         }
     }
     return true;

@@ -139,3 +139,40 @@ extern "C" int y_b200_peer_read(void* host_dst, const void* device_src, size_t b
     if (!host_dst || !device_src) return yb::fail(Y_B200_ERR_INVALID, "y_b200_peer_read: null pointer");
     return yb::check_cuda(cudaMemcpy(host_dst, device_src, bytes, cudaMemcpyDeviceToHost), "cudaMemcpy(device to host)");
 }
+
+// ---- self-test of the bounded-wait path ---------------------------------------------------------
+// One CTA, two warps. Warp 0 waits on an mbarrier that nothing will ever complete, with a
+// budget of `cycles`; when the budget runs out it records the timeout exactly as the GEMM's
+// roles do. Warp 1 plays a second role of the CTA: it watches the abort flag (bounded too)
+// and leaves when it is raised. The kernel always returns; the context stays usable.
+namespace yb {
+namespace {
+__global__ void bounded_wait_selftest_kernel(DeviceStatus* status, long long cycles) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_word;
+    volatile uint32_t* abort_flag = &abort_word;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_word = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!mbar_wait(smem_u32(&bar), 0u, abort_flag, cycles)) report_timeout(status, abort_flag, 0x7e57u, 0u);
+    } else if (threadIdx.x == 32) {
+        const long long t0 = clock64();
+        while (*abort_flag == 0 && clock64() - t0 < 4 * cycles + 1000000) {
+        }
+    }
+}
+}  // namespace
+}  // namespace yb
+
+extern "C" int y_b200_selftest_bounded_wait(unsigned long long cycles, void* stream) {
+    if (cycles == 0 || cycles > 2000000000ull)
+        return yb::fail(Y_B200_ERR_INVALID, "y_b200_selftest_bounded_wait: cycles must be in 1..2e9 (about one second)");
+    yb::DeviceStatus* st = yb::device_status_ptr();
+    if (!st) return yb::fail(Y_B200_ERR_CUDA, "y_b200_selftest_bounded_wait: no CUDA device");
+    yb::bounded_wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(st, (long long)cycles);
+    return yb::check_cuda(cudaGetLastError(), "bounded_wait_selftest_kernel launch");
+}
