@@ -300,11 +300,12 @@ def other_config_metrics(peaks):
     return out
 
 
-def decode_metrics(peaks, iters=200):
-    """INT4 decode GEMM, K=4096, N=11008, M in {1,4,8,32}: HBM-bound weight streaming.
+def decode_metrics(peaks, iters=200, n=None, tokens=(1, 4, 8, 32)):
+    """INT4 decode GEMM, K=4096, N=11008 (or `n`), M in `tokens`: HBM-bound weight streaming.
     Launches are issued by the library's own timing loop (the mirror of the reference's
     time_launches) over a rotating pool of weight buffers of >= 4x L2 so every launch
     reads its weights from HBM, not L2."""
+    DECODE_N = n or globals()["DECODE_N"]
     import torch
 
     from y_b200 import quant as q
@@ -321,7 +322,7 @@ def decode_metrics(peaks, iters=200):
     pool = [q.int4_repack(qw, sc) for _ in range(nbuf)]
     kern = ctx.load_module(None, "y_int4_decode_gemm")
     out = []
-    for m in (1, 4, 8, 32):
+    for m in tokens:
         x = torch.randn(m, DECODE_K, device="cuda", dtype=torch.float16)
         o = torch.empty(m, DECODE_N, device="cuda", dtype=torch.float16)
         sets = [[x.data_ptr(), p.data_ptr(), o.data_ptr(), ("i32", m), ("i32", DECODE_N), ("i32", DECODE_K)]
@@ -528,6 +529,9 @@ def run_ours(args):
     if rank == 0 and world == 1:
         if not args.no_decode:
             line["decode"] = decode_metrics(peaks)
+            # the same kernel on a twice as wide weight matrix (gate and up projections as
+            # one launch): the per-launch fixed latencies weigh half as much
+            line["decode"]["wider"] = decode_metrics(peaks, n=2 * DECODE_N, tokens=(1, 8))
             line["other_configs"] = other_config_metrics(peaks)
         if not args.no_cpu:
             rows = args.cpu_rows

@@ -44,7 +44,8 @@ def _check(got_bits, ref_bits):
     (64, 8, 8, 1, [5, 64, 65]),                       # MHA, page size 1
     (64, 16, 2, 32, [31, 32, 33, 700]),               # GQA 8:1, partial last pages
     (256, 8, 4, 64, [200, 1]),                        # head 256
-    (128, 16, 1, 16, [50] * 40),                      # 16 query heads on one KV head, enough sequences not to split
+    (128, 16, 1, 16, [50] * 40),                      # 16 query heads on one KV head; splits thinner than one tile
+    (128, 8, 2, 16, [40, 9] * 100),                   # more CTAs than the SMs hold at once: no split, no merge kernel
     (128, 4, 4, 16, [0, 0]),                          # nothing to attend to
 ])
 def test_paged_decode_attention_matches_oracle(q, hd, hq, hkv, ps, seq_lens):

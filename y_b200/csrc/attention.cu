@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(kAttnThreads)
     const int gq = lane >> 2, c4 = lane & 3;
     const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
     const int group = p.num_q_heads / p.num_kv_heads;  // query heads per KV head, <= 16
+    pdl_wait();  // q and the newest K/V rows come from the kernels before this one
     const int seq_len = p.seq_lens[seq];
     const int tiles = (seq_len + kTileTokens - 1) / kTileTokens;
     const int tiles_per_split = (tiles + p.splits - 1) / p.splits;
@@ -230,6 +231,7 @@ __global__ void __launch_bounds__(kAttnThreads)
         if (++slot == kAttnDepth) slot = 0;
     }
     cp_wait<0>();
+    pdl_launch_dependents();  // the merge kernel (or the caller's next one) may become resident
 
     // ---- merge the warps' states, then write the CTA's result -----------------------------------
 #pragma unroll
@@ -284,6 +286,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
                                        __half* __restrict__ out, int num_q_heads, int splits, int D) {
     const size_t head = (size_t)blockIdx.y * num_q_heads + blockIdx.x;
     const float* ml = part_ml + head * splits * 2;
+    pdl_wait();  // the splits' partial states are complete and visible
     float M = kNegBig;
     for (int i = 0; i < splits; ++i) M = fmaxf(M, ml[2 * i]);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
@@ -297,11 +300,22 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
     }
 }
 
-int choose_splits(int num_seqs, int num_kv_heads) {
-    // Enough CTAs for two per SM; a split is never thinner than the CTA's four warps can fill,
-    // which the kernel guarantees by itself (empty splits write neutral states).
+// CTAs of the kernel that one SM holds at a time: shared memory decides (three K/V tiles per
+// warp in flight), 227 KB per SM less 1 KB that the system keeps per resident CTA.
+int ctas_per_sm(int head_dim) {
+    const int smem = head_dim == 64 ? AttnCfg<64>::smem_bytes
+                     : head_dim == 128 ? AttnCfg<128>::smem_bytes
+                                       : AttnCfg<256>::smem_bytes;
+    const int n = (227 * 1024) / (smem + 1024);
+    return n < 1 ? 1 : (n > 4 ? 4 : n);
+}
+
+int choose_splits(int num_seqs, int num_kv_heads, int head_dim) {
+    // As many CTAs as are resident at once, and no more: a few CTAs left over for a second
+    // wave would stream their share alone, far below the HBM rate. Empty splits (a sequence
+    // shorter than its share) write neutral states.
     const long long base = (long long)num_seqs * num_kv_heads;
-    long long want = (2LL * sm_count() + base - 1) / base;
+    long long want = (long long)sm_count() * ctas_per_sm(head_dim) / base;
     if (want < 1) want = 1;
     if (want > kMaxSplits) want = kMaxSplits;
     return (int)want;
@@ -319,12 +333,11 @@ int launch_attention(const AttnParams& p, int num_seqs, cudaStream_t st) {
         configured[dev] = true;
     }
     dim3 grid((unsigned)p.num_kv_heads, (unsigned)num_seqs, (unsigned)p.splits);
-    paged_decode_attention_kernel<D><<<grid, kAttnThreads, Cfg::smem_bytes, st>>>(p);
-    YB_CUDA(cudaGetLastError());
+    YB_CUDA(launch_pdl(paged_decode_attention_kernel<D>, grid, dim3(kAttnThreads), Cfg::smem_bytes, st, p));
     if (p.splits > 1) {
         dim3 mgrid((unsigned)p.num_q_heads, (unsigned)num_seqs);
-        attention_merge_kernel<<<mgrid, D < 128 ? D : 128, 0, st>>>(p.part_o, p.part_ml, p.out, p.num_q_heads, p.splits, D);
-        YB_CUDA(cudaGetLastError());
+        YB_CUDA(launch_pdl(attention_merge_kernel, mgrid, dim3(D < 128 ? D : 128), 0, st, p.part_o, p.part_ml, p.out,
+                           p.num_q_heads, p.splits, D));
     }
     return 0;
 }
@@ -337,7 +350,7 @@ using namespace yb;
 extern "C" size_t y_b200_paged_decode_attention_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads,
                                                                 int head_dim) {
     if (num_seqs < 1 || num_q_heads < 1 || num_kv_heads < 1 || head_dim < 1) return 0;
-    const int splits = choose_splits(num_seqs, num_kv_heads);
+    const int splits = choose_splits(num_seqs, num_kv_heads, head_dim);
     if (splits == 1) return 256;
     const size_t heads = (size_t)num_seqs * num_q_heads * splits;
     return ((heads * head_dim * 4 + 255) & ~(size_t)255) + ((heads * 8 + 255) & ~(size_t)255);
@@ -374,7 +387,7 @@ extern "C" int y_b200_paged_decode_attention(const void* q_f16, const void* kcac
     p.num_kv_heads = num_kv_heads;
     p.page_size = page_size;
     p.max_pages = max_pages;
-    p.splits = choose_splits(num_seqs, num_kv_heads);
+    p.splits = choose_splits(num_seqs, num_kv_heads, head_dim);
     p.scale_log2e = (float)(1.4426950408889634 / sqrt((double)head_dim));
     if (p.splits > 1) {
         const size_t need = y_b200_paged_decode_attention_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim);
