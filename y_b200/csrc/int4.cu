@@ -14,6 +14,9 @@
 // across the warps of a CTA and reduced in shared memory in a fixed order: no
 // atomics, results overwrite the output and are run-to-run identical. Nothing in
 // the kernel waits on a barrier that another agent has to complete.
+#include <type_traits>
+#include <utility>
+
 #include "common.cuh"
 
 namespace yb {
@@ -153,10 +156,26 @@ constexpr uint32_t kOffsetHi = 0x54805480u;  // f16 pair (72, 72)
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
 }
+// 16-byte copy that writes zeros and reads nothing when `valid` is false.
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t dst_smem, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// f(integral_constant<int, 0>), ..., f(integral_constant<int, N - 1>): a loop whose index
+// is a compile-time constant inside the body.
+template <typename F, int... I>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
+    (f(std::integral_constant<int, I>()), ...);
+}
+template <int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+    static_for_impl(f, std::make_integer_sequence<int, N>());
 }
 
 // The blocks one warp works through, in order: rounds of up to round_tiles tiles; within a
@@ -244,115 +263,235 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
 
     pdl_wait();  // earlier kernels' writes to x / reads of out are complete
     const int gq = lane >> 2, c = lane & 3;
-    {
-        // ---- weights are the 16-row MMA operand, tokens the 8-wide one.
-        for (int r0 = t_begin; r0 < t_end; r0 += kRoundTiles) {
-            const int rt = min(kRoundTiles, t_end - r0);
-            float acc[kRoundTiles][NT][4];
+    // ---- weights are the 16-row MMA operand, tokens the 8-wide one.
+    // The common decode shape (K = 4096 with 16 warps: two K groups per warp; a CTA share of
+    // four or five tiles: one round) runs as straight-line code: block b of the warp is
+    // (group b / RT, tile b % RT), so its ring slot, its source and whether a block kDepth
+    // ahead exists are all known at compile time. The blocks requested before the wait
+    // above are the first kDepth of the same order. Against the loop below this saves about
+    // a quarter of the instructions per block. (Only for up to 8 tokens: with wider token
+    // tiles the second code path costs the loop below registers it does not have.)
+    if constexpr (NT == 1) {
+        const int share = t_end - t_begin;
+        if (ngroups == 2 * kWarps && (share == kRoundTiles || share == kRoundTiles - 1)) {
+            float acc[kRoundTiles][4];
+            uint4 xf[4];       // activation fragments of the current group: token gq, k = 128g + 32pp + 8c + (0..7)
+            float neg_off[4];  // minus the group's offset contribution (see the dequantisation note above)
+#pragma unroll
+            for (int t = 0; t < kRoundTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+            auto group_offsets = [&]() {
+                float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[pp].x, xf[pp].y);
+                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[pp].z, xf[pp].w);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) neg_off[i] = -o[i];
+            };
+            // One 16 x 128 block against the group's activations, added into `a`. `done_reading`
+            // runs as soon as the block's bytes are in registers (it frees the ring slot).
+            auto block_math = [&](const uint8_t* blk, auto&& done_reading, float (&a)[4]) {
+                const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
+                const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
+                const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
+                const float s_lo = __half2float(sc[gq]);
+                const float s_hi = __half2float(sc[gq + 8]);
+                done_reading();
+                const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
+                const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
+                float tmp[4] = {neg_off[0], neg_off[1], neg_off[2], neg_off[3]};
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
+                    const uint32_t a0 = and_or(wA[pp], dq.mask_lo, dq.exp_lo), a1 = and_or(wB[pp], dq.mask_lo, dq.exp_lo);
+                    const uint32_t a2 = and_or(wA[pp], dq.mask_hi, dq.exp_hi), a3 = and_or(wB[pp], dq.mask_hi, dq.exp_hi);
+                    const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
+                    const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
+                    mma_16816(tmp, a0, a1, a2, a3, xf[pp].x, xf[pp].y);
+                    mma_16816(tmp, e0, e1, e2, e3, xf[pp].z, xf[pp].w);
+                }
+                a[0] = fmaf(s_lo, tmp[0], a[0]);
+                a[1] = fmaf(s_lo, tmp[1], a[1]);
+                a[2] = fmaf(s_hi, tmp[2], a[2]);
+                a[3] = fmaf(s_hi, tmp[3], a[3]);
+            };
+            float* const mine = red + (size_t)warp * (kRoundTiles * 128);
+            auto straight_line = [&](auto rt_const) {
+                constexpr int RT = decltype(rt_const)::value;
+                static_assert(RT >= kDepth, "the second group's activations must land before its first block");
+                const uint8_t* const s0 = wmine + (size_t)t_begin * tile_stride + lane * 16;
+                const uint8_t* const s1 = s0 + (size_t)kWarps * kBlkBytes;
+                const uint32_t d0 = stage0 + lane * 16;
+                // First group's activations straight into registers.
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    xf[pp] = make_uint4(0, 0, 0, 0);
+                    if (gq < M)
+                        xf[pp] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)gq * K + (size_t)warp * 128 + pp * 32 + c * 8));
+                }
+                // The second group's travel with the first block request after the wait, into
+                // this warp's part of the reduction area (unused until the round ends), so that
+                // the switch of groups does not wait on a global load.
+                {
+                    const uint32_t xdst = smem_u32(mine) + lane * 16;
+                    const __half* xsrc = x + (size_t)(gq < M ? gq : 0) * K + (size_t)(kWarps + warp) * 128 + c * 8;
+#pragma unroll
+                    for (int pp = 0; pp < 4; ++pp) cp_async_16_zfill(xdst + pp * 512, xsrc + pp * 32, gq < M);
+                }
+                group_offsets();
+                static_for<2 * RT>([&](auto b_const) {
+                    constexpr int b = decltype(b_const)::value;
+                    cp_async_wait<kDepth - 1>();  // blocks 0..b and, from b = kDepth on, the activations
+                    __syncwarp();
+                    if constexpr (b == RT) {
+#pragma unroll
+                        for (int pp = 0; pp < 4; ++pp)
+                            xf[pp] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(mine) + pp * 512 + lane * 16);
+                        group_offsets();
+                    }
+                    block_math(stage + (b % kDepth) * kBlkBytes,
+                               [&]() {
+                                   __syncwarp();
+                                   constexpr int nb = b + kDepth;
+                                   if constexpr (nb < 2 * RT) {
+                                       const uint8_t* src = (nb < RT ? s0 : s1) + (size_t)(nb % RT) * tile_stride;
+                                       const uint32_t dst = d0 + (nb % kDepth) * kBlkBytes;
+                                       cp_async_16(dst, src);
+                                       cp_async_16(dst + 512, src + 512);
+                                       if (lane < 2) cp_async_16(dst + 1024, src + 1024);
+                                   }
+                                   cp_async_commit();
+                               },
+                               acc[b % RT]);
+                });
+            };
+            if (share == kRoundTiles)
+                straight_line(std::integral_constant<int, kRoundTiles>());
+            else
+                straight_line(std::integral_constant<int, kRoundTiles - 1>());
+            cp_async_wait<0>();  // only empty groups are left
+            // ---- cross-warp reduction in warp order, then store (as in the loop below) ----
 #pragma unroll
             for (int t = 0; t < kRoundTiles; ++t)
-#pragma unroll
-                for (int j = 0; j < NT; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[t][j][i] = 0.0f;
-
-            for (int p = 0; p < my_phases; ++p) {
-                const int g = p * kWarps + warp;
-                // Activation fragments of this warp's group: token gq + 8j,
-                // k = 128g + 32pp + 8c + (0..7).
-                uint4 xf[NT][4];
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    const int tok = gq + 8 * j;
-#pragma unroll
-                    for (int pp = 0; pp < 4; ++pp) {
-                        xf[j][pp] = make_uint4(0, 0, 0, 0);
-                        if (tok < M)
-                            xf[j][pp] = __ldg(reinterpret_cast<const uint4*>(
-                                x + (size_t)tok * K + (size_t)g * 128 + pp * 32 + c * 8));
-                    }
-                }
-                // Offset contribution of this group (see the dequantisation note above): identical for
-                // all 16 weight columns, so one MMA pass with a constant operand.
-                float neg_off[NT][4];
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                    for (int pp = 0; pp < 4; ++pp) {
-                        mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].x, xf[j][pp].y);
-                        mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].z, xf[j][pp].w);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) neg_off[j][i] = -o[i];
-                }
-                auto tile_step = [&](const int t) {
-                        const uint8_t* blk = acquire();
-                        const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
-                        const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
-                        const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
-                        const float s_lo = __half2float(sc[gq]);
-                        const float s_hi = __half2float(sc[gq + 8]);
-                        release();
-                        const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
-                        const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
-                        float tmp[NT][4];
-#pragma unroll
-                        for (int j = 0; j < NT; ++j)
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) tmp[j][i] = neg_off[j][i];
-#pragma unroll
-                        for (int pp = 0; pp < 4; ++pp) {
-                            const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
-                            const uint32_t a0 = and_or(wA[pp], dq.mask_lo, dq.exp_lo), a1 = and_or(wB[pp], dq.mask_lo, dq.exp_lo);
-                            const uint32_t a2 = and_or(wA[pp], dq.mask_hi, dq.exp_hi), a3 = and_or(wB[pp], dq.mask_hi, dq.exp_hi);
-                            const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
-                            const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
-#pragma unroll
-                            for (int j = 0; j < NT; ++j) {
-                                mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
-                                mma_16816(tmp[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
-                            }
-                        }
-#pragma unroll
-                        for (int j = 0; j < NT; ++j) {
-                            acc[t][j][0] = fmaf(s_lo, tmp[j][0], acc[t][j][0]);
-                            acc[t][j][1] = fmaf(s_lo, tmp[j][1], acc[t][j][1]);
-                            acc[t][j][2] = fmaf(s_hi, tmp[j][2], acc[t][j][2]);
-                            acc[t][j][3] = fmaf(s_hi, tmp[j][3], acc[t][j][3]);
-                        }
-                };
-                if (rt == kRoundTiles) {
-#pragma unroll
-                    for (int t = 0; t < kRoundTiles; ++t) tile_step(t);
-                } else {
-#pragma unroll
-                    for (int t = 0; t < kRoundTiles; ++t)
-                        if (t < rt) tile_step(t);
-                }
-            }
-
-            // ---- cross-warp reduction in warp order, then store --------------
-            float* mine = red + (size_t)warp * (kRoundTiles * NT * 128);
-#pragma unroll
-            for (int t = 0; t < kRoundTiles; ++t)
-#pragma unroll
-                for (int j = 0; j < NT; ++j)
-                    *reinterpret_cast<float4*>(mine + (t * NT + j) * 128 + lane * 4) =
-                        make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
+                *reinterpret_cast<float4*>(mine + t * 128 + lane * 4) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
             __syncthreads();
-            const int nout = rt * NT * 128;
-            for (int e = threadIdx.x; e < nout; e += kWarps * 32) {
+            for (int e = threadIdx.x; e < share * 128; e += kWarps * 32) {
                 float v = red[e];
 #pragma unroll
-                for (int w = 1; w < kWarps; ++w) v += red[w * (kRoundTiles * NT * 128) + e];
-                const int t = e / (NT * 128), j = (e / 128) % NT, l = (e % 128) / 4, i = e % 4;
-                const int col = (r0 + t) * 16 + (l >> 2) + 8 * (i >> 1);
-                const int tok = 8 * j + 2 * (l & 3) + (i & 1);
+                for (int w = 1; w < kWarps; ++w) v += red[w * (kRoundTiles * 128) + e];
+                const int t = e / 128, l = (e % 128) / 4, i = e % 4;
+                const int col = (t_begin + t) * 16 + (l >> 2) + 8 * (i >> 1);
+                const int tok = 2 * (l & 3) + (i & 1);
                 if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
             }
-            __syncthreads();
+            return;
         }
+    }
+    for (int r0 = t_begin; r0 < t_end; r0 += kRoundTiles) {
+        const int rt = min(kRoundTiles, t_end - r0);
+        float acc[kRoundTiles][NT][4];
+#pragma unroll
+        for (int t = 0; t < kRoundTiles; ++t)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[t][j][i] = 0.0f;
+        for (int p = 0; p < my_phases; ++p) {
+            const int g = p * kWarps + warp;
+            // Activation fragments of this warp's group: token gq + 8j,
+            // k = 128g + 32pp + 8c + (0..7).
+            uint4 xf[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int tok = gq + 8 * j;
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    xf[j][pp] = make_uint4(0, 0, 0, 0);
+                    if (tok < M)
+                        xf[j][pp] = __ldg(reinterpret_cast<const uint4*>(
+                            x + (size_t)tok * K + (size_t)g * 128 + pp * 32 + c * 8));
+                }
+            }
+            // Offset contribution of this group (see the dequantisation note above): identical for
+            // all 16 weight columns, so one MMA pass with a constant operand.
+            float neg_off[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].x, xf[j][pp].y);
+                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].z, xf[j][pp].w);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) neg_off[j][i] = -o[i];
+            }
+            auto tile_step = [&](const int t) {
+                const uint8_t* blk = acquire();
+                const uint4 u0 = *reinterpret_cast<const uint4*>(blk + lane * 16);
+                const uint4 u1 = *reinterpret_cast<const uint4*>(blk + 512 + lane * 16);
+                const __half* sc = reinterpret_cast<const __half*>(blk + 1024);
+                const float s_lo = __half2float(sc[gq]);
+                const float s_hi = __half2float(sc[gq + 8]);
+                release();
+                const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
+                const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
+                float tmp[NT][4];
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) tmp[j][i] = neg_off[j][i];
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
+                    const uint32_t a0 = and_or(wA[pp], dq.mask_lo, dq.exp_lo), a1 = and_or(wB[pp], dq.mask_lo, dq.exp_lo);
+                    const uint32_t a2 = and_or(wA[pp], dq.mask_hi, dq.exp_hi), a3 = and_or(wB[pp], dq.mask_hi, dq.exp_hi);
+                    const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
+                    const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
+                        mma_16816(tmp[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    acc[t][j][0] = fmaf(s_lo, tmp[j][0], acc[t][j][0]);
+                    acc[t][j][1] = fmaf(s_lo, tmp[j][1], acc[t][j][1]);
+                    acc[t][j][2] = fmaf(s_hi, tmp[j][2], acc[t][j][2]);
+                    acc[t][j][3] = fmaf(s_hi, tmp[j][3], acc[t][j][3]);
+                }
+            };
+            if (rt == kRoundTiles) {
+#pragma unroll
+                for (int t = 0; t < kRoundTiles; ++t) tile_step(t);
+            } else {
+#pragma unroll
+                for (int t = 0; t < kRoundTiles; ++t)
+                    if (t < rt) tile_step(t);
+            }
+        }
+        // ---- cross-warp reduction in warp order, then store --------------
+        float* mine = red + (size_t)warp * (kRoundTiles * NT * 128);
+#pragma unroll
+        for (int t = 0; t < kRoundTiles; ++t)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+                *reinterpret_cast<float4*>(mine + (t * NT + j) * 128 + lane * 4) =
+                    make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
+        __syncthreads();
+        const int nout = rt * NT * 128;
+        for (int e = threadIdx.x; e < nout; e += kWarps * 32) {
+            float v = red[e];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) v += red[w * (kRoundTiles * NT * 128) + e];
+            const int t = e / (NT * 128), j = (e / 128) % NT, l = (e % 128) / 4, i = e % 4;
+            const int col = (r0 + t) * 16 + (l >> 2) + 8 * (i >> 1);
+            const int tok = 8 * j + 2 * (l & 3) + (i & 1);
+            if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
+        }
+        __syncthreads();
     }
     cp_async_wait<0>();  // only empty groups can be left; nothing may be pending at exit
 }
