@@ -125,3 +125,30 @@ def test_decode_warp_block_sequence_matches_its_consumption_order():
                 for pp in range(my_phases)
                 for tt in range(min(round_tiles, t_end - rr))]
         assert seq == want
+
+
+@pytest.mark.parametrize("share", [4, 5])
+def test_decode_straight_line_order_is_the_general_order(share):
+    """int4.cu, the one-round two-group path: block b is (group b // RT, tile b % RT) read from
+    s0 or s1 + (b % RT) * tile_stride into ring slot b % depth. That must be the order of the
+    general sequence (whose first `depth` requests the kernel's prologue has already issued),
+    a block's slot must be free when it is requested (block b - depth has been read), and the
+    activations copied with the first request after the wait must have landed at b = RT."""
+    blk, warps, depth, ngroups = 1056, 16, 3, 32
+    tile_stride = ngroups * blk
+    for warp in (0, 7, 15):
+        for t_begin in (0, 9, 683):
+            s0 = warp * blk + t_begin * tile_stride
+            s1 = s0 + warps * blk
+            straight = [(s0 if b < share else s1) + (b % share) * tile_stride for b in range(2 * share)]
+            general = [((t_begin + t) * ngroups + p * warps + warp) * blk for p in range(2) for t in range(share)]
+            assert straight == general
+    # ring discipline: before step b the committed groups are blocks 0 .. depth - 1 + b; waiting for
+    # all but the newest depth - 1 leaves blocks 0 .. b complete; the x copies ride in group `depth`
+    for b in range(2 * share):
+        committed = depth + b
+        complete = committed - (depth - 1)
+        assert complete == b + 1
+        if b + depth < 2 * share:
+            assert (b + depth) % depth == b % depth  # the slot just read is the one refilled
+    assert share >= depth  # group `depth` (first commit after the wait) is complete from step depth on
