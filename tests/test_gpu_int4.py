@@ -78,12 +78,16 @@ def test_decode_config_shape_full(q, golden_dir):
     qint = np.where(nib >= 8, nib - 16, nib)
     wd = qint * np.repeat(sc_h.view(np.float16).astype(np.float32), 128, axis=0)
     assert np.abs(wd - w.float().cpu().numpy()).max() <= np.abs(w.float().cpu().numpy()).max() / 7 * 0.51 + 1e-6
-    for m in (1, 4, 8, 32):
+    for m in (1, 3, 4, 8, 32):
         x = torch.randn(m, k, device="cuda", dtype=torch.float16)
         out = q.gemm_int4_decode(x, stream, n)
         q.device_status()
         ref = oracle.gemm_int4_decode(host_bits(x), qw_h, sc_h)
         assert_gemm_close(to_f64(host_bits(out), oracle.OUT_F16), to_f64(ref, oracle.OUT_F16), f"M={m}")
+    # up to 8 tokens this shape takes the kernel's straight-line path, 9 tokens its loop: the
+    # same sums in the same order, so the first 8 rows must agree bit for bit
+    x9 = torch.randn(9, k, device="cuda", dtype=torch.float16)
+    assert torch.equal(q.gemm_int4_decode(x9[:8].contiguous(), stream, n), q.gemm_int4_decode(x9, stream, n)[:8])
     g = np.load(os.path.join(golden_dir, "path_small.npz"))
     M4, N4, K4 = g["int4_shape"]
     xw = oracle.fill_normal_f16(M4 * K4, oracle.SEED_A + 3).reshape(M4, K4)
