@@ -201,7 +201,7 @@ struct BlockSeq {
 template <int NT>
 __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
     int4_decode_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ wstream,
-                       __half* __restrict__ out, int M, int N, int K) {
+                       __half* __restrict__ out, int M, int N, int K, int share_q, int share_r) {
     using Cfg = DecodeCfg<NT>;
     constexpr int kRoundTiles = Cfg::round_tiles, kWarps = Cfg::warps, kDepth = Cfg::depth;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -215,9 +215,12 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
 
     const int ngroups = K / 128;
     const int my_phases = warp < ngroups ? (ngroups - warp + kWarps - 1) / kWarps : 0;
-    const int T = N / 16;
-    const int t_begin = (int)(((long long)blockIdx.x * T) / gridDim.x);
-    const int t_end = (int)(((long long)(blockIdx.x + 1) * T) / gridDim.x);
+    // CTA b owns share_q tiles, the first share_r CTAs one more (both computed by the host: a
+    // division is a long dependent subroutine at the very start of a kernel whose first
+    // requests should go out at once).
+    const int bid = (int)blockIdx.x;
+    const int t_begin = bid * share_q + min(bid, share_r);
+    const int t_end = t_begin + share_q + (bid < share_r ? 1 : 0);
 
     const size_t tile_stride = (size_t)ngroups * kBlkBytes;  // same group, next tile
     const uint8_t* const wmine = wstream + (size_t)warp * kBlkBytes;  // this warp's group of phase 0, tile 0
@@ -512,7 +515,7 @@ int launch_decode(const void* x, const void* wstream, void* out, int m, int n, i
     const int grid = tiles < sm_count() ? tiles : sm_count();
     return check_cuda(launch_pdl(int4_decode_kernel<NT>, (unsigned)grid, (unsigned)Cfg::threads, Cfg::smem_bytes, st,
                                  static_cast<const __half*>(x), static_cast<const uint8_t*>(wstream),
-                                 static_cast<__half*>(out), m, n, k),
+                                 static_cast<__half*>(out), m, n, k, tiles / grid, tiles % grid),
                       "int4_decode_kernel launch");
 }
 
