@@ -152,3 +152,23 @@ def test_decode_straight_line_order_is_the_general_order(share):
         if b + depth < 2 * share:
             assert (b + depth) % depth == b % depth  # the slot just read is the one refilled
     assert share >= depth  # group `depth` (first commit after the wait) is complete from step depth on
+
+
+@pytest.mark.parametrize("tiles,sms", [(688, 148), (1376, 148), (86, 148), (149, 148), (1, 148), (4096, 132)])
+def test_decode_tile_partition_covers_every_tile_once(tiles, sms):
+    """int4.cu: the host passes share_q = tiles // grid and share_r = tiles % grid; CTA b owns
+    [b * q + min(b, r), + q + (b < r)). The shares must tile [0, tiles) in order and differ by
+    at most one; 688 tiles on 148 CTAs give only shares of 4 and 5 (the straight-line path)."""
+    grid = min(tiles, sms)
+    q, r = divmod(tiles, grid)
+    end = 0
+    shares = set()
+    for b in range(grid):
+        t_begin = b * q + min(b, r)
+        t_end = t_begin + q + (1 if b < r else 0)
+        assert t_begin == end and t_end > t_begin
+        shares.add(t_end - t_begin)
+        end = t_end
+    assert end == tiles and max(shares) - min(shares) <= 1
+    if (tiles, sms) == (688, 148):
+        assert shares == {4, 5}
