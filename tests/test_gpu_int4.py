@@ -106,3 +106,22 @@ def test_decode_preconditions(q):
     assert e.value.code == ERR_SHAPE
     with pytest.raises(YB200Error):
         q.gemm_int4_decode(x[:4, :100].contiguous(), s, 16)
+
+
+@pytest.mark.parametrize("tiles", [592, 740, 800, 149])
+def test_decode_both_paths_on_mixed_shares(q, tiles):
+    # K = 4096 with 592 / 740 column tiles: every CTA owns 4 / 5 tiles (straight-line path);
+    # 800: shares of 5 and 6 (both paths in one launch); 149: shares of 1 and 2 (loop only)
+    k, n = 4096, 16 * tiles
+    w = oracle.fill_normal_f16(k * n, oracle.SEED_B + 11, 1.0 / 64.0).reshape(k, n)
+    rq, rs = oracle.int4_quantize(w)
+    stream = dev(oracle.int4_repack(rq, rs))
+    x = oracle.fill_normal_f16(9 * k, oracle.SEED_A + 11).reshape(9, k)
+    xd = f16_dev(x)
+    out9 = q.gemm_int4_decode(xd, stream, n)          # 9 tokens: the loop path everywhere
+    for m in (1, 5, 8):
+        out = q.gemm_int4_decode(xd[:m].contiguous(), stream, n)
+        assert torch.equal(out, out9[:m]), m
+    q.device_status()
+    ref = oracle.gemm_int4_decode(x[:8], rq, rs)
+    assert_gemm_close(to_f64(host_bits(out), oracle.OUT_F16), to_f64(ref, oracle.OUT_F16))
