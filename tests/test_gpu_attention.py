@@ -101,3 +101,25 @@ def test_through_the_launch_api_with_the_reference_fixture_name(q):
                                               sld.data_ptr(), out.data_ptr(), ("i32", pt.shape[1])])
     kern.free()
     ctx.close()
+
+
+@pytest.mark.parametrize("hd,hq,hkv,ps,ns", [
+    (128, 32, 8, 16, 3),      # 12 splits per sequence
+    (128, 32, 8, 16, 37),     # one split: more CTAs than the SMs hold
+    (64, 8, 1, 16, 9),        # one KV head, few sequences: the maximum of 32 splits, most of them empty
+    (256, 16, 2, 32, 150),    # head 256 (one CTA per SM), no split
+    (128, 16, 16, 8, 5),      # MHA, 3 splits
+])
+def test_ragged_batches_over_the_range_of_split_counts(q, hd, hq, hkv, ps, ns):
+    """The split count depends on the number of sequences and KV heads only, so ragged
+    lengths leave some splits short or empty; whatever the count, the result is the oracle's."""
+    rng = np.random.default_rng(1000 + ns)
+    seq_lens = [int(v) for v in rng.integers(0, 700, size=ns)]
+    seq_lens[0] = max(seq_lens[0], 1)
+    if ns <= 5:
+        seq_lens = [v * 5 for v in seq_lens]
+    qv, kc, vc, pt, sl = _case(hd, hq, hkv, ps, seq_lens, 500 + ns)
+    out = q.paged_decode_attention(f16_dev(qv), f16_dev(kc), f16_dev(vc), torch.from_numpy(pt).cuda(),
+                                   torch.from_numpy(sl).cuda())
+    q.device_status()
+    _check(host_bits(out), oracle.paged_decode_attention(qv, kc, vc, pt, sl))
