@@ -13,6 +13,7 @@
 #ifndef Y_B200_H
 #define Y_B200_H
 
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -130,6 +131,63 @@ typedef struct y_b200_gemm_fp8_args {
 
 Y_B200_API int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* args, void* stream);
 
+/* ---- F16 GEMM ---------------------------------------------------------------
+ * Replaces gemm_f16_<tag>, gemm_f16_bias_relu_<tag>, gemm_f16_swiglu_<tag>
+ * (src/ptx_emitter.rs:4199-4694, :4729-4814, :5064-5565; entries
+ * tests/gemm_f16_decode_m1.ptx:6-9, tests/gemm_f16_bias_relu_4096.ptx:6-10,
+ * tests/gemm_f16_swiglu_4096.ptx:6-10) and y_tensor_core_gemm_kernel /
+ * y_fused_gemm_bias_relu_fp16_kernel (tests/y_tensor_core_gemm.cu:102-107, :2712-2719):
+ *   C = epilogue(alpha * (A @ B)), f16 operands, f32 accumulation in tensor memory
+ *   (tcgen05.mma.kind::f16), the same kernels and epilogues as the FP8 GEMM.
+ * a: [M, K] f16 row-major. bt: [N, K] f16 row-major (B stored K-major). K % 8 == 0.
+ * alpha == 0 means 1. EPI_SWIGLU: bt rows are gate|up interleaved (2j gate, 2j+1 up),
+ * c is [M, N/2], out_kind F32 or BF16. */
+typedef struct y_b200_gemm_f16_args {
+    const void* a;
+    const void* bt;
+    void* c;
+    int m, n, k;
+    float alpha;
+    const void* bias;  /* [N], bias_kind F16 or F32; NULL for EPI_NONE/SWIGLU */
+    int bias_kind;
+    int epilogue;      /* Y_B200_EPI_*  */
+    int out_kind;      /* Y_B200_F32 / F16 / BF16 */
+    int cta_n, max_ctas, cta_m;  /* as in y_b200_gemm_fp8_args */
+} y_b200_gemm_f16_args;
+Y_B200_API int y_b200_gemm_f16(const y_b200_gemm_f16_args* args, void* stream);
+
+/* Drop-ins for the reference entries, which take B row-major [K, N]:
+ *   gemm_f16_<tag>(A, B, C) and gemm_f16_bias_relu_<tag>(A, B, Bias f32 [N], C):
+ *     C [M, N] = A @ B (+ Bias, ReLU when bias != NULL / relu != 0); out_kind F32 (the compiled
+ *     entries) or F16 (the runtime-shape .cu entries); bias_kind F32 or F16.
+ *   gemm_f16_swiglu_<tag>(X, Wgate, Wup, Out): Out [M, N] f32 = silu(X @ Wgate) * (X @ Wup),
+ *     Wgate and Wup separate [K, N] matrices.
+ * Each call first copies the weights K-major into `workspace` (one HBM-bound pass; a caller
+ * that keeps its weights K-major uses y_b200_gemm_f16 and skips it), then runs the GEMM.
+ * K % 8 == 0. workspace: the matching *_workspace_bytes, 256-byte aligned. */
+Y_B200_API size_t y_b200_gemm_f16_rowmajor_workspace_bytes(int n, int k);
+Y_B200_API int y_b200_gemm_f16_rowmajor(const void* a_f16, const void* b_f16, const void* bias, int bias_kind,
+                                        int relu, void* c, int out_kind, int m, int n, int k, void* workspace,
+                                        size_t workspace_bytes, void* stream);
+Y_B200_API size_t y_b200_gemm_f16_swiglu_workspace_bytes(int n, int k);
+Y_B200_API int y_b200_gemm_f16_swiglu(const void* x_f16, const void* wgate_f16, const void* wup_f16, float* out,
+                                      int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Small-M F16 GEMM with the weights streamed once from HBM, row-major [K, N] as the
+ * reference's gemm_f16_decode_m<M> entries take them (tests/gemm_f16_decode_m1.ptx:6-9):
+ *   out [M, N] (F32 or F16) = x [M, K] f16 (row stride ldx elements) @ w [K, N] f16.
+ * 1 <= M <= 32, K % 16 == 0, N % 8 == 0, ldx % 2 == 0; no workspace, no atomics (K is split
+ * across the warps of a CTA and reduced in a fixed order). */
+Y_B200_API int y_b200_gemm_f16_decode(const void* x_f16, int ldx, const void* w_f16, void* out, int out_kind,
+                                      int m, int n, int k, void* stream);
+/* The reference's split-K pair for decode shapes (tests/y_tensor_core_gemm.cu:4732-4738,
+ * :4852-4858): partial sums over k_splits equal K ranges into workspace [k_splits, M, N] f32,
+ * then their sum in split order rounded to f16. K % (16 * k_splits) == 0. */
+Y_B200_API int y_b200_gemm_f16_splitk_workspace(const void* a_f16, const void* b_f16, float* workspace, int m,
+                                                int n, int k, int k_splits, void* stream);
+Y_B200_API int y_b200_splitk_reduction(const float* workspace, void* c_f16, size_t total, int m, int n,
+                                       int k_splits, void* stream);
+
 /* Launch geometry the library would use for this problem (the reference
  * embeds it in PTX comments, src/ptx_emitter.rs:3337, :4323-4331). */
 typedef struct y_b200_launch_info {
@@ -137,6 +195,9 @@ typedef struct y_b200_launch_info {
     unsigned dyn_smem_bytes;
     size_t workspace_bytes;
     int cta_m, cta_n, cta_k, stages;
+    /* EpilogueFusionPass's statistic (src/quantization_pass.rs:802-819): 1 when an activation
+     * (ReLU, SiLU) is fused into this kernel's accumulator write-back, else 0. */
+    int fused_epilogues;
 } y_b200_launch_info;
 Y_B200_API int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b200_launch_info* out);
 
@@ -157,18 +218,25 @@ Y_B200_API int y_b200_gemm_fp8_f32(const float* a, const float* b, float scale_a
  * buffers itself.
  * The e4m3 operand copies go to a fixed array inside the library image instead
  * of a workspace: every GPU that loads the library holds
- * Y_B200_STATIC_OPERAND_BYTES + 256 bytes of it until the process exits.
+ * Y_B200_STATIC_OPERAND_BYTES + 256 bytes of it until the process exits. That
+ * memory is reserved when the CUDA module holding the array is loaded on a
+ * device - with CUDA's default lazy loading, on the first call that touches it,
+ * which is normally the first call of this entry - not per call. A caller whose
+ * own pool is about to take the rest of HBM therefore makes one warm-up call
+ * per device first (any small shape).
  * Limit: round256(M*K) + round256(N*K) <= Y_B200_STATIC_OPERAND_BYTES (for
  * example 2048 x 2048 x 2048); larger problems return Y_B200_ERR_WORKSPACE and
- * must use y_b200_gemm_fp8_f32. The call itself makes no cudaMalloc / cudaFree
- * and uses no allocating library routine.
+ * must use y_b200_gemm_fp8_f32. The call itself makes no cudaMalloc / cudaFree,
+ * uses no allocating library routine and does not synchronise: it enqueues
+ * three kernels on `stream` and returns.
  * The first call on each device looks up the array's device address (with that
  * device current); make that first call before any stream capture begins.
  * All calls on a device share the one array and it keeps the last call's
  * contents: calls that can overlap on the GPU (different streams, different
- * threads) race on it and must be serialised by the caller. A bounded wait that
- * runs out is recorded inside the array, not in the word y_b200_device_status
- * reads; the next call on an idle stream reports it as Y_B200_ERR_DEVICE. */
+ * threads) race on it and must be serialised by the caller. Nothing in the
+ * array needs clearing between calls. A bounded wait that runs out is recorded
+ * in a status word inside the array (the first report is kept) and is read and
+ * cleared by y_b200_device_status like the other entries' reports. */
 #define Y_B200_STATIC_OPERAND_BYTES (8u << 20)
 Y_B200_API int y_b200_gemm_fp8_f32_static(const float* a, const float* b, float scale_a, float scale_b,
                                           float* c, int m, int n, int k, void* stream);
@@ -282,10 +350,11 @@ Y_B200_API int y_b200_peer_read(void* host_dst, const void* device_src, size_t b
 Y_B200_API int y_b200_fill_random_f16(void* out_f16, size_t n, uint64_t index0, uint64_t seed, void* stream);
 
 /* ---- c_api.rs symbols (src/c_api.rs:27-212) -----------------------------------
- * Strings returned by these are owned by the library; free with y_free_string. */
+ * Strings returned by these are owned by the library; free with y_free_string.
+ * is_fp8 is one byte, as the reference's `bool` (src/c_api.rs:109, :183). */
 Y_B200_API char* y_compile_to_ptx(const char* source, const char* target_sm, char** error_out);
-Y_B200_API char* y_autotune_search_space_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8);
-Y_B200_API char* y_autotune_select_config_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8);
+Y_B200_API char* y_autotune_search_space_json(uint32_t m, uint32_t n, uint32_t k, bool is_fp8);
+Y_B200_API char* y_autotune_select_config_json(uint32_t m, uint32_t n, uint32_t k, bool is_fp8);
 Y_B200_API int32_t y_interpret_kernel(const char* source, char** error_out);
 Y_B200_API uint32_t y_block_cdiv(uint32_t a, uint32_t b);
 Y_B200_API void y_free_string(char* s);

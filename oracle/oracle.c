@@ -438,7 +438,10 @@ void orc_paged_decode_attention(const uint16_t* q, const uint16_t* kcache, const
 #pragma omp parallel for collapse(2) schedule(dynamic)
     for (int s = 0; s < num_seqs; ++s)
         for (int h = 0; h < num_q_heads; ++h) {
-            const int len = seq_lens[s], kvh = h / group;
+            /* lengths are clamped to what the page table can address, as the device kernel does */
+            int len = seq_lens[s] < 0 ? 0 : seq_lens[s];
+            if ((long long)len > (long long)max_pages * page_size) len = max_pages * page_size;
+            const int kvh = h / group;
             uint16_t* o = out + ((size_t)s * num_q_heads + h) * head_dim;
             if (len <= 0) {
                 for (int d = 0; d < head_dim; ++d) o[d] = 0;

@@ -118,6 +118,16 @@ def test_other_reference_shapes_are_classified():
     ]:
         text = runtime.compile_to_ptx(f"@tile(512, 512, 512)\nkernel {name}({params}) {{\n}}\n")
         assert f"entry={name} family={fam}" in text
+        # the descriptor names the kernel that really runs, its workspace and the fused-epilogue count
+        assert "tcgen05.mma.cta_group::1.kind::f16" in text and "Workspace required:" in text
+        assert ("Fused epilogues: 0" if fam == "gemm_f16" else "Fused epilogues: 1") in text
+    # decode shapes of the plain F16 GEMM stream the row-major weights: no workspace, no tcgen05 claim
+    dec = runtime.compile_to_ptx("@tile(8, 4096, 4096)\nkernel gemm_f16_decode_m8(A: GlobalMemory<F16>, "
+                                 "B: GlobalMemory<F16>, C: GlobalMemory<F32>) {\n}\n")
+    assert "weight streaming" in dec and "Workspace required: 0 bytes" in dec and "tcgen05" not in dec
+    out = (C.c_uint32 * 4)()
+    assert lib.y_parse_launch_config(dec.encode(), 8, 4096, out) == 0
+    assert (out[0], out[1], out[2], out[3]) == (128, 1, 256, 81920)
     rms = ("kernel rmsnorm_residual_4096(X: GlobalMemory<F16>, Residual: GlobalMemory<F16>, "
            "Weight: GlobalMemory<F16>, Out: GlobalMemory<F16>, NewResidual: GlobalMemory<F16>) {\n}\n")
     assert "family=rmsnorm_residual" in runtime.compile_to_ptx(rms)
@@ -135,6 +145,14 @@ def test_argument_errors_are_codes_not_crashes():
     assert lib.y_b200_gemm_fp8_f32_workspace_bytes(256, 256, 256) == 2 * 65536 + 256
     assert lib.y_b200_swiglu_workspace_bytes(4096, 22016) == 256 + 4096 * 11008 * 2
     assert lib.y_b200_rmsnorm_workspace_bytes(8192) == 8192 * 4 + 256
+    assert lib.y_b200_gemm_f16_rowmajor_workspace_bytes(4096, 4096) == 4096 * 4096 * 2
+    assert lib.y_b200_gemm_f16_swiglu_workspace_bytes(11008, 4096) == 2 * 11008 * 4096 * 2
+    assert lib.y_b200_gemm_f16(None, None) == _lib.ERR_INVALID
+    assert lib.y_b200_gemm_f16_decode(None, 0, None, None, 0, 1, 8, 16, None) == _lib.ERR_INVALID
+    one = C.c_int(0)
+    p = C.addressof(one)
+    assert lib.y_b200_gemm_f16_decode(p, 4096, p, p, _lib.F32, 33, 4096, 4096, None) == _lib.ERR_SHAPE
+    assert lib.y_b200_gemm_f16_decode(p, 4096, p, p, _lib.F32, 1, 4096, 4100, None) == _lib.ERR_SHAPE
     assert b"sm_100a" in lib.y_b200_version()
 
 
@@ -145,7 +163,17 @@ def test_context_creation_never_aborts_without_a_device():
     assert runtime.CudaContext.new() is None  # src/cuda_runtime.rs:330-364
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/tests"), reason="the reference checkout is not on this machine")
+def _reference_tests_dir():
+    """The reference checkout's tests/ directory: $Y_REFERENCE_ROOT, else a directory named
+    `reference` beside the repository; None when neither exists (the GPU box has none)."""
+    roots = [os.environ.get("Y_REFERENCE_ROOT"), os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference")]
+    for r in roots:
+        if r and os.path.isdir(os.path.join(r, "tests")):
+            return os.path.join(os.path.abspath(r), "tests")
+    return None
+
+
+@pytest.mark.skipif(_reference_tests_dir() is None, reason="the reference checkout is not on this machine")
 def test_the_references_own_kernel_fixtures_compile_to_the_right_family():
     """Every .ysu kernel fixture of the reference goes through y_compile_to_ptx verbatim and
     lands in the family its name says (a CPU-side check: the GPU box has no reference tree)."""
@@ -155,7 +183,7 @@ def test_the_references_own_kernel_fixtures_compile_to_the_right_family():
               ("rmsnorm_residual_", "rmsnorm_residual"), ("rope_", "rope"),
               ("paged_decode_attention_", "paged_decode_attention"))
     seen = 0
-    for path in sorted(glob.glob("/root/reference/tests/*.ysu")):
+    for path in sorted(glob.glob(os.path.join(_reference_tests_dir(), "*.ysu"))):
         stem = os.path.basename(path)[:-4]
         fam = next((f for prefix, f in expect if stem.startswith(prefix)), None)
         if fam is None:

@@ -33,6 +33,35 @@ def test_forward_matches_the_oracle_chain(layer_and_inputs):
     assert_gemm_close(to_f64(host_bits(c), oracle.OUT_BF16), to_f64(ref, oracle.OUT_BF16))
 
 
+def test_step_at_the_benchmark_shape(cuda):
+    """The column-parallel step at its full size (M = K = N = 8192): the RMSNorm -> e4m3 prologue
+    bit-exact on the whole tensor (codes and scale), whole GEMM rows from several M tiles against
+    the oracle, and repeated steps bit-identical."""
+    from y_b200 import colpar, quant as q
+    m = k = n = 8192
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234)
+    x = torch.randn(m, k, device="cuda", dtype=torch.float16, generator=g)
+    gamma = (torch.rand(k, device="cuda", generator=g) + 0.5).to(torch.float16)
+    w = torch.randn(k, n, device="cuda", dtype=torch.float16, generator=g)
+    bqt, sb = q.quantize_fp8_dynamic(w, transpose=True)
+    del w
+    layer = colpar.ColumnParallelFp8Linear(bqt, sb, gamma, 1e-6, m)
+    c = layer.forward(x).clone()
+    q.device_status()
+    x_h, g_h = host_bits(x), host_bits(gamma)
+    aq_ref, sa_ref = oracle.rmsnorm_quantize_fp8(x_h, g_h, 1e-6)
+    aq_dev, sa_dev = q.rmsnorm_quantize_fp8(x, gamma, 1e-6)
+    assert sa_dev.item() == np.float32(sa_ref)
+    assert np.array_equal(aq_dev.cpu().numpy(), aq_ref)
+    bqt_h = bqt.cpu().numpy()
+    for r in (0, 129, 2047, 2048, 4100, 6000, 8063, 8191):
+        ref = oracle.gemm_fp8(aq_ref, bqt_h, sa_ref, sb.item(), out_kind=oracle.OUT_BF16, row_begin=r, row_count=1)
+        assert_gemm_close(to_f64(host_bits(c[r:r + 1]), oracle.OUT_BF16), to_f64(ref, oracle.OUT_BF16), f"row {r}")
+    for _ in range(2):
+        assert torch.equal(layer.forward(x), c)
+
+
 def test_host_pipeline_equals_device_path_step_by_step(layer_and_inputs):
     layer, xs, g, bqt_h, sb, q = layer_and_inputs
     m, k, n = layer.m, layer.k, layer.n_shard

@@ -201,6 +201,35 @@ def test_full_size_4096_sampled_rows_and_linearity(q):
     assert torch.allclose(ct.t(), c1, rtol=0, atol=0)
 
 
+def test_swiglu_requant_at_the_benchmark_shape_sampled_rows(q):
+    """The fused SwiGLU configuration at its full size: M = K = 4096, N = 2 x 11008 gate|up
+    interleaved (1376 tiles over 74 CTA pairs: 18 full waves and a partial one), bf16 h with a
+    running amax, then e4m3 re-quantisation. Whole rows from several M tiles against the oracle;
+    the re-quantisation of the whole tensor bit-exact given the device's h."""
+    m, k, n = 4096, 4096, 22016
+    g = torch.Generator(device="cuda")
+    g.manual_seed(44)
+    a = torch.randn(m, k, device="cuda", dtype=torch.float16, generator=g)
+    w = (torch.randn(k, n, device="cuda", generator=g) / 64).to(torch.float16)
+    aq, sa = q.quantize_fp8_dynamic(a)
+    bqt, sb = q.quantize_fp8_dynamic(w, transpose=True)
+    del a, w
+    codes, scale, h = q.gemm_fp8_swiglu_requant(aq, bqt, sa, sb)
+    q.device_status()
+    aq_h, bqt_h = aq.cpu().numpy(), bqt.cpu().numpy()
+    h_got = host_bits(h)
+    assert h_got.shape == (m, n // 2)
+    for r in (0, 255, 256, 1000, 2047, 2048, 3333, 4095):
+        ref = oracle.gemm_fp8(aq_h, bqt_h, sa.item(), sb.item(), epilogue=oracle.EPI_SWIGLU,
+                              out_kind=oracle.OUT_BF16, row_begin=r, row_count=1)
+        assert_gemm_close(to_f64(h_got[r:r + 1], oracle.OUT_BF16), to_f64(ref, oracle.OUT_BF16), f"h row {r}")
+    q_ref, s_ref = oracle.requant_bf16_fp8(h_got)
+    assert scale.item() == np.float32(s_ref)
+    assert np.array_equal(codes.cpu().numpy(), q_ref)
+    # the running amax the epilogue kept equals the maximum of what it stored
+    assert np.float32(s_ref) == np.float32(oracle.scale_from_amax(float(np.abs(to_f64(h_got, oracle.OUT_BF16)).max())))
+
+
 def test_preconditions_are_errors(q):
     from y_b200._lib import YB200Error, ERR_SHAPE, ERR_INVALID
     a = torch.zeros(16, 24, dtype=torch.uint8, device="cuda")

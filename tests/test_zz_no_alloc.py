@@ -12,18 +12,29 @@ from helpers import assert_gemm_close
 pytestmark = pytest.mark.gpu
 
 
-def _pair(m, n, k, seed):
-    from y_b200 import quant as q
-    from y_b200._lib import check, lib
+def _inputs(m, n, k, seed):
     g = torch.Generator(device="cuda")
     g.manual_seed(seed)
     a = torch.randn(m, k, device="cuda", generator=g) * 3
     b = torch.randn(k, n, device="cuda", generator=g) * 3
     sa, sb = float(a.abs().max()) / 448.0, float(b.abs().max()) / 448.0
-    want = q.gemm_fp8_f32(a, b, sa, sb)                      # existing entry: caller-provided workspace
-    got = torch.full((m, n), float("nan"), device="cuda")
+    return a, b, sa, sb
+
+
+def _static_call(a, b, sa, sb, got):
+    from y_b200._lib import check, lib
+    m, k = a.shape
+    n = b.shape[1]
     check(lib.y_b200_gemm_fp8_f32_static(a.data_ptr(), b.data_ptr(), sa, sb, got.data_ptr(), m, n, k,
                                          torch.cuda.current_stream().cuda_stream))
+
+
+def _pair(m, n, k, seed):
+    from y_b200 import quant as q
+    a, b, sa, sb = _inputs(m, n, k, seed)
+    want = q.gemm_fp8_f32(a, b, sa, sb)                      # existing entry: caller-provided workspace
+    got = torch.full((m, n), float("nan"), device="cuda")
+    _static_call(a, b, sa, sb, got)
     torch.cuda.synchronize()
     return got.cpu().numpy(), want.cpu().numpy()
 
@@ -35,7 +46,22 @@ def test_two_calls_in_a_row_match_the_workspace_entry(cuda):
         got, want = _pair(m, n, k, seed)
         assert_gemm_close(got, want, f"{m}x{n}x{k}")
     from y_b200 import quant as q
-    q.device_status()
+    q.device_status()   # also reads the status word that lives inside the built-in scratch
+
+
+def test_calls_leave_free_device_memory_unchanged(cuda):
+    # What the entry is for: once the module is loaded (the warm-up call below, which is
+    # also when the built-in array is reserved), further calls take no device memory.
+    a, b, sa, sb = _inputs(256, 256, 256, 3)
+    got = torch.empty(256, 256, device="cuda")
+    _static_call(a, b, sa, sb, got)                           # warm-up: module load, address lookup
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(2):
+        _static_call(a, b, sa, sb, got)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
 
 
 def test_sizes_beyond_the_built_in_scratch_are_refused(cuda):

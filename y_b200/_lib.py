@@ -40,11 +40,23 @@ class GemmFp8Args(C.Structure):
     ]
 
 
+class GemmF16Args(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("bt", C.c_void_p), ("c", C.c_void_p),
+        ("m", C.c_int), ("n", C.c_int), ("k", C.c_int),
+        ("alpha", C.c_float),
+        ("bias", C.c_void_p), ("bias_kind", C.c_int),
+        ("epilogue", C.c_int), ("out_kind", C.c_int),
+        ("cta_n", C.c_int), ("max_ctas", C.c_int), ("cta_m", C.c_int),
+    ]
+
+
 class LaunchInfo(C.Structure):
     _fields_ = [
         ("grid", C.c_uint * 3), ("block", C.c_uint * 3), ("cluster", C.c_uint * 3),
         ("dyn_smem_bytes", C.c_uint), ("workspace_bytes", C.c_size_t),
         ("cta_m", C.c_int), ("cta_n", C.c_int), ("cta_k", C.c_int), ("stages", C.c_int),
+        ("fused_epilogues", C.c_int),
     ]
 
 
@@ -78,6 +90,14 @@ SIGNATURES = {
     "y_b200_gemm_fp8_f32_workspace_bytes": (_sz, [_i, _i, _i]),
     "y_b200_gemm_fp8_f32": (_i, [_vp, _vp, _f, _f, _vp, _i, _i, _i, _vp, _sz, _vp]),
     "y_b200_gemm_fp8_f32_static": (_i, [_vp, _vp, _f, _f, _vp, _i, _i, _i, _vp]),
+    "y_b200_gemm_f16": (_i, [C.POINTER(GemmF16Args), _vp]),
+    "y_b200_gemm_f16_rowmajor_workspace_bytes": (_sz, [_i, _i]),
+    "y_b200_gemm_f16_rowmajor": (_i, [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    "y_b200_gemm_f16_swiglu_workspace_bytes": (_sz, [_i, _i]),
+    "y_b200_gemm_f16_swiglu": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _vp]),
+    "y_b200_gemm_f16_decode": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "y_b200_gemm_f16_splitk_workspace": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "y_b200_splitk_reduction": (_i, [_vp, _vp, _sz, _i, _i, _i, _vp]),
     "y_b200_swiglu_workspace_bytes": (_sz, [_i, _i]),
     "y_b200_gemm_fp8_swiglu_requant": (_i, [C.POINTER(GemmFp8Args), _vp, _vp, _vp, _sz, _vp]),
     "y_b200_mlp_workspace_bytes": (_sz, [_i, _i]),
@@ -99,8 +119,8 @@ SIGNATURES = {
     "y_b200_peer_read": (_i, [_vp, _vp, _sz]),
     "y_b200_fill_random_f16": (_i, [_vp, _sz, _u64, _u64, _vp]),
     "y_compile_to_ptx": (_vp, [C.c_char_p, C.c_char_p, C.POINTER(_vp)]),
-    "y_autotune_search_space_json": (_vp, [_u32, _u32, _u32, _i]),
-    "y_autotune_select_config_json": (_vp, [_u32, _u32, _u32, _i]),
+    "y_autotune_search_space_json": (_vp, [_u32, _u32, _u32, C.c_bool]),
+    "y_autotune_select_config_json": (_vp, [_u32, _u32, _u32, C.c_bool]),
     "y_interpret_kernel": (C.c_int32, [C.c_char_p, C.POINTER(_vp)]),
     "y_block_cdiv": (_u32, [_u32, _u32]),
     "y_free_string": (None, [_vp]),

@@ -91,7 +91,9 @@ __global__ void __launch_bounds__(kAttnThreads)
     const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
     const int group = p.num_q_heads / p.num_kv_heads;  // query heads per KV head, <= 16
     pdl_wait();  // q and the newest K/V rows come from the kernels before this one
-    const int seq_len = p.seq_lens[seq];
+    // A length beyond the page table's reach would index past this sequence's row of it;
+    // lengths are device data the host never sees, so they are clamped here.
+    const int seq_len = min(max(p.seq_lens[seq], 0), p.max_pages * p.page_size);
     const int tiles = (seq_len + kTileTokens - 1) / kTileTokens;
     const int tiles_per_split = (tiles + p.splits - 1) / p.splits;
     const int tile_begin = split * tiles_per_split;

@@ -245,13 +245,48 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         out += "// [Y PAGED DECODE ATTENTION] launch grid (num_q_heads, num_seqs, 1) as the reference entry; the library "
                "regroups the work per KV head and splits long sequences across CTAs itself\n";
     } else {
-        const uint32_t cta_k = 64;
-        snprintf(buf, sizeof buf,
-                 "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA 128x256x%u | 4x1 warps | "
-                 "tcgen05.mma.cta_group::1.kind::f16 f16 x f16 -> f32 (TMEM)\n",
-                 k.m, k.n, k.k, cta_k);
+        // F16 families. Decode shapes of the plain GEMM stream the row-major weights once through
+        // mma.sync; everything else copies the weights K-major and runs the tcgen05 kernels on rows
+        // of 2 K bytes (kind::f16), so the tile line below is the one of that launch.
+        const bool swiglu = fam == KernelFamily::GemmF16Swiglu;
+        const bool decode = fam == KernelFamily::GemmF16 && k.m <= 32 && k.k % 16 == 0 && k.n % 8 == 0;
+        if (decode) {
+            snprintf(buf, sizeof buf,
+                     "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %dx32x16 | 8x1 warps | "
+                     "weight streaming, mma.sync.m16n8k16 f16 x f16 -> f32, K split across the warps of a CTA\n"
+                     "// Launch grid required: (%lld, 1, 1) CTAs, block (256,1,1).\n"
+                     "// Dynamic shared memory required: 81920 bytes.\n"
+                     "// Workspace required: 0 bytes.\n",
+                     k.m, k.n, k.k, k.m <= 16 ? 16 : 32, (k.n + 31) / 32);
+        } else {
+            const long long n_eff = swiglu ? 2 * k.n : k.n;
+            Candidate c = autotune((uint32_t)k.m, (uint32_t)n_eff, (uint32_t)(2 * k.k), Precision::Fp8, "NVIDIA B200", 148);
+            const bool pair = c.cta_m == 256;
+            const long long tiles = ((k.m + c.cta_m - 1) / c.cta_m) * ((n_eff + c.cta_n - 1) / c.cta_n);
+            const long long ctas = pair ? 2 * tiles : tiles;
+            const long long cap = pair ? 148 & ~1 : 148;
+            const unsigned b_rows = pair ? 128u : c.cta_n;
+            const unsigned smem = c.num_stages * (128u * 128u + b_rows * 128u) + (2 * c.num_stages + 4) * 8 + 16 + 4096 + 8 * 2048 + 1024;
+            const size_t ws = (size_t)(swiglu ? 2 : 1) * (size_t)k.n * (size_t)k.k * 2;
+            snprintf(buf, sizeof buf,
+                     "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %ux%ux%u | %ux%u warps | "
+                     "tcgen05.mma.cta_group::%d.kind::f16 f16 x f16 -> f32 (TMEM)%s\n"
+                     "// The row-major weights are copied K-major into the workspace by one HBM-bound kernel per launch.\n"
+                     "// Launch grid required: (%lld, 1, 1) CTAs, block (320,1,1), cluster (%d,1,1); persistent over %lld tiles, %u stages.\n"
+                     "// Dynamic shared memory required: %u bytes.\n"
+                     "// Workspace required: %zu bytes.\n",
+                     k.m, k.n, k.k, c.cta_m, c.cta_n, c.cta_k / 2, c.warps_m, c.warps_n, pair ? 2 : 1,
+                     swiglu ? " | Out=SiLU(X@Wgate)*(X@Wup), gate|up interleaved" : (fam == KernelFamily::GemmF16BiasRelu ? " | +bias, ReLU" : ""),
+                     ctas < cap ? ctas : cap, pair ? 2 : 1, tiles, c.num_stages, smem, (ws + 255) & ~(size_t)255);
+        }
         out += buf;
     }
+    // EpilogueFusionPass's statistic (src/quantization_pass.rs:802-819): activations fused into
+    // the accumulator write-back of this kernel.
+    const int fused = fam == KernelFamily::GemmF16BiasRelu || fam == KernelFamily::GemmF16Swiglu ? 1 : 0;
+    snprintf(buf, sizeof buf, "// Fused epilogues: %d%s\n", fused,
+             fam == KernelFamily::GemmF16BiasRelu ? " (ReLU)" : fam == KernelFamily::GemmF16Swiglu ? " (SiLU)" : "");
+    out += buf;
     return out;
 }
 
@@ -309,24 +344,24 @@ static std::string candidate_json(const Candidate& c, int with_fp8, bool is_fp8)
 
 // is_fp8 == 0 selects the 16-bit namespace; decode shapes (M <= 32) there are
 // served by the INT4 weight-streaming kernel.
-static Precision precision_for(uint32_t m, int is_fp8) {
+static Precision precision_for(uint32_t m, bool is_fp8) {
     if (is_fp8) return Precision::Fp8;
     return m <= 32 ? Precision::Int4 : Precision::F16;
 }
 
-extern "C" char* y_autotune_search_space_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8) {
+extern "C" char* y_autotune_search_space_json(uint32_t m, uint32_t n, uint32_t k, bool is_fp8) {
     std::string out = "[";
     bool first = true;
     for (const Candidate& c : generate_candidates(m, n, k, precision_for(m, is_fp8))) {
         if (!first) out += ",";
         first = false;
-        out += candidate_json(c, 1, is_fp8 != 0);
+        out += candidate_json(c, 1, is_fp8);
     }
     out += "]";
     return dup_string(out);
 }
 
-extern "C" char* y_autotune_select_config_json(uint32_t m, uint32_t n, uint32_t k, int is_fp8) {
+extern "C" char* y_autotune_select_config_json(uint32_t m, uint32_t n, uint32_t k, bool is_fp8) {
     // The reference resolves against a default hardware profile here
     // (src/c_api.rs:183-185), not the GPU that happens to be present.
     Candidate c = autotune(m, n, k, precision_for(m, is_fp8), "NVIDIA B200", 148);

@@ -37,6 +37,7 @@ struct DeviceStatus {
     unsigned int extra;
 };
 DeviceStatus* device_status_ptr();  // per-device, allocated on first use
+DeviceStatus* static_entry_status_ptr();  // status word of the allocation-free GEMM entry; null until it has run
 
 #ifdef __CUDACC__
 
@@ -166,6 +167,17 @@ __device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, ui
         : "memory");
 }
 
+// The same for 16-bit operands (f16 x f16 -> f32): K = 16 elements per instruction, i.e. the
+// same 32 bytes of K as kind::f8f6f4, so operand tiles and descriptors are laid out alike.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // ---- CTA pairs (cta_group::2) --------------------------------------------------------
 // Two CTAs of a cluster share one MMA: the even-ranked CTA issues it, each CTA holds its
 // half of both operands in its own shared memory and its half of the accumulator rows
@@ -202,6 +214,14 @@ __device__ __forceinline__ void umma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_des
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }

@@ -88,15 +88,21 @@ extern "C" int y_b200_device_status(void* stream) {
     DeviceStatus* dptr = device_status_ptr();
     if (!dptr) return fail(Y_B200_ERR_CUDA, "y_b200_device_status: no CUDA device");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    DeviceStatus h;
-    YB_CUDA(cudaMemcpyAsync(&h, dptr, sizeof h, cudaMemcpyDeviceToHost, st));
+    // Two words: the one every workspace-taking entry reports into, and the one inside the
+    // allocation-free entry's built-in scratch (present once that entry has run here).
+    DeviceStatus* words[2] = {dptr, static_entry_status_ptr()};
+    DeviceStatus h[2] = {};
+    for (int i = 0; i < 2; ++i)
+        if (words[i]) YB_CUDA(cudaMemcpyAsync(&h[i], words[i], sizeof h[i], cudaMemcpyDeviceToHost, st));
     YB_CUDA(cudaStreamSynchronize(st));
-    if (h.code == 0) return 0;
-    YB_CUDA(cudaMemsetAsync(dptr, 0, sizeof h, st));
+    if (h[0].code == 0 && h[1].code == 0) return 0;
+    for (int i = 0; i < 2; ++i)
+        if (h[i].code != 0) YB_CUDA(cudaMemsetAsync(words[i], 0, sizeof h[i], st));
     YB_CUDA(cudaStreamSynchronize(st));
+    const int w = h[0].code != 0 ? 0 : 1;
     return fail(Y_B200_ERR_DEVICE,
-                "device wait ran out: code %u at role/barrier 0x%x, CTA %u, detail %u", h.code,
-                h.where, h.block, h.extra);
+                "device wait ran out%s: code %u at role/barrier 0x%x, CTA %u, detail %u",
+                w == 1 ? " in y_b200_gemm_fp8_f32_static" : "", h[w].code, h[w].where, h[w].block, h[w].extra);
 }
 
 // ---- peer memory (CUDA IPC) -----------------------------------------------------------------

@@ -42,7 +42,7 @@
 namespace yb {
 
 int quantize_with_host_scale(const void* x, int kind, size_t rows, size_t cols, bool transpose,
-                             float scale, float* scale_slot, void* q, cudaStream_t st);
+                             float scale, void* q, cudaStream_t st);
 int quantize_from_amax(const void* x, int kind, size_t n, const float* amax, void* q,
                        float* scale_out, cudaStream_t st);
 
@@ -68,6 +68,8 @@ constexpr int kSwizzleGroup = 8;  // M-tiles per raster group
 struct GemmParams {
     void* c;
     int m, n, k;
+    int k_bytes;       // bytes of K in an operand row: K for e4m3 operands, 2 K for f16 operands
+    int f16_operands;  // 0: e4m3 x e4m3 (kind::f8f6f4); 1: f16 x f16 (kind::f16). Same tiles, same descriptors.
     float scale_a, scale_b;
     const float* scale_a_dev;
     const float* scale_b_dev;
@@ -211,27 +213,43 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
         if (EPI == Y_B200_EPI_SWIGLU) {
             // columns 2j (gate) and 2j+1 (up) -> output column col0/2 + j
             float h[16];
-            uint32_t packed[8];
 #pragma unroll
             for (int j = 0; j < 16; ++j) h[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+            if constexpr (OUT == Y_B200_F32) {
+                // f32 output (the reference's gemm_f16_swiglu entries): no re-quantisation follows,
+                // so no running amax either.
+                if (row < p.m) {
+                    const int ocol0 = col0 / 2;
+                    float* dst = static_cast<float*>(p.c) + (size_t)row * n_out + ocol0;
+                    if (rows_aligned && col0 + 32 <= p.n) {
+                        store_vec<Y_B200_F32, 16>(dst, h);
+                    } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                packed[j] = pack_bf16x2(h[2 * j], h[2 * j + 1]);
-                // amax over the bf16-rounded values, as f32 bit patterns
-                amax_bits = max(amax_bits, (packed[j] << 16) & 0x7fffffffu);
-                amax_bits = max(amax_bits, packed[j] & 0x7fff0000u);
-            }
-            if (row < p.m) {
-                const int ocol0 = col0 / 2;
-                __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + (size_t)row * n_out + ocol0;
-                if (rows_aligned && col0 + 32 <= p.n) {
-                    uint4* d = reinterpret_cast<uint4*>(dst);
-                    d[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    d[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                } else {
+                        for (int j = 0; j < 16; ++j)
+                            if (ocol0 + j < n_out) dst[j] = h[j];
+                    }
+                }
+            } else {
+                uint32_t packed[8];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (ocol0 + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
+                for (int j = 0; j < 8; ++j) {
+                    packed[j] = pack_bf16x2(h[2 * j], h[2 * j + 1]);
+                    // amax over the bf16-rounded values, as f32 bit patterns
+                    amax_bits = max(amax_bits, (packed[j] << 16) & 0x7fffffffu);
+                    amax_bits = max(amax_bits, packed[j] & 0x7fff0000u);
+                }
+                if (row < p.m) {
+                    const int ocol0 = col0 / 2;
+                    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + (size_t)row * n_out + ocol0;
+                    if (rows_aligned && col0 + 32 <= p.n) {
+                        uint4* d = reinterpret_cast<uint4*>(dst);
+                        d[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        d[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (ocol0 + j < n_out) dst[j] = __float2bfloat16_rn(h[j]);
+                    }
                 }
             }
         } else if (row < p.m) {
@@ -302,7 +320,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = p.m_tiles * p.n_tiles;
-    const int num_kb = (p.k + kCtaK - 1) / kCtaK;
+    const int num_kb = (p.k_bytes + kCtaK - 1) / kCtaK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::stages; ++s) {
@@ -380,12 +398,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const uint32_t a_addr = ring0 + stage * Cfg::stage_bytes;
                     const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
                     const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + Cfg::a_bytes);
+                    // +32 bytes of K inside the swizzle span = +2 in 16-byte units.
+                    if (p.f16_operands) {
 #pragma unroll
-                    for (int k = 0; k < kCtaK / kUmmaK; ++k) {
-                        // +32 bytes of K inside the swizzle span = +2 in 16-byte units.
-                        umma_f8f6f4(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
-                                    b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc,
-                                    (uint32_t)((kb | k) != 0));
+                        for (int k = 0; k < kCtaK / kUmmaK; ++k)
+                            umma_f16(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)), b_desc + (uint64_t)(k * (kUmmaK >> 4)),
+                                     idesc, (uint32_t)((kb | k) != 0));
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < kCtaK / kUmmaK; ++k)
+                            umma_f8f6f4(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
+                                        b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc, (uint32_t)((kb | k) != 0));
                     }
                     tc_commit(empty0 + 8 * stage);  // frees the stage once the MMAs have read it
                     if (++stage == Cfg::stages) { stage = 0; phase ^= 1u; }
@@ -506,7 +529,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int num_units = p.units;
-    const int num_kb = (p.k + kCtaK - 1) / kCtaK;
+    const int num_kb = (p.k_bytes + kCtaK - 1) / kCtaK;
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
@@ -586,10 +609,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const uint32_t a_addr = ring0 + stage * kPairStageBytes;
                     const uint64_t a_desc = make_kmajor_sw128_desc(a_addr);
                     const uint64_t b_desc = make_kmajor_sw128_desc(a_addr + kCtaM * kCtaK);
+                    if (p.f16_operands) {
 #pragma unroll
-                    for (int k = 0; k < kCtaK / kUmmaK; ++k)
-                        umma_f8f6f4_pair(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
-                                         b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc, (uint32_t)((kb | k) != 0));
+                        for (int k = 0; k < kCtaK / kUmmaK; ++k)
+                            umma_f16_pair(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
+                                          b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc, (uint32_t)((kb | k) != 0));
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < kCtaK / kUmmaK; ++k)
+                            umma_f8f6f4_pair(d_tmem, a_desc + (uint64_t)(k * (kUmmaK >> 4)),
+                                             b_desc + (uint64_t)(k * (kUmmaK >> 4)), idesc, (uint32_t)((kb | k) != 0));
+                    }
                     tc_commit_pair(empty0 + 8 * stage, 3);  // both CTAs' stages are free again
                     if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
                 }
@@ -668,7 +698,9 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// K-major e4m3 matrix [rows, k]; box = 128 bytes of K x box_rows rows.
+// K-major operand matrix [rows, k bytes of K]; box = 128 bytes of K x box_rows rows. The map is
+// byte-typed for both operand kinds: the 128-byte swizzle permutes 16-byte units, so an f16 row
+// of K elements is a row of 2 K bytes.
 int make_operand_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(Y_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -746,8 +778,9 @@ int launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
         case Y_B200_EPI_BIAS: return launch_out<BN, Y_B200_EPI_BIAS>(ta, tb, p, out_kind, grid, st);
         case Y_B200_EPI_BIAS_RELU: return launch_out<BN, Y_B200_EPI_BIAS_RELU>(ta, tb, p, out_kind, grid, st);
         case Y_B200_EPI_SWIGLU:
+            if (out_kind == Y_B200_F32) return launch_one<BN, Y_B200_EPI_SWIGLU, Y_B200_F32>(ta, tb, p, grid, st);
             if (out_kind != Y_B200_BF16)
-                return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: the SwiGLU epilogue writes bf16");
+                return fail(Y_B200_ERR_INVALID, "the SwiGLU epilogue writes bf16 (with a running amax) or f32");
             return launch_one<BN, Y_B200_EPI_SWIGLU, Y_B200_BF16>(ta, tb, p, grid, st);
     }
     return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad epilogue %d", epi);
@@ -787,8 +820,9 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
         case Y_B200_EPI_BIAS: return launch_pair_out<Y_B200_EPI_BIAS>(ta, tb, tbh, p, out_kind, grid, st);
         case Y_B200_EPI_BIAS_RELU: return launch_pair_out<Y_B200_EPI_BIAS_RELU>(ta, tb, tbh, p, out_kind, grid, st);
         case Y_B200_EPI_SWIGLU:
+            if (out_kind == Y_B200_F32) return launch_pair_one<Y_B200_EPI_SWIGLU, Y_B200_F32>(ta, tb, tbh, p, grid, st);
             if (out_kind != Y_B200_BF16)
-                return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: the SwiGLU epilogue writes bf16");
+                return fail(Y_B200_ERR_INVALID, "the SwiGLU epilogue writes bf16 (with a running amax) or f32");
             return launch_pair_one<Y_B200_EPI_SWIGLU, Y_B200_BF16>(ta, tb, tbh, p, grid, st);
     }
     return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bad epilogue %d", epi);
@@ -848,8 +882,8 @@ int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, in
     int rc;
     // Every CTA loads 128 rows of A; of B it loads its whole N tile, or its 128-row half
     // of the pair's 256.
-    if ((rc = make_operand_map(&ta, a, p.m, p.k, kCtaM))) return rc;
-    if ((rc = make_operand_map(&tb, bt, p.n, p.k, tile.cta_m == 256 ? 128 : tile.cta_n))) return rc;
+    if ((rc = make_operand_map(&ta, a, p.m, p.k_bytes, kCtaM))) return rc;
+    if ((rc = make_operand_map(&tb, bt, p.n, p.k_bytes, tile.cta_m == 256 ? 128 : tile.cta_n))) return rc;
     p.m_tiles = (p.m + tile.cta_m - 1) / tile.cta_m;
     p.n_tiles = (p.n + tile.cta_n - 1) / tile.cta_n;
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
@@ -868,7 +902,7 @@ int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, in
         p.full_units = pu.full_units;
         p.units = pu.units;
         CUtensorMap tbh;  // 64-row B boxes for half tiles
-        if ((rc = make_operand_map(&tbh, bt, p.n, p.k, 64))) return rc;
+        if ((rc = make_operand_map(&tbh, bt, p.n, p.k_bytes, 64))) return rc;
         const int grid = (int)(2LL * p.units < cap ? 2LL * p.units : cap);
         return launch_pair(ta, tb, tbh, p, epi, out_kind, grid, st);
     }
@@ -900,6 +934,7 @@ extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
     GemmParams p = {};
     p.c = a->c;
     p.m = a->m; p.n = a->n; p.k = a->k;
+    p.k_bytes = a->k;
     p.scale_a = a->scale_a; p.scale_b = a->scale_b;
     p.scale_a_dev = a->scale_a_dev; p.scale_b_dev = a->scale_b_dev;
     p.bias = a->bias; p.bias_kind = a->bias_kind;
@@ -907,6 +942,48 @@ extern "C" int y_b200_gemm_fp8(const y_b200_gemm_fp8_args* a, void* stream) {
     p.status = device_status_ptr();
     p.n_rep = a->c_replica_count;
     for (int d = 0; d < p.n_rep; ++d) p.c_rep[d] = a->c_replicas[d];
+    return launch_tiled(a->a, a->bt, p, tile, a->epilogue, a->out_kind, a->max_ctas, st);
+}
+
+// F16-operand form of the same kernels (the reference's gemm_f16_<tag> family,
+// src/ptx_emitter.rs:4199-4694): A [M, K] and Bt [N, K] are K-major f16, the MMA is
+// tcgen05.mma.kind::f16 with f32 accumulation in tensor memory, the epilogues are the same.
+extern "C" int y_b200_gemm_f16(const y_b200_gemm_f16_args* a, void* stream) {
+    if (!a) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: null argument block");
+    if (!a->a || !a->bt || !a->c) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: null operand pointer");
+    if (a->m < 1 || a->n < 1 || a->k < 1)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16: M, N, K must be positive (M=%d N=%d K=%d)", a->m, a->n, a->k);
+    if (a->k % 8 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16: K=%d must be a multiple of 8 (operand rows are 16-byte aligned for TMA)", a->k);
+    if (a->k > 0x3fffffff) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16: K too large");
+    if ((reinterpret_cast<uintptr_t>(a->a) & 15u) || (reinterpret_cast<uintptr_t>(a->bt) & 15u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_f16: a and bt must be 16-byte aligned");
+    if (a->epilogue == Y_B200_EPI_BIAS || a->epilogue == Y_B200_EPI_BIAS_RELU) {
+        if (!a->bias) return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: bias epilogue without a bias pointer");
+        if (a->bias_kind != Y_B200_F16 && a->bias_kind != Y_B200_F32)
+            return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: bias_kind must be F16 or F32");
+    }
+    if (a->epilogue == Y_B200_EPI_SWIGLU && a->n % 2 != 0)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16: SwiGLU needs an even N (gate|up pairs), got %d", a->n);
+    if (a->cta_n != 0 && a->cta_n != 64 && a->cta_n != 128 && a->cta_n != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: cta_n must be 0, 64, 128 or 256");
+    if (a->cta_m != 0 && a->cta_m != 128 && a->cta_m != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: cta_m must be 0, 128 or 256");
+    if (a->cta_m == 256 && a->cta_n != 0 && a->cta_n != 256)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: cta_m 256 (CTA pair) needs cta_n 0 or 256");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The tile table is keyed by bytes of K (what a stage holds), so an f16 problem
+    // borrows the entry of the e4m3 problem with twice its K.
+    const TileShape tile = pick_tile(a->m, a->n, 2 * a->k, a->cta_m, a->cta_n);
+    GemmParams p = {};
+    p.c = a->c;
+    p.m = a->m; p.n = a->n; p.k = a->k;
+    p.k_bytes = 2 * a->k;
+    p.f16_operands = 1;
+    p.scale_a = a->alpha != 0.0f ? a->alpha : 1.0f;
+    p.scale_b = 1.0f;
+    p.bias = a->bias; p.bias_kind = a->bias_kind;
+    p.status = device_status_ptr();
     return launch_tiled(a->a, a->bt, p, tile, a->epilogue, a->out_kind, a->max_ctas, st);
 }
 
@@ -932,6 +1009,7 @@ extern "C" int y_b200_gemm_fp8_launch_info(int m, int n, int k, int cta_n, y_b20
     out->workspace_bytes = 0;
     out->cta_m = tile.cta_m; out->cta_n = tile.cta_n; out->cta_k = kCtaK;
     out->stages = pair ? kPairStages : stages_for(tile.cta_n);
+    out->fused_epilogues = 0;
     return 0;
 }
 
@@ -961,10 +1039,9 @@ extern "C" int y_b200_gemm_fp8_f32(const float* a, const float* b, float scale_a
     const size_t a_bytes = ((size_t)m * k + 255) & ~(size_t)255, b_bytes = ((size_t)n * k + 255) & ~(size_t)255;
     void* aq = ws;
     void* bq = ws + a_bytes;
-    float* slots = reinterpret_cast<float*>(ws + a_bytes + b_bytes);
-    int rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, slots, aq, st);
+    int rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, aq, st);
     if (rc) return rc;
-    rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, slots + 1, bq, st);
+    rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, bq, st);
     if (rc) return rc;
     y_b200_gemm_fp8_args g = {};
     g.a = aq; g.bt = bq; g.c = c;
@@ -1056,34 +1133,48 @@ extern "C" int y_b200_mlp_swiglu_fp8(const void* a, float scale_a, const float* 
 namespace yb {
 namespace {
 
-constexpr size_t kStaticHeader = 256;                       // status word + two scale slots
+constexpr size_t kStaticHeader = 256;                       // the status word of this entry's launches
 constexpr size_t kStaticOperandBytes = Y_B200_STATIC_OPERAND_BYTES;  // e4m3 copies of A and Bt together
 constexpr size_t kStaticScratchBytes = kStaticHeader + kStaticOperandBytes;
 
 // In host code this name is only a handle for the runtime; the device address
-// is obtained once per device with cudaGetSymbolAddress (below).
+// is obtained once per device with cudaGetSymbolAddress (below). The array is
+// part of the module image: the device memory behind it is reserved when the
+// module is loaded on a device (with lazy loading: on the first call that
+// touches this file's kernels or this symbol), not per call.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mu;
+unsigned char* g_static_ptrs[64] = {};
 
 // Device address of g_static_scratch on the current device, looked up on the
 // first call on that device (with that device current) and cached.
 int static_scratch_ptr(unsigned char** out) {
-    static std::mutex mu;
-    static unsigned char* ptrs[64] = {};
     int dev = 0;
     YB_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(Y_B200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-    std::lock_guard<std::mutex> lock(mu);
-    if (ptrs[dev] == nullptr) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptrs[dev] == nullptr) {
         void* p = nullptr;
         YB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
         if (p == nullptr) return fail(Y_B200_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
-        ptrs[dev] = static_cast<unsigned char*>(p);
+        g_static_ptrs[dev] = static_cast<unsigned char*>(p);
     }
-    *out = ptrs[dev];
+    *out = g_static_ptrs[dev];
     return 0;
 }
 
 }  // namespace
+
+// The status word of the allocation-free entry on the current device, or null while that
+// entry has not run there (the lookup itself is left to the entry's first call).
+DeviceStatus* static_entry_status_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    return reinterpret_cast<DeviceStatus*>(g_static_ptrs[dev]);
+}
+
 }  // namespace yb
 
 extern "C" int y_b200_gemm_fp8_f32_static(const float* a, const float* b, float scale_a, float scale_b,
@@ -1105,34 +1196,23 @@ extern "C" int y_b200_gemm_fp8_f32_static(const float* a, const float* b, float 
     int rc = static_scratch_ptr(&base);
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The scratch keeps the previous call's contents. Nothing in it has to start at
+    // zero: the operand areas are fully overwritten by the quantise kernels, and the
+    // status word is zero from module load until a bounded wait runs out, after which it
+    // keeps that first report (compare-and-swap) until y_b200_device_status reads and
+    // clears it. So the call enqueues three kernels and nothing else: no stream query,
+    // no copy, no memset, no synchronisation.
     DeviceStatus* status = reinterpret_cast<DeviceStatus*>(base);
-    float* slots = reinterpret_cast<float*>(base + 64);
     void* aq = base + kStaticHeader;
     void* bq = base + kStaticHeader + a_bytes;
-    // The scratch keeps the previous call's contents. If the stream is idle, look
-    // at what that call left in the status word (it is not the word
-    // y_b200_device_status reads) before clearing it; the operand areas are fully
-    // overwritten by the quantise kernels and need no clearing.
-    if (cudaStreamQuery(st) == cudaSuccess) {
-        DeviceStatus prev;
-        YB_CUDA(cudaMemcpy(&prev, status, sizeof prev, cudaMemcpyDeviceToHost));
-        if (prev.code != 0) {
-            YB_CUDA(cudaMemset(status, 0, sizeof(DeviceStatus)));
-            return fail(Y_B200_ERR_DEVICE,
-                        "y_b200_gemm_fp8_f32_static: the previous call on this device gave up a bounded wait "
-                        "(code %u at 0x%x, CTA %u); its output is not valid", prev.code, prev.where, prev.block);
-        }
-    } else {
-        (void)cudaGetLastError();
-    }
-    YB_CUDA(cudaMemsetAsync(status, 0, sizeof(DeviceStatus), st));
-    if ((rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, slots, aq, st))) return rc;
-    if ((rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, slots + 1, bq, st))) return rc;
+    if ((rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, aq, st))) return rc;
+    if ((rc = quantize_with_host_scale(b, Y_B200_F32, (size_t)k, (size_t)n, true, scale_b, bq, st))) return rc;
     // One-CTA tile from the analytic score only: no cache file, no measurement run.
     const TileShape tile = pick_tile(m, n, k, 128, 0);
     GemmParams p = {};
     p.c = c;
     p.m = m; p.n = n; p.k = k;
+    p.k_bytes = k;
     p.scale_a = scale_a; p.scale_b = scale_b;
     p.status = status;
     return launch_tiled(aq, bq, p, tile, Y_B200_EPI_NONE, Y_B200_F32, 0, st);

@@ -132,11 +132,11 @@ __global__ void scale_from_amax_kernel(const float* amax, float* scale) {
 // thread 0 publishes it to scale_out.
 template <int KIND, bool SCALE_IS_AMAX>
 __global__ void __launch_bounds__(kThreads)
-    quantize_kernel(const void* __restrict__ x, size_t n, const float* __restrict__ s,
+    quantize_kernel(const void* __restrict__ x, size_t n, const float* __restrict__ s, float s_val,
                     uint8_t* __restrict__ q, float* __restrict__ scale_out) {
     pdl_wait();
     pdl_launch_dependents();
-    const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
+    const float scale = s == nullptr ? s_val : (SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0]);
     const float inv = inv_scale(scale);
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
         scale_out[0] = scale;
@@ -175,12 +175,12 @@ constexpr int kTR = 128, kTC = 64;
 template <int KIND, bool SCALE_IS_AMAX>
 __global__ void __launch_bounds__(kThreads)
     quantize_transpose_kernel(const void* __restrict__ x, size_t rows, size_t cols,
-                              const float* __restrict__ s, uint8_t* __restrict__ q,
+                              const float* __restrict__ s, float s_val, uint8_t* __restrict__ q,
                               float* __restrict__ scale_out) {
     __shared__ __align__(16) uint32_t tile[kTC][kTR / 4];
     pdl_wait();
     pdl_launch_dependents();
-    const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
+    const float scale = s == nullptr ? s_val : (SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0]);
     const float inv = inv_scale(scale);
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&
         threadIdx.x == 0)
@@ -236,12 +236,12 @@ __global__ void __launch_bounds__(kThreads)
 template <int KIND, bool SCALE_IS_AMAX>
 __global__ void __launch_bounds__(kThreads)
     quantize_transpose_strip_kernel(const uint16_t* __restrict__ x, size_t rows, size_t cols,
-                                    const float* __restrict__ s, uint8_t* __restrict__ q,
+                                    const float* __restrict__ s, float s_val, uint8_t* __restrict__ q,
                                     float* __restrict__ scale_out, int tiles_per_cta) {
     __shared__ __align__(16) uint32_t tile[2][kTC][kTR / 4];
     pdl_wait();
     pdl_launch_dependents();
-    const float scale = SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0];
+    const float scale = s == nullptr ? s_val : (SCALE_IS_AMAX ? scale_from_amax(s[0]) : s[0]);
     const float inv = inv_scale(scale);
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 &&
         threadIdx.x == 0)
@@ -673,26 +673,26 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 int kind_ok(int kind) { return kind == Y_B200_F32 || kind == Y_B200_F16 || kind == Y_B200_BF16; }
 
 template <bool IS_AMAX>
-int launch_quantize(const void* x, int kind, size_t n, const float* s, void* q, float* scale_out,
+int launch_quantize(const void* x, int kind, size_t n, const float* s, float s_val, void* q, float* scale_out,
                     cudaStream_t st) {
     int grid = grid_for(n / 16 + 1);
     uint8_t* qq = static_cast<uint8_t*>(q);
     switch (kind) {
         case Y_B200_F16:
-            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_F16, IS_AMAX>, grid, kThreads, 0, st, x, n, s, qq, scale_out));
+            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_F16, IS_AMAX>, grid, kThreads, 0, st, x, n, s, s_val, qq, scale_out));
             break;
         case Y_B200_BF16:
-            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_BF16, IS_AMAX>, grid, kThreads, 0, st, x, n, s, qq, scale_out));
+            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_BF16, IS_AMAX>, grid, kThreads, 0, st, x, n, s, s_val, qq, scale_out));
             break;
         default:
-            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_F32, IS_AMAX>, grid, kThreads, 0, st, x, n, s, qq, scale_out));
+            YB_CUDA(launch_pdl(quantize_kernel<Y_B200_F32, IS_AMAX>, grid, kThreads, 0, st, x, n, s, s_val, qq, scale_out));
             break;
     }
     return check_cuda(cudaGetLastError(), "quantize_kernel launch");
 }
 
 template <bool IS_AMAX>
-int launch_quantize_t(const void* x, int kind, size_t rows, size_t cols, const float* s, void* q,
+int launch_quantize_t(const void* x, int kind, size_t rows, size_t cols, const float* s, float s_val, void* q,
                       float* scale_out, cudaStream_t st) {
     dim3 grid((unsigned)((cols + kTC - 1) / kTC), (unsigned)((rows + kTR - 1) / kTR));
     uint8_t* qq = static_cast<uint8_t*>(q);
@@ -705,20 +705,20 @@ int launch_quantize_t(const void* x, int kind, size_t rows, size_t cols, const f
         dim3 sgrid((unsigned)(cols / kTC), (unsigned)((row_tiles + tpc - 1) / tpc));
         const uint16_t* xs = static_cast<const uint16_t*>(x);
         if (kind == Y_B200_F16)
-            YB_CUDA(launch_pdl(quantize_transpose_strip_kernel<Y_B200_F16, IS_AMAX>, sgrid, kThreads, 0, st, xs, rows, cols, s, qq, scale_out, tpc));
+            YB_CUDA(launch_pdl(quantize_transpose_strip_kernel<Y_B200_F16, IS_AMAX>, sgrid, kThreads, 0, st, xs, rows, cols, s, s_val, qq, scale_out, tpc));
         else
-            YB_CUDA(launch_pdl(quantize_transpose_strip_kernel<Y_B200_BF16, IS_AMAX>, sgrid, kThreads, 0, st, xs, rows, cols, s, qq, scale_out, tpc));
+            YB_CUDA(launch_pdl(quantize_transpose_strip_kernel<Y_B200_BF16, IS_AMAX>, sgrid, kThreads, 0, st, xs, rows, cols, s, s_val, qq, scale_out, tpc));
         return check_cuda(cudaGetLastError(), "quantize_transpose_strip_kernel launch");
     }
     switch (kind) {
         case Y_B200_F16:
-            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_F16, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, qq, scale_out));
+            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_F16, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, s_val, qq, scale_out));
             break;
         case Y_B200_BF16:
-            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_BF16, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, qq, scale_out));
+            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_BF16, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, s_val, qq, scale_out));
             break;
         default:
-            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_F32, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, qq, scale_out));
+            YB_CUDA(launch_pdl(quantize_transpose_kernel<Y_B200_F32, IS_AMAX>, grid, kThreads, 0, st, x, rows, cols, s, s_val, qq, scale_out));
             break;
     }
     return check_cuda(cudaGetLastError(), "quantize_transpose_kernel launch");
@@ -738,18 +738,19 @@ int launch_amax(const void* x, int kind, size_t n, float* amax_out, cudaStream_t
 
 }  // namespace
 
-// Internal entry used by the f32 drop-in GEMM (by-value scale from the host).
+// Internal entry used by the f32 drop-in GEMM. The host's scale travels as a kernel
+// argument, not through a device word: a copy from the caller's stack would leave a
+// dangling host address in a captured graph.
 int quantize_with_host_scale(const void* x, int kind, size_t rows, size_t cols, bool transpose,
-                             float scale, float* scale_slot, void* q, cudaStream_t st) {
-    YB_CUDA(cudaMemcpyAsync(scale_slot, &scale, sizeof(float), cudaMemcpyHostToDevice, st));
-    if (transpose) return launch_quantize_t<false>(x, kind, rows, cols, scale_slot, q, nullptr, st);
-    return launch_quantize<false>(x, kind, rows * cols, scale_slot, q, nullptr, st);
+                             float scale, void* q, cudaStream_t st) {
+    if (transpose) return launch_quantize_t<false>(x, kind, rows, cols, nullptr, scale, q, nullptr, st);
+    return launch_quantize<false>(x, kind, rows * cols, nullptr, scale, q, nullptr, st);
 }
 
 // Internal: requantise with the scale derived from an amax word.
 int quantize_from_amax(const void* x, int kind, size_t n, const float* amax, void* q,
                        float* scale_out, cudaStream_t st) {
-    return launch_quantize<true>(x, kind, n, amax, q, scale_out, st);
+    return launch_quantize<true>(x, kind, n, amax, 0.0f, q, scale_out, st);
 }
 
 }  // namespace yb
@@ -775,7 +776,7 @@ extern "C" int y_b200_quantize_fp8(const void* x, int x_kind, size_t n, const fl
     if (!kind_ok(x_kind)) return fail(Y_B200_ERR_INVALID, "y_b200_quantize_fp8: bad element kind %d", x_kind);
     if (!aligned16(x) || !aligned16(q))
         return fail(Y_B200_ERR_ALIGN, "y_b200_quantize_fp8: x and q must be 16-byte aligned");
-    return launch_quantize<false>(x, x_kind, n, scale, q, nullptr, static_cast<cudaStream_t>(stream));
+    return launch_quantize<false>(x, x_kind, n, scale, 0.0f, q, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int y_b200_quantize_fp8_transpose(const void* x, int x_kind, size_t rows, size_t cols,
@@ -785,7 +786,7 @@ extern "C" int y_b200_quantize_fp8_transpose(const void* x, int x_kind, size_t r
     if (rows == 0 || cols == 0) return Y_B200_OK;
     if (!aligned16(x) || !aligned16(q))
         return fail(Y_B200_ERR_ALIGN, "y_b200_quantize_fp8_transpose: x and q must be 16-byte aligned");
-    return launch_quantize_t<false>(x, x_kind, rows, cols, scale, q, nullptr,
+    return launch_quantize_t<false>(x, x_kind, rows, cols, scale, 0.0f, q, nullptr,
                                     static_cast<cudaStream_t>(stream));
 }
 
@@ -801,9 +802,9 @@ extern "C" int y_b200_quantize_fp8_dynamic(const void* x, int x_kind, size_t row
     int rc = launch_amax(x, x_kind, rows * cols, scale_out, st);
     if (rc) return rc;
     if (transpose && rows != 0 && cols != 0)
-        rc = launch_quantize_t<true>(x, x_kind, rows, cols, scale_out, q, nullptr, st);
+        rc = launch_quantize_t<true>(x, x_kind, rows, cols, scale_out, 0.0f, q, nullptr, st);
     else
-        rc = launch_quantize<true>(x, x_kind, rows * cols, scale_out, q, nullptr, st);
+        rc = launch_quantize<true>(x, x_kind, rows * cols, scale_out, 0.0f, q, nullptr, st);
     if (rc) return rc;
     YB_CUDA(launch_pdl(scale_from_amax_kernel, 1, 1, 0, st, static_cast<const float*>(scale_out), scale_out));
     return check_cuda(cudaGetLastError(), "scale_from_amax_kernel launch");

@@ -23,7 +23,11 @@ struct y_buf {
     int device;
 };
 
-enum class Entry { GemmFp8F32, Fp8Gemm, Int4Decode, RmsnormResidual, Rope, PagedDecodeAttention };
+enum class Entry {
+    GemmFp8F32, Fp8Gemm, Fp8GemmBiasRelu, Fp8GemmSwiglu, Int4Decode, RmsnormResidual, Rope, PagedDecodeAttention,
+    GemmF16, GemmF16BiasRelu, GemmF16Swiglu,                      // descriptor kernels, baked shape, f32 out
+    TensorCoreGemm, FusedGemmBiasReluFp16, SplitkWorkspace, SplitkReduction  // runtime-shape .cu entries, f16 out
+};
 
 struct y_kernel {
     Entry entry;
@@ -37,10 +41,38 @@ struct y_kernel {
 
 namespace yb {
 void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsigned* smem, int* slots, int* unit_k);
+void f16_decode_launch_geometry(int n, unsigned* grid, unsigned* block, unsigned* smem, int* stages);
 }
 using namespace yb;
 
 namespace {
+
+// Shapes the weight-streaming kernel takes (y_b200_gemm_f16_decode's preconditions); other
+// F16 shapes go through the tensor-core GEMM.
+bool uses_decode_kernel(int m, int n, int k) { return m <= 32 && k % 16 == 0 && n % 8 == 0; }
+
+// Grows a kernel object's workspace (owned by it, freed with it).
+int ensure_workspace(y_kernel* k, size_t need) {
+    if (need <= k->workspace_bytes) return 0;
+    if (k->workspace) cudaFree(k->workspace);
+    k->workspace = nullptr;
+    k->workspace_bytes = 0;
+    int rc = check_cuda(cudaMalloc(&k->workspace, need), "cudaMalloc(kernel workspace)");
+    if (rc) return rc;
+    k->workspace_bytes = need;
+    return 0;
+}
+
+// F16 GEMM with row-major B [K, N]: the weight-streaming kernel for decode shapes, else the
+// K-major copy + tensor-core GEMM. `bias` may be null.
+int run_f16_rowmajor(y_kernel* k, const void* a, const void* b, const void* bias, int bias_kind, int relu, void* c,
+                     int out_kind, int m, int n, int kk) {
+    if (!bias && uses_decode_kernel(m, n, kk)) return y_b200_gemm_f16_decode(a, kk, b, c, out_kind, m, n, kk, nullptr);
+    int rc = ensure_workspace(k, y_b200_gemm_f16_rowmajor_workspace_bytes(n, kk));
+    if (rc) return rc;
+    return y_b200_gemm_f16_rowmajor(a, b, bias, bias_kind, relu, c, out_kind, m, n, kk, k->workspace, k->workspace_bytes,
+                                    nullptr);
+}
 
 char* dup_cstr(const std::string& s) {
     char* p = static_cast<char*>(malloc(s.size() + 1));
@@ -81,9 +113,25 @@ int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out
         out->cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32); out->cta_n = 16; out->cta_k = unit_k; out->stages = slots;
         return 0;
     }
-    int rc = y_b200_gemm_fp8_launch_info(m, n, kk, 0, out);
+    const bool f16 = k->entry == Entry::GemmF16 || k->entry == Entry::GemmF16BiasRelu || k->entry == Entry::GemmF16Swiglu ||
+                     k->entry == Entry::TensorCoreGemm || k->entry == Entry::FusedGemmBiasReluFp16;
+    if ((k->entry == Entry::GemmF16 || k->entry == Entry::TensorCoreGemm) && uses_decode_kernel(m, n, kk)) {
+        f16_decode_launch_geometry(n, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages);
+        out->grid[1] = out->grid[2] = out->block[1] = out->block[2] = 1;
+        out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
+        out->cta_m = m <= 16 ? 16 : 32; out->cta_n = 32; out->cta_k = 16;
+        return 0;
+    }
+    // An f16 problem runs the byte-tiled kernels on rows of 2 K bytes; SwiGLU on 2 N interleaved columns.
+    const int n_eff = k->entry == Entry::GemmF16Swiglu ? 2 * n : n;
+    int rc = y_b200_gemm_fp8_launch_info(m, n_eff, f16 ? 2 * kk : kk, 0, out);
     if (rc) return rc;
     if (k->entry == Entry::GemmFp8F32) out->workspace_bytes = y_b200_gemm_fp8_f32_workspace_bytes(m, n, kk);
+    if (k->entry == Entry::GemmF16Swiglu) out->workspace_bytes = y_b200_gemm_f16_swiglu_workspace_bytes(n, kk);
+    else if (f16) out->workspace_bytes = y_b200_gemm_f16_rowmajor_workspace_bytes(n, kk);
+    out->fused_epilogues = (k->entry == Entry::GemmF16BiasRelu || k->entry == Entry::GemmF16Swiglu ||
+                            k->entry == Entry::Fp8GemmBiasRelu || k->entry == Entry::Fp8GemmSwiglu ||
+                            k->entry == Entry::FusedGemmBiasReluFp16) ? 1 : 0;
     return 0;
 }
 
@@ -143,6 +191,116 @@ int launch_once(y_kernel* k, const unsigned grid[3], const unsigned block[3], un
             g.m = a[5].v.i32; g.n = a[6].v.i32; g.k = a[7].v.i32;
             g.out_kind = Y_B200_BF16;
             return y_b200_gemm_fp8(&g, nullptr);
+        }
+        case Entry::Fp8GemmBiasRelu: {
+            // (Aq, Bqt, bias f16 [N], C bf16, scale_a, scale_b, M, N, K, is_relu): the FP8 form of
+            // y_fused_gemm_bias_relu_fp16_kernel (tests/y_tensor_core_gemm.cu:2712-2719).
+            static const int kinds[10] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_F32,
+                                          Y_ARG_F32, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 10, "y_fp8_gemm_bias_relu");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, a[6].v.i32, a[7].v.i32, a[8].v.i32, grid, block, smem))) return rc;
+            y_b200_gemm_fp8_args g = {};
+            g.a = reinterpret_cast<const void*>(a[0].v.ptr);
+            g.bt = reinterpret_cast<const void*>(a[1].v.ptr);
+            g.bias = reinterpret_cast<const void*>(a[2].v.ptr);
+            g.bias_kind = Y_B200_F16;
+            g.c = reinterpret_cast<void*>(a[3].v.ptr);
+            g.scale_a = a[4].v.f32; g.scale_b = a[5].v.f32;
+            g.m = a[6].v.i32; g.n = a[7].v.i32; g.k = a[8].v.i32;
+            g.epilogue = a[9].v.i32 ? Y_B200_EPI_BIAS_RELU : Y_B200_EPI_BIAS;
+            g.out_kind = Y_B200_BF16;
+            return y_b200_gemm_fp8(&g, nullptr);
+        }
+        case Entry::Fp8GemmSwiglu: {
+            // (Aq, Bqt gate|up interleaved [N, K], C bf16 [M, N/2], scale_a, scale_b, M, N, K)
+            static const int kinds[8] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_F32,
+                                         Y_ARG_F32, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 8, "y_fp8_gemm_swiglu");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, a[5].v.i32, a[6].v.i32, a[7].v.i32, grid, block, smem))) return rc;
+            y_b200_gemm_fp8_args g = {};
+            g.a = reinterpret_cast<const void*>(a[0].v.ptr);
+            g.bt = reinterpret_cast<const void*>(a[1].v.ptr);
+            g.c = reinterpret_cast<void*>(a[2].v.ptr);
+            g.scale_a = a[3].v.f32; g.scale_b = a[4].v.f32;
+            g.m = a[5].v.i32; g.n = a[6].v.i32; g.k = a[7].v.i32;
+            g.epilogue = Y_B200_EPI_SWIGLU;
+            g.out_kind = Y_B200_BF16;
+            return y_b200_gemm_fp8(&g, nullptr);
+        }
+        case Entry::GemmF16: {
+            static const int kinds[3] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR};
+            int rc = expect_args(a, nargs, kinds, 3, "gemm_f16_<tag>");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, k->m, k->n, k->k, grid, block, smem))) return rc;
+            return run_f16_rowmajor(k, reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                                    nullptr, 0, 0, reinterpret_cast<void*>(a[2].v.ptr), Y_B200_F32, k->m, k->n, k->k);
+        }
+        case Entry::GemmF16BiasRelu: {
+            static const int kinds[4] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR};
+            int rc = expect_args(a, nargs, kinds, 4, "gemm_f16_bias_relu_<tag>");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, k->m, k->n, k->k, grid, block, smem))) return rc;
+            if (!a[2].v.ptr) return fail(Y_B200_ERR_INVALID, "gemm_f16_bias_relu_<tag>: null Bias");
+            return run_f16_rowmajor(k, reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                                    reinterpret_cast<const void*>(a[2].v.ptr), Y_B200_F32, 1,
+                                    reinterpret_cast<void*>(a[3].v.ptr), Y_B200_F32, k->m, k->n, k->k);
+        }
+        case Entry::GemmF16Swiglu: {
+            static const int kinds[4] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR};
+            int rc = expect_args(a, nargs, kinds, 4, "gemm_f16_swiglu_<tag>");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, k->m, k->n, k->k, grid, block, smem))) return rc;
+            if ((rc = ensure_workspace(k, y_b200_gemm_f16_swiglu_workspace_bytes(k->n, k->k)))) return rc;
+            return y_b200_gemm_f16_swiglu(reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                                          reinterpret_cast<const void*>(a[2].v.ptr), reinterpret_cast<float*>(a[3].v.ptr),
+                                          k->m, k->n, k->k, k->workspace, k->workspace_bytes, nullptr);
+        }
+        case Entry::TensorCoreGemm: {
+            // (A f16, B f16 [K, N], C f16, M, N, K): y_tensor_core_gemm_kernel, tests/y_tensor_core_gemm.cu:102-107
+            static const int kinds[6] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 6, "y_tensor_core_gemm");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, a[3].v.i32, a[4].v.i32, a[5].v.i32, grid, block, smem))) return rc;
+            return run_f16_rowmajor(k, reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                                    nullptr, 0, 0, reinterpret_cast<void*>(a[2].v.ptr), Y_B200_F16, a[3].v.i32, a[4].v.i32,
+                                    a[5].v.i32);
+        }
+        case Entry::FusedGemmBiasReluFp16: {
+            // (A, B, bias f16, C f16, M, N, K, is_relu): tests/y_tensor_core_gemm.cu:2712-2719
+            static const int kinds[8] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 8, "y_fused_gemm_bias_relu_fp16");
+            if (rc) return rc;
+            if ((rc = check_geometry(k, a[4].v.i32, a[5].v.i32, a[6].v.i32, grid, block, smem))) return rc;
+            if (!a[2].v.ptr) return fail(Y_B200_ERR_INVALID, "y_fused_gemm_bias_relu_fp16: null bias");
+            return run_f16_rowmajor(k, reinterpret_cast<const void*>(a[0].v.ptr), reinterpret_cast<const void*>(a[1].v.ptr),
+                                    reinterpret_cast<const void*>(a[2].v.ptr), Y_B200_F16, a[7].v.i32 != 0,
+                                    reinterpret_cast<void*>(a[3].v.ptr), Y_B200_F16, a[4].v.i32, a[5].v.i32, a[6].v.i32);
+        }
+        case Entry::SplitkWorkspace: {
+            // (A, B, Workspace f32 [k_splits, M, N], M, N, K, k_splits): tests/y_tensor_core_gemm.cu:4732-4738
+            static const int kinds[7] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 7, "y_fused_gemm_splitk_workspace");
+            if (rc) return rc;
+            if (grid || block || smem)
+                return fail(Y_B200_ERR_INVALID, "y_fused_gemm_splitk_workspace: pass no launch geometry (the library splits K itself)");
+            if (a[3].v.i32 < 1 || a[3].v.i32 > 32)
+                return fail(Y_B200_ERR_SHAPE, "y_fused_gemm_splitk_workspace: M=%d outside the decode range 1..32", a[3].v.i32);
+            return y_b200_gemm_f16_splitk_workspace(reinterpret_cast<const void*>(a[0].v.ptr),
+                                                    reinterpret_cast<const void*>(a[1].v.ptr),
+                                                    reinterpret_cast<float*>(a[2].v.ptr), a[3].v.i32, a[4].v.i32, a[5].v.i32,
+                                                    a[6].v.i32, nullptr);
+        }
+        case Entry::SplitkReduction: {
+            // (Workspace, C f16, total, M, N, k_splits): tests/y_tensor_core_gemm.cu:4852-4858
+            static const int kinds[6] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
+            int rc = expect_args(a, nargs, kinds, 6, "y_splitk_reduction");
+            if (rc) return rc;
+            if (grid || block || smem) return fail(Y_B200_ERR_INVALID, "y_splitk_reduction: pass no launch geometry");
+            return y_b200_splitk_reduction(reinterpret_cast<const float*>(a[0].v.ptr), reinterpret_cast<void*>(a[1].v.ptr),
+                                           (size_t)(a[2].v.i32 < 0 ? 0 : a[2].v.i32), a[3].v.i32, a[4].v.i32, a[5].v.i32,
+                                           nullptr);
         }
         case Entry::Int4Decode: {
             static const int kinds[6] = {Y_ARG_PTR, Y_ARG_PTR, Y_ARG_PTR, Y_ARG_I32, Y_ARG_I32, Y_ARG_I32};
@@ -352,7 +510,13 @@ extern "C" y_kernel* y_ctx_load_module(y_ctx* ctx, const char* image, const char
     const std::string name(entry);
     if (image == nullptr) {
         if (name == "y_fp8_gemm") k.entry = Entry::Fp8Gemm;
+        else if (name == "y_fp8_gemm_bias_relu") k.entry = Entry::Fp8GemmBiasRelu;
+        else if (name == "y_fp8_gemm_swiglu") k.entry = Entry::Fp8GemmSwiglu;
         else if (name == "y_int4_decode_gemm") k.entry = Entry::Int4Decode;
+        else if (name == "y_tensor_core_gemm") k.entry = Entry::TensorCoreGemm;
+        else if (name == "y_fused_gemm_bias_relu_fp16") k.entry = Entry::FusedGemmBiasReluFp16;
+        else if (name == "y_fused_gemm_splitk_workspace") k.entry = Entry::SplitkWorkspace;
+        else if (name == "y_splitk_reduction") k.entry = Entry::SplitkReduction;
         else { fail(Y_B200_ERR_UNSUPPORTED, "y_ctx_load_module: no built-in entry named '%s'", entry); return nullptr; }
     } else {
         // Find "// [Y B200 KERNEL] entry=<name> family=<f>" and the shape line after it.
@@ -410,7 +574,8 @@ extern "C" y_kernel* y_ctx_load_module(y_ctx* ctx, const char* image, const char
             *res = k;
             return res;
         }
-        if (fam != "gemm_fp8") {
+        const bool f16_family = fam == "gemm_f16" || fam == "gemm_f16_bias_relu" || fam == "gemm_f16_swiglu";
+        if (fam != "gemm_fp8" && !f16_family) {
             fail(Y_B200_ERR_UNSUPPORTED, "y_ctx_load_module: family '%s' of '%s' has no sm_100a kernel in this library",
                  fam.c_str(), entry);
             return nullptr;
@@ -423,10 +588,26 @@ extern "C" y_kernel* y_ctx_load_module(y_ctx* ctx, const char* image, const char
             fail(Y_B200_ERR_INVALID, "y_ctx_load_module: could not read M/N/K of '%s' from the image", entry);
             return nullptr;
         }
-        k.entry = Entry::GemmFp8F32;
         k.m = (int)m; k.n = (int)n; k.k = (int)kk;
-        k.workspace_bytes = y_b200_gemm_fp8_f32_workspace_bytes(k.m, k.n, k.k);
-        if (check_cuda(cudaMalloc(&k.workspace, k.workspace_bytes), "cudaMalloc(workspace)")) return nullptr;
+        if (f16_family) {
+            // The reference's preconditions (src/ptx_emitter.rs:4252-4260, :5110-5112), checked again
+            // here because a descriptor is only text.
+            if (k.k % 8 != 0 || 2LL * k.n > 0x7fffffff) {
+                fail(Y_B200_ERR_SHAPE, "y_ctx_load_module: F16 GEMM '%s' needs K %% 8 == 0", entry);
+                return nullptr;
+            }
+            k.entry = fam == "gemm_f16" ? Entry::GemmF16 : fam == "gemm_f16_bias_relu" ? Entry::GemmF16BiasRelu : Entry::GemmF16Swiglu;
+            size_t need = 0;  // decode shapes stream the weights as they lie and need none
+            if (k.entry == Entry::GemmF16Swiglu) need = y_b200_gemm_f16_swiglu_workspace_bytes(k.n, k.k);
+            else if (k.entry == Entry::GemmF16BiasRelu || !uses_decode_kernel(k.m, k.n, k.k))
+                need = y_b200_gemm_f16_rowmajor_workspace_bytes(k.n, k.k);
+            if (need && check_cuda(cudaMalloc(&k.workspace, need), "cudaMalloc(workspace)")) return nullptr;
+            k.workspace_bytes = need;
+        } else {
+            k.entry = Entry::GemmFp8F32;
+            k.workspace_bytes = y_b200_gemm_fp8_f32_workspace_bytes(k.m, k.n, k.k);
+            if (check_cuda(cudaMalloc(&k.workspace, k.workspace_bytes), "cudaMalloc(workspace)")) return nullptr;
+        }
     }
     y_kernel* out = static_cast<y_kernel*>(malloc(sizeof(y_kernel)));
     if (!out) { if (k.workspace) cudaFree(k.workspace); return nullptr; }
@@ -452,7 +633,8 @@ extern "C" int y_kernel_set_max_dynamic_smem(y_kernel* kernel, unsigned bytes) {
 
 extern "C" int y_kernel_launch_info(const y_kernel* kernel, y_b200_launch_info* out) {
     if (!kernel || !out) return fail(Y_B200_ERR_INVALID, "y_kernel_launch_info: null argument");
-    if (kernel->entry != Entry::GemmFp8F32)
+    if (kernel->entry != Entry::GemmFp8F32 && kernel->entry != Entry::GemmF16 && kernel->entry != Entry::GemmF16BiasRelu &&
+        kernel->entry != Entry::GemmF16Swiglu)
         return fail(Y_B200_ERR_INVALID, "y_kernel_launch_info: runtime-shape entries have no baked geometry; use y_b200_gemm_fp8_launch_info");
     return kernel_info(kernel, kernel->m, kernel->n, kernel->k, out);
 }

@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from ._lib import (BF16, E4M3, EPI_BIAS, EPI_BIAS_RELU, EPI_NONE, EPI_SWIGLU, F16, F32,
-                   GemmFp8Args, LaunchInfo, check, lib)
+                   GemmF16Args, GemmFp8Args, LaunchInfo, check, lib)
 
 _KIND = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 _OUT_DTYPE = {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16}
@@ -252,6 +252,75 @@ def gemm_fp8_f32(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: floa
     check(lib.y_b200_gemm_fp8_f32(a.data_ptr(), b.data_ptr(), scale_a, scale_b, c.data_ptr(), m, n,
                                   k, ws.data_ptr(), ws.numel(), _stream()))
     return c
+
+
+# ---- F16 GEMM family -------------------------------------------------------------
+def gemm_f16_kmajor(a: torch.Tensor, bt: torch.Tensor, *, bias=None, epilogue: int = EPI_NONE,
+                    out_dtype=torch.float32, out: torch.Tensor | None = None, cta_n: int = 0, cta_m: int = 0):
+    """C = epilogue(a @ bt^T) on the tensor cores (kind::f16): a [M, K], bt [N, K], both f16,
+    K-major. EPI_SWIGLU: bt rows gate|up interleaved, C [M, N/2] f32 or bf16."""
+    _dev(a, "a"), _dev(bt, "bt")
+    (m, k), (n, k2) = a.shape, bt.shape
+    if k != k2 or a.dtype != torch.float16 or bt.dtype != torch.float16:
+        raise ValueError("gemm_f16_kmajor takes f16 a [M, K] and bt [N, K]")
+    n_out = n // 2 if epilogue == EPI_SWIGLU else n
+    c = out if out is not None else torch.empty((m, n_out), dtype=out_dtype, device=a.device)
+    args = GemmF16Args()
+    args.a, args.bt, args.c = a.data_ptr(), bt.data_ptr(), c.data_ptr()
+    args.m, args.n, args.k = m, n, k
+    if bias is not None:
+        _dev(bias, "bias")
+        args.bias, args.bias_kind = bias.data_ptr(), _kind(bias, "bias")
+    args.epilogue, args.out_kind = epilogue, {v: kk for kk, v in _OUT_DTYPE.items()}[out_dtype]
+    args.cta_n, args.cta_m = cta_n, cta_m
+    check(lib.y_b200_gemm_f16(C.byref(args), _stream()))
+    return c
+
+
+def gemm_f16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, relu: bool = False,
+             out_dtype=torch.float32, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Drop-in for gemm_f16_<tag>(A, B, C) / gemm_f16_bias_relu_<tag>(A, B, Bias, C): f16 A [M, K],
+    f16 B [K, N] row-major, C [M, N] f32 (or f16)."""
+    _dev(a, "a"), _dev(b, "b")
+    (m, k), (k2, n) = a.shape, b.shape
+    if k != k2 or a.dtype != torch.float16 or b.dtype != torch.float16:
+        raise ValueError("gemm_f16 takes f16 A [M, K] and B [K, N]")
+    need = lib.y_b200_gemm_f16_rowmajor_workspace_bytes(n, k)
+    ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=a.device)
+    c = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    check(lib.y_b200_gemm_f16_rowmajor(a.data_ptr(), b.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                       _kind(bias, "bias") if bias is not None else 0, int(relu), c.data_ptr(),
+                                       {v: kk for kk, v in _OUT_DTYPE.items()}[out_dtype], m, n, k, ws.data_ptr(),
+                                       ws.numel(), _stream()))
+    return c
+
+
+def gemm_f16_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                    workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Drop-in for gemm_f16_swiglu_<tag>(X, Wgate, Wup, Out): Out [M, N] f32 = silu(X @ Wgate) * (X @ Wup)."""
+    _dev(x, "x"), _dev(w_gate, "w_gate"), _dev(w_up, "w_up")
+    (m, k), (k2, n) = x.shape, w_gate.shape
+    if k != k2 or w_up.shape != w_gate.shape or any(t.dtype != torch.float16 for t in (x, w_gate, w_up)):
+        raise ValueError("gemm_f16_swiglu takes f16 X [M, K] and Wgate, Wup [K, N]")
+    need = lib.y_b200_gemm_f16_swiglu_workspace_bytes(n, k)
+    ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x.device)
+    out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    check(lib.y_b200_gemm_f16_swiglu(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(), m, n, k,
+                                     ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
+def gemm_f16_decode(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    """Small-M GEMM with f16 weights streamed once, row-major [K, N] (the reference's
+    gemm_f16_decode_m<M> entries): out [M, N] = x [M, K] @ w, 1 <= M <= 32."""
+    _dev(x, "x"), _dev(w, "w")
+    (m, k), (k2, n) = x.shape, w.shape
+    if k != k2 or x.dtype != torch.float16 or w.dtype != torch.float16:
+        raise ValueError("gemm_f16_decode takes f16 x [M, K] and w [K, N]")
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    check(lib.y_b200_gemm_f16_decode(x.data_ptr(), k, w.data_ptr(), out.data_ptr(), F32 if out_dtype == torch.float32 else F16,
+                                     m, n, k, _stream()))
+    return out
 
 
 def gemm_fp8_swiglu_requant(aq: torch.Tensor, bqt: torch.Tensor, scale_a, scale_b,

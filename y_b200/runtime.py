@@ -164,11 +164,11 @@ def compile_to_ptx(source: str, target_sm: str = "sm_100a") -> str:
 
 
 def autotune_search_space(m: int, n: int, k: int, is_fp8: bool):
-    return json.loads(take_string(lib.y_autotune_search_space_json(m, n, k, int(is_fp8))))
+    return json.loads(take_string(lib.y_autotune_search_space_json(m, n, k, bool(is_fp8))))
 
 
 def autotune_select_config(m: int, n: int, k: int, is_fp8: bool):
-    return json.loads(take_string(lib.y_autotune_select_config_json(m, n, k, int(is_fp8))))
+    return json.loads(take_string(lib.y_autotune_select_config_json(m, n, k, bool(is_fp8))))
 
 
 def block_cdiv(a: int, b: int) -> int:
