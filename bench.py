@@ -11,6 +11,17 @@ The all-gather of C is measured separately and reported under "gather".
 
 Prints ONE JSON line (rank 0). `--impl reference` times the CPU restatement of
 the same step on the host cores instead (rank 0 only).
+
+`--only <case>` runs a few launches of one kernel family and prints "ok" instead: small,
+self-contained runs sized for a profiler capture (inputs larger than L2, a few hundred MB
+on the device):
+  --only step      [--m 8192 --n 8192 --k 8192] [--iters 3]    prologue + GEMM
+  --only gemm      [--m .. --n .. --k ..] [--epilogue none|bias_relu|swiglu] [--cta-n N]
+  --only decode    [--tokens 8] [--iters 48]                   INT4 decode GEMM, K=4096, N=11008
+  --only f16_decode [--tokens 8] [--iters 48]                  F16 weight streaming, K=N=4096
+  --only quantize  [--m 8192 --k 8192]                         dynamic e4m3 quantisation, both layouts
+  --only layer_ops [--m 8192 --k 8192]                         fused add+RMSNorm, RoPE
+  --only attention [--seqs 16 --seq-len 4096]                  paged decode attention
 """
 from __future__ import annotations
 
@@ -35,6 +46,15 @@ NOMINAL_FP8_TFLOPS = 4500.0
 
 
 _emit = print  # replaced in main() by a writer to the process's original stdout
+
+
+def workload_config(world: int) -> dict:
+    """The `config` object of the JSON line: the workload, identical for both arms."""
+    return {"workload": WORKLOAD, "m": M, "k": K, "n_per_gpu": N_SHARD, "n_total": N_SHARD * max(world, 1),
+            "parallelism": f"column-parallel N over {max(world, 1)} GPU(s)",
+            "step": "rmsnorm_stats + rmsnorm_quantize_fp8 + gemm_fp8 (weights pre-quantised)",
+            "l2": "inputs larger than L2 (X 134 MB + Bt 67 MB + C 134 MB per step)",
+            "all_gather": "not in value; see gather"}
 
 
 def load_peaks():
@@ -179,9 +199,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 accumulate over e4m3 (CPU)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "m": M, "k": K, "n_per_gpu": N_SHARD, "n_total": N_SHARD * max(args.gpus, 1),
-                   "parallelism": "host cores of rank 0 only", "sample": sample,
-                   "step": "rmsnorm_stats + rmsnorm_quantize_fp8 + gemm_fp8 (weights pre-quantised), oracle port"},
+        "config": workload_config(args.gpus),
+        "runs_on": "host cores of rank 0 only; the oracle port of the step (the reference has no CPU path for it)",
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -193,6 +212,7 @@ def other_config_metrics(peaks):
     import torch
 
     from y_b200 import quant as q
+    from y_b200._lib import check, lib
 
     def timeit(fn, iters=20, warm=5):
         for _ in range(warm):
@@ -296,6 +316,63 @@ def other_config_metrics(peaks):
     out["paged_decode_attention_64x4096_h32_kv8_d128_p16"] = {
         "us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
         "bytes": "K and V of every sequence once (1.07 GB)"}
+    # INT4 group quantisation and the repack into the streaming layout, K = 4096, N = 11008
+    del qv, kc, vc, pt, sl, oa, aws
+    kk, nn = DECODE_K, DECODE_N
+    wsets = [(torch.randn(kk, nn, device="cuda") / 64).to(torch.float16) for _ in range(3)]  # 3 x 90 MB, rotated
+    qw = torch.empty(kk // 8, nn, dtype=torch.int32, device="cuda")
+    sc = torch.empty(kk // 128, nn, dtype=torch.float16, device="cuda")
+    it = [0]
+
+    def int4_q():
+        w = wsets[it[0] % 3]
+        it[0] += 1
+        check(lib.y_b200_int4_quantize(w.data_ptr(), kk, nn, qw.data_ptr(), sc.data_ptr(), torch.cuda.current_stream().cuda_stream))
+
+    us = timeit(int4_q, iters=30)
+    nbytes = kk * nn * 2 + kk * nn // 2 + (kk // 128) * nn * 2
+    out["int4_quantize_4096x11008_g128"] = {"us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1),
+                                            "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
+                                            "bytes": "read f16 weights once (90.2 MB), write nibbles (22.5 MB) and group scales (0.7 MB)"}
+    stream = torch.empty(int(lib.y_b200_int4_stream_bytes(kk, nn)), dtype=torch.uint8, device="cuda")
+    us = timeit(lambda: check(lib.y_b200_int4_repack(qw.data_ptr(), sc.data_ptr(), kk, nn, stream.data_ptr(),
+                                                      torch.cuda.current_stream().cuda_stream)), iters=30)
+    nbytes = 2 * stream.numel()
+    out["int4_repack_4096x11008"] = {"us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1),
+                                     "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
+                                     "bytes": "read and write 23.2 MB each (L2-resident at this size: once per weight matrix, not a hot path)"}
+    del wsets, qw, sc, stream
+    # F16 family: the reference's decode fixture shape (weights [4096, 4096] f16 streamed once,
+    # 16 rotating buffers = 4 x L2) and the tensor-core GEMM on K-major f16 operands
+    wpool = [(torch.randn(4096, 4096, device="cuda") / 64).to(torch.float16) for _ in range(16)]
+    for mtok in (1, 8, 32):
+        xs = torch.randn(mtok, 4096, device="cuda", dtype=torch.float16)
+        it[0] = 0
+
+        def f16_dec():
+            q.gemm_f16_decode(xs, wpool[it[0] % 16], out_dtype=torch.float32)
+            it[0] += 1
+
+        us = timeit(f16_dec, iters=64, warm=16)
+        nbytes = 4096 * 4096 * 2 + mtok * 4096 * 2 + mtok * 4096 * 4
+        out[f"f16_decode_m{mtok}_4096x4096"] = {"us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1),
+                                                 "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes}
+    del wpool
+    m = n = k = 4096
+    sets = [(torch.randn(m, k, device="cuda", dtype=torch.float16), (torch.randn(n, k, device="cuda") / 64).to(torch.float16),
+             torch.empty(m, n, device="cuda", dtype=torch.float32)) for _ in range(2)]
+    it[0] = 0
+
+    def f16_gemm():
+        a, bt, c = sets[it[0] % 2]
+        it[0] += 1
+        q.gemm_f16_kmajor(a, bt, out=c)
+
+    us = timeit(f16_gemm, iters=20)
+    tf = 2.0 * m * n * k / us / 1e6
+    out["f16_gemm_4096_kmajor_f32_out"] = {"us": round(us, 2), "tflops": round(tf, 1),
+                                           "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
+                                           "note": "tcgen05 kind::f16; two rotating operand sets (2 x 134 MB)"}
     q.device_status()
     return out
 
@@ -433,6 +510,87 @@ def run_ours(args):
     gemm_kernel = ("gemm_fp8_pair_kernel<NONE, BF16> (tcgen05.mma.cta_group::2, 256x256 tile per CTA pair)"
                    if info.cta_m == 256 else f"gemm_fp8_kernel<{info.cta_n}, NONE, BF16> (128x{info.cta_n} tile per CTA)")
 
+    # ---- a measured FP8 yardstick in the same run: cuBLASLt's e4m3 x e4m3 -> bf16 GEMM through
+    # torch._scaled_mm on the same operands, timed like the GEMM above and interleaved with it so
+    # both see the same clocks. A comparator only: nothing of the product path goes through it.
+    comparator = None
+    try:
+        if args.no_comparator:
+            raise RuntimeError("skipped (--no-comparator)")
+        aq_c, sa_c = q.rmsnorm_quantize_fp8(x, gamma, EPS)
+        a8, b8 = aq_c.view(torch.float8_e4m3fn), bqt.view(torch.float8_e4m3fn).t()
+        sb_c = sb if isinstance(sb, torch.Tensor) else torch.tensor([sb], device=dev)
+        sa_s, sb_s = sa_c.reshape(()), sb_c.reshape(())
+        c_cmp = torch.empty(M, N_SHARD, dtype=torch.bfloat16, device=dev)
+
+        def ours_gemm():
+            q.gemm_fp8_codes(aq_c, bqt, sa_c, sb, out_dtype=torch.bfloat16, out=c)
+
+        def lib_gemm():
+            torch._scaled_mm(a8, b8, scale_a=sa_s, scale_b=sb_s, out_dtype=torch.bfloat16, out=c_cmp)
+
+        def burst(fn, iters=10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            fn()
+            e0.record()
+            for _ in range(iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / iters * 1e3
+
+        lib_gemm()
+        torch.cuda.synchronize()
+        ours_us, lib_us = [], []
+        for _ in range(3):
+            ours_us.append(burst(ours_gemm, 5))
+            lib_us.append(burst(lib_gemm, 5))
+        ours_us.sort(), lib_us.sort()
+        flop = 2.0 * M * K * N_SHARD
+        comparator = {"what": "torch._scaled_mm (cuBLASLt) e4m3 x e4m3 -> bf16, same operands, 3 interleaved bursts of 5",
+                      "library_us_median": lib_us[1], "library_tflops": flop / lib_us[1] / 1e6,
+                      "ours_us_median": ours_us[1], "ours_tflops": flop / ours_us[1] / 1e6,
+                      "ours_over_library": lib_us[1] / ours_us[1],
+                      "max_abs_diff_vs_library": float((c.float() - c_cmp.float()).abs().max())}
+        del a8, b8, c_cmp
+    except Exception as e:  # the yardstick is optional; the product path does not depend on it
+        comparator = {"unavailable": str(e)[:200]}
+
+    # ---- sustained: the same step back to back for about two seconds, with the clocks the
+    # GPU held over that window (a burst of a few ms ends before the power cap reacts)
+    sustained = None
+    if args.sustained_seconds > 0:
+        n_sus = max(50, int(args.sustained_seconds * 1.1 / (ms_per_step * 1e-3)))
+        sus_events = []
+
+        def sus_step(i):
+            if i % 64 == 0:
+                aq_s, sa_s2 = q.rmsnorm_quantize_fp8(x, gamma, EPS, workspace=layer._ws[0], out=layer._aq[0])
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                q.gemm_fp8_codes(aq_s, bqt, sa_s2, sb, out_dtype=torch.bfloat16, out=c)
+                e1.record()
+                sus_events.append((e0, e1))
+            else:
+                layer.forward(x, out=c)
+
+        with clk.window("sustained"):
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for i in range(n_sus):
+                sus_step(i)
+            t1.record()
+            barrier()
+        sus_ms = t0.elapsed_time(t1)
+        # the GEMM samples of the second half of the window: the first half is the ramp into the cap
+        half = sus_events[len(sus_events) // 2:]
+        sus_gemm_ms = sum(a.elapsed_time(b) for a, b in half) / len(half)
+        sustained = {"seconds": sus_ms / 1e3, "steps": n_sus, "ms_per_step": sus_ms / n_sus,
+                     "tflops": flops_step / (sus_ms / n_sus * 1e-3) / 1e12,
+                     "gemm_us_second_half": sus_gemm_ms * 1e3,
+                     "gemm_tflops_second_half": 2.0 * M * K * N_SHARD / (sus_gemm_ms * 1e-3) / 1e12}
+
     # ---- end to end through the operator API with host buffers: every step copies its X
     # from pinned host memory and its C back; the operator overlaps the copy-in of step
     # i+1, the kernels of step i and the copy-out of step i-1 on three streams.
@@ -453,7 +611,33 @@ def run_ours(args):
     clk.close()
     clocks = clk.summary("value")
     clocks["e2e_region"] = clk.summary("e2e")
+    if sustained is not None:
+        sc = clk.summary("sustained")
+        sustained.update({"sm_mhz": sc["sm_mhz"], "sm_mhz_min": sc["sm_mhz_min"], "reasons": sc["reasons"],
+                          "power_w_max": sc["power_w_max"], "clock_samples": sc["samples"],
+                          "ms_per_step_x_sm_mhz": (sustained["ms_per_step"] * sc["sm_mhz"]) if sc["sm_mhz"] else None,
+                          "bf16_sustained_yardstick_tflops": peaks["bf16_tflops_sustained"],
+                          "gemm_frac_of_2x_bf16_sustained": sustained["gemm_tflops_second_half"] / (2.0 * peaks["bf16_tflops_sustained"])})
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+
+    # ---- what the host link itself carries: bare pinned copies of one step's output and input,
+    # every rank at once (the floor the pipelined step is held against)
+    def link_gbs(dst, src):
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(10):
+            dst.copy_(src, non_blocking=True)
+        t1.record()
+        barrier()
+        ms_ = torch.tensor([t0.elapsed_time(t1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms_, op=dist.ReduceOp.MAX)
+        return world * 10 * src.numel() * src.element_size() / (ms_.item() * 1e-3) / 1e9
+
+    host_link = {"d2h_gb_s_all_ranks": link_gbs(c_host[0], c), "h2d_gb_s_all_ranks": link_gbs(x, x_host),
+                 "what": f"10 pinned {M * N_SHARD * 2 >> 20} MiB copies per rank, all {world} rank(s) at once, one direction at a time",
+                 "e2e_bytes_gb_s_all_ranks": world * sum(layer.host_bytes_per_step()) / (e2e_ms * 1e-3) / 1e9}
 
     # ---- the exchange step, reported separately: the same step followed by NCCL's all-gather,
     # and the step whose GEMM epilogue stores its shard straight into every peer's gathered
@@ -467,8 +651,13 @@ def run_ours(args):
         for _ in range(2):
             gather_step()
         g_ms = timed(gather_step, args.steps) / args.steps
-        gather = {"nccl": {"ms_per_step": g_ms, "tflops": flops_step / (g_ms * 1e-3) / 1e12},
-                  "gathered_layout": "[rank, M, N_shard] bf16", "recv_bytes_per_gpu": (world - 1) * M * N_SHARD * 2}
+        recv = (world - 1) * M * N_SHARD * 2
+        # floor of a step that delivers the whole C to every GPU: each GPU has to take in `recv`
+        # bytes over NVLink (measured peer copy on this pool: 770 GB/s per direction per GPU)
+        floor_ms = max(ms_per_step, recv / 770e9 * 1e3)
+        gather = {"nccl": {"ms_per_step": g_ms, "tflops": flops_step / (g_ms * 1e-3) / 1e12, "floor_over_time": floor_ms / g_ms},
+                  "gathered_layout": "[rank, M, N_shard] bf16", "recv_bytes_per_gpu": recv,
+                  "floor_ms": floor_ms, "floor_is": "max(step without gather, received bytes / 770 GB/s measured peer copy)"}
         fused, why = None, ""
         try:
             fused = colpar.GatheredOutput(M, N_SHARD)
@@ -488,6 +677,7 @@ def run_ours(args):
             agree = torch.tensor([1.0 if same else 0.0], device=dev)
             dist.all_reduce(agree, op=dist.ReduceOp.MIN)
             gather["fused_epilogue_stores"] = {"ms_per_step": f_ms, "tflops": flops_step / (f_ms * 1e-3) / 1e12,
+                                               "floor_over_time": floor_ms / f_ms,
                                                "equals_nccl_result_on_every_rank": bool(agree.item() > 0)}
             fused.close()
         else:
@@ -502,25 +692,24 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32 accumulate, bf16 out", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "m": M, "k": K, "n_per_gpu": N_SHARD, "n_total": N_SHARD * world,
-                       "parallelism": f"column-parallel N over {world} GPU(s)",
-                       "step": "rmsnorm_stats + rmsnorm_quantize_fp8 + gemm_fp8 (weights pre-quantised)",
-                       "l2": "inputs larger than L2 (X 134 MB + Bt 67 MB + C 134 MB per step)",
-                       "all_gather": "not in value; see gather"},
+            "config": workload_config(world),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                    "api": "y_b200.colpar.ColumnParallelFp8Linear.submit_host (3-stream pipeline, depth 2)",
+                    "api": layer.host_api() + f", depth {layer.depth}",
                     "h2d_bytes_per_step": layer.host_bytes_per_step()[0], "d2h_bytes_per_step": layer.host_bytes_per_step()[1],
                     "bytes_are": "per rank; with N > 1 each rank copies 1/N of X from the host and the ranks "
-                                 "all-gather it over NVLink"},
+                                 "all-gather it over NVLink",
+                    "host_link": host_link},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "tensor", "kernel": gemm_kernel, "achieved": gemm_tflops,
                          "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
-                         "peak_note": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s); "
-                                      f"nominal dense FP8 is {NOMINAL_FP8_TFLOPS}",
+                         "peak_note": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TF/s): the peaks file "
+                                      f"holds no FP8 figure; nominal dense FP8 is {NOMINAL_FP8_TFLOPS}; a measured FP8 "
+                                      "yardstick of the same run is under comparator",
                          "frac_of_nominal": gemm_tflops / NOMINAL_FP8_TFLOPS, "us_per_launch": gemm_ms * 1e3,
-                         "flops_per_launch": 2.0 * M * K * N_SHARD, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
-                         "launches_timed": len(gemm_events)},
+                         "flops_per_launch": 2.0 * M * K * N_SHARD,
+                         "traffic": traffic_for(gemm_kernel, M, N_SHARD, K), "traffic_source": GEMM_TRAFFIC["source"],
+                         "launches_timed": len(gemm_events), "comparator": comparator, "sustained": sustained},
         }
         if gather:
             line["gather"] = gather
@@ -528,11 +717,14 @@ def run_ours(args):
         dist.barrier()
     if rank == 0 and world == 1:
         if not args.no_decode:
-            line["decode"] = decode_metrics(peaks)
+            # BASELINE's second metric (INT4 decode GB/s against the HBM roofline) and the other
+            # single-GPU configurations travel inside `roofline`, the object the record keeps
+            dec = decode_metrics(peaks)
             # the same kernel on a twice as wide weight matrix (gate and up projections as
             # one launch): the per-launch fixed latencies weigh half as much
-            line["decode"]["wider"] = decode_metrics(peaks, n=2 * DECODE_N, tokens=(1, 8))
-            line["other_configs"] = other_config_metrics(peaks)
+            dec["wider"] = decode_metrics(peaks, n=2 * DECODE_N, tokens=(1, 8))
+            line["roofline"]["decode"] = dec
+            line["roofline"]["other_configs"] = other_config_metrics(peaks)
         if not args.no_cpu:
             rows = args.cpu_rows
             stepfn, cores = cpu_step_sample(rows)
@@ -552,9 +744,87 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch at the bench shape
-# (346.9 MB + 115.8 MB), from the ncu capture summarised under profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 462.7e6
+# DRAM bytes of one launch of the dominant kernel, keyed by what produced the figure: it is
+# reported only for the kernel and shape it was captured on (a profiler run cannot be part of a
+# timed benchmark, so this is the one number of the line that is not measured live).
+GEMM_TRAFFIC = {"kernel_prefix": "gemm_fp8_pair_kernel<NONE, BF16>", "shape": (8192, 8192, 8192),
+                "bytes": 346.9e6 + 115.8e6,
+                "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at this shape "
+                          "(346.9 MB + 115.8 MB; algorithmic 134.2 MB + 134.2 MB)"}
+
+
+def traffic_for(kernel: str, m: int, n: int, k: int):
+    if kernel.startswith(GEMM_TRAFFIC["kernel_prefix"]) and (m, n, k) == GEMM_TRAFFIC["shape"]:
+        return GEMM_TRAFFIC["bytes"]
+    return None
+
+
+def run_only(a):
+    """A few launches of one kernel family (see the module docstring), then "ok"."""
+    import torch
+
+    from y_b200 import quant as q
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    if a.only in ("step", "gemm", "quantize", "layer_ops"):
+        x = torch.randn(a.m, a.k, device=dev, dtype=torch.float16)
+    if a.only == "layer_ops":
+        r = torch.randn_like(x)
+        g = (torch.rand(a.k, device=dev) + 0.5).to(torch.float16)
+        heads = x.view(-1, 128)  # rows of one head each
+        pos = torch.randint(0, 4096, (heads.shape[0],), dtype=torch.int32, device=dev)
+        for _ in range(a.iters):
+            q.fused_add_rmsnorm(x, r, g, 1e-5)
+            q.rope(heads, pos)
+    elif a.only == "attention":
+        hq, hkv, hd, ps = 32, 8, 128, 16
+        pages = a.seqs * (a.seq_len // ps)
+        kc = torch.randn(pages, ps, hkv, hd, device=dev, dtype=torch.float16)
+        vc = torch.randn(pages, ps, hkv, hd, device=dev, dtype=torch.float16)
+        qv = torch.randn(a.seqs, hq, hd, device=dev, dtype=torch.float16)
+        pt = torch.randperm(pages, device=dev).to(torch.int32).view(a.seqs, a.seq_len // ps)
+        sl = torch.full((a.seqs,), a.seq_len, dtype=torch.int32, device=dev)
+        for _ in range(a.iters):
+            q.paged_decode_attention(qv, kc, vc, pt, sl)
+    elif a.only == "quantize":
+        for _ in range(a.iters):
+            q.quantize_fp8_dynamic(x)
+            q.quantize_fp8_dynamic(x, transpose=True)
+    elif a.only in ("step", "gemm"):
+        w = torch.randn(a.k, a.n, device=dev, dtype=torch.float16)
+        bqt, sb = q.quantize_fp8_dynamic(w, transpose=True)
+        del w
+        gamma = (torch.rand(a.k, device=dev) + 0.5).to(torch.float16)
+        aq, sa = q.quantize_fp8_dynamic(x)
+        bias = (torch.randn(a.n, device=dev) * 0.1).to(torch.float16)
+        for _ in range(a.iters):
+            if a.only == "step":
+                aq, sa = q.rmsnorm_quantize_fp8(x, gamma, EPS)
+            if a.epilogue == "swiglu":
+                q.gemm_fp8_swiglu_requant(aq, bqt, sa, sb, cta_n=a.cta_n)
+            elif a.epilogue == "bias_relu":
+                q.gemm_fp8_codes(aq, bqt, sa, sb, bias=bias, epilogue=q.EPI_BIAS_RELU,
+                                 out_dtype=torch.bfloat16, cta_n=a.cta_n)
+            else:
+                q.gemm_fp8_codes(aq, bqt, sa, sb, out_dtype=torch.bfloat16, cta_n=a.cta_n)
+    elif a.only == "f16_decode":
+        pool = [(torch.randn(4096, 4096, device=dev) / 64).to(torch.float16) for _ in range(16)]  # 16 x 33.5 MB > 4 x L2
+        xs = torch.randn(a.tokens, 4096, device=dev, dtype=torch.float16)
+        for i in range(a.iters):
+            q.gemm_f16_decode(xs, pool[i % len(pool)])
+    else:
+        k, n = DECODE_K, DECODE_N
+        w = (torch.randn(k, n, device=dev) / 64).to(torch.float16)
+        qw, sc = q.int4_quantize(w)
+        pool = [q.int4_repack(qw, sc) for _ in range(24)]  # 24 x 23 MB > 4 x L2
+        xs = torch.randn(a.tokens, k, device=dev, dtype=torch.float16)
+        out = torch.empty(a.tokens, n, device=dev, dtype=torch.float16)
+        for i in range(a.iters):
+            q.gemm_int4_decode(xs, pool[i % len(pool)], n, out=out)
+    torch.cuda.synchronize()
+    q.device_status()
+    _emit("ok")
 
 
 def main():
@@ -562,9 +832,22 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained leg (0 = skip)")
+    ap.add_argument("--only", default=None, choices=["step", "gemm", "decode", "f16_decode", "quantize", "layer_ops", "attention"],
+                    help="run a few launches of one kernel family (for a profiler capture) and print ok")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--seqs", type=int, default=16)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--cta-n", type=int, default=0)
+    ap.add_argument("--epilogue", default="none", choices=["none", "bias_relu", "swiglu"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the INT4 decode section")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-comparator", action="store_true", help="skip the cuBLASLt FP8 yardstick (a library kernel)")
     ap.add_argument("--cpu-rows", type=int, default=64)
     ap.add_argument("--clock-sampler", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
@@ -577,7 +860,9 @@ def main():
     os.dup2(2, 1)
     global _emit
     _emit = lambda text: os.write(real_stdout, (text + "\n").encode())
-    if args.impl == "reference":
+    if args.only is not None:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -55,10 +55,23 @@ Y_B200_API int y_ctx_memcpy_dtod(y_ctx* ctx, y_buf* dst, const y_buf* src);
  * for the runtime-shape entries below. Entries:
  *   from a descriptor, by the kernel's own name:
  *     gemm_fp8_<tag>(A f32*, B f32*, scale_a f32, scale_b f32, C f32*)
+ *     gemm_f16_<tag>(A f16*, B f16* [K,N], C f32*)                      tests/gemm_f16_decode_m1.ptx:6-9
+ *     gemm_f16_bias_relu_<tag>(A f16*, B f16* [K,N], Bias f32* [N], C f32*)  tests/gemm_f16_bias_relu_4096.ptx:6-10
+ *     gemm_f16_swiglu_<tag>(X f16*, Wgate f16* [K,N], Wup f16* [K,N], Out f32*)  tests/gemm_f16_swiglu_4096.ptx:6-10
+ *     rmsnorm_residual_<H>, rope_<d>, paged_decode_attention_<d>_<qh>_<kvh>_<page>[_<warps>]
+ *       (the kernel object owns the K-major weight copy the F16 families need; M <= 32 shapes of
+ *        gemm_f16_<tag> stream the row-major weights as they lie and need none)
  *   runtime-shape, image == NULL:
  *     y_fp8_gemm(Aq u8* [M,K], Bqt u8* [N,K], C bf16*, scale_a f32, scale_b f32, M i32, N i32, K i32)
  *       (argument order of y_fp8_tensor_core_gemm_kernel, tests/y_tensor_core_gemm.cu:4152-4159;
  *        B is K-major here and C is bf16)
+ *     y_fp8_gemm_bias_relu(Aq, Bqt, bias f16* [N], C bf16*, scale_a, scale_b, M, N, K, is_relu i32)
+ *     y_fp8_gemm_swiglu(Aq, Bqt gate|up interleaved [N,K], C bf16* [M,N/2], scale_a, scale_b, M, N, K)
+ *     y_tensor_core_gemm(A f16*, B f16* [K,N], C f16*, M, N, K)         tests/y_tensor_core_gemm.cu:102-107
+ *     y_fused_gemm_bias_relu_fp16(A, B, bias f16*, C f16*, M, N, K, is_relu)  tests/y_tensor_core_gemm.cu:2712-2719
+ *     y_fused_gemm_splitk_workspace(A, B, Workspace f32* [k_splits,M,N], M, N, K, k_splits)  :4732-4738
+ *     y_splitk_reduction(Workspace, C f16*, total, M, N, k_splits)      :4852-4858
+ *       (the split-K pair takes no launch geometry: the library cuts K itself)
  *     y_int4_decode_gemm(X f16*, Wstream u8*, Out f16*, M i32, N i32, K i32)
  *       (argument order of y_tensor_core_gemm_kernel, tests/y_tensor_core_gemm.cu:102-107)
  * Returns NULL with the reason in y_b200_last_error(). */
@@ -93,6 +106,31 @@ Y_B200_API int y_ctx_launch(y_ctx* ctx, y_kernel* kernel, const unsigned grid[3]
 Y_B200_API int y_ctx_time_launches(y_ctx* ctx, y_kernel* kernel, const unsigned grid[3],
                                    const unsigned block[3], unsigned shared_bytes, const y_arg* arg_sets,
                                    int n_sets, int nargs, unsigned iters, double* mean_us_out);
+
+/* ---- pipelined host path of the column-parallel step -------------------------------
+ * The asynchronous extension of the reference's synchronous host copies
+ * (src/cuda_runtime.rs:402-456) for the step
+ *   C [M, N_s] bf16 = fp8_gemm(e4m3(rmsnorm(X; gamma, eps)), Bt shard)
+ * with X and C in PINNED host memory. y_colpar_submit_host enqueues the host-to-device copy
+ * of this step, its three kernels and the device-to-host copy of its result on three
+ * internal streams; consecutive submissions overlap (copy-in of step i + 1, kernels of step
+ * i, copy-out of step i - 1). Device buffers are reused round-robin over `depth` slots
+ * (1..8). A host output buffer may be read once y_colpar_synchronize has returned, or on
+ * `caller_stream` after y_colpar_drain. The handle keeps the weight shard, its scale and
+ * gamma by pointer: they stay owned by the caller and must outlive it. One handle per GPU
+ * and host thread; create it with that GPU current.
+ *   bqt_e4m3 [N_s, K] e4m3 K-major, scale_b_dev one device float, gamma_f16 [K]; K % 16 == 0. */
+typedef struct y_colpar y_colpar;
+Y_B200_API y_colpar* y_colpar_create(const void* bqt_e4m3, const float* scale_b_dev, const void* gamma_f16, float eps,
+                                     int m, int k, int n_shard, int depth);
+Y_B200_API void y_colpar_destroy(y_colpar* handle);
+/* The step on device buffers, on `stream`, using slot `slot`'s scratch (no copies). */
+Y_B200_API int y_colpar_forward(y_colpar* handle, const void* x_dev_f16, void* c_dev_bf16, int slot, void* stream);
+/* Work already enqueued on `caller_stream` (e.g. the kernel that fills x_host) is ordered first. */
+Y_B200_API int y_colpar_submit_host(y_colpar* handle, const void* x_host_f16, void* c_host_bf16, void* caller_stream);
+Y_B200_API int y_colpar_drain(y_colpar* handle, void* caller_stream);
+Y_B200_API int y_colpar_synchronize(y_colpar* handle);
+Y_B200_API int y_colpar_host_bytes_per_step(const y_colpar* handle, size_t* h2d_out, size_t* d2h_out);
 
 /* ---- autotuner hooks (src/autotuner.rs, src/empirical_autotune.rs) ------------ */
 /* precision: 0 F16, 1 F32, 2 BF16, 3 FP8, 4 INT4. Strings are library-owned. */

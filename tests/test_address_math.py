@@ -172,3 +172,31 @@ def test_decode_tile_partition_covers_every_tile_once(tiles, sms):
     assert end == tiles and max(shares) - min(shares) <= 1
     if (tiles, sms) == (688, 148):
         assert shares == {4, 5}
+
+
+def _tile_coords(tile, m_tiles, n_tiles, group):
+    """Integer model of the persistent GEMM scheduler's tile order (tile_coords in gemm_fp8.cu):
+    grouped raster, odd groups walking the N tiles backwards."""
+    per_group = n_tiles * group
+    gid, off = divmod(tile, per_group)
+    first_m = gid * group
+    gsz = min(group, m_tiles - first_m)
+    tm, tn = first_m + off % gsz, off // gsz
+    if gid & 1:
+        tn = n_tiles - 1 - tn
+    return tm, tn
+
+
+def test_gemm_tile_order_is_a_bijection_and_turns_around_between_groups():
+    # the reference validates its swizzle on these grids (src/ptx_emitter.rs:7477-7513); the
+    # byte-sized groups of this build range from 1 to all M tiles
+    for m_tiles, n_tiles in [(1, 1), (1, 7), (7, 1), (8, 8), (32, 32), (16, 86), (33, 17), (5, 3), (100, 9)]:
+        for group in (1, 2, 3, 8, 16, 32, 1000):
+            group = min(group, m_tiles)
+            seen = [_tile_coords(t, m_tiles, n_tiles, group) for t in range(m_tiles * n_tiles)]
+            assert sorted(seen) == [(m, n) for m in range(m_tiles) for n in range(n_tiles)]
+            if m_tiles > group:
+                # the last N tile of the first group is the first N tile of the second
+                last_of_first = seen[n_tiles * group - 1]
+                first_of_second = seen[n_tiles * group]
+                assert last_of_first[1] == first_of_second[1] == n_tiles - 1

@@ -127,7 +127,8 @@ def test_other_reference_shapes_are_classified():
     assert "weight streaming" in dec and "Workspace required: 0 bytes" in dec and "tcgen05" not in dec
     out = (C.c_uint32 * 4)()
     assert lib.y_parse_launch_config(dec.encode(), 8, 4096, out) == 0
-    assert (out[0], out[1], out[2], out[3]) == (128, 1, 256, 81920)
+    assert (out[0], out[1], out[2], out[3]) == (64, 1, 256, 81920)   # 64-column blocks (the parser knows no clusters)
+    assert "Launch grid required: (256, 1, 1) CTAs, block (256,1,1), cluster (4,1,1)" in dec
     rms = ("kernel rmsnorm_residual_4096(X: GlobalMemory<F16>, Residual: GlobalMemory<F16>, "
            "Weight: GlobalMemory<F16>, Out: GlobalMemory<F16>, NewResidual: GlobalMemory<F16>) {\n}\n")
     assert "family=rmsnorm_residual" in runtime.compile_to_ptx(rms)

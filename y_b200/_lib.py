@@ -63,7 +63,7 @@ class LaunchInfo(C.Structure):
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m y_b200.build` (needs nvcc); "
+            f"{LIB_PATH} is missing: build it with `python y_b200/build.py` (needs nvcc); "
             "this package has no CPU or PyTorch fallback")
     return C.CDLL(LIB_PATH)
 
@@ -162,6 +162,13 @@ SIGNATURES.update({
     "y_ctx_launch": (_i, [_vp, _vp, _u3, _u3, C.c_uint, C.POINTER(Arg), _i]),
     "y_ctx_time_launches": (_i, [_vp, _vp, _u3, _u3, C.c_uint, C.POINTER(Arg), _i, _i, C.c_uint,
                                  C.POINTER(C.c_double)]),
+    "y_colpar_create": (_vp, [_vp, _vp, _vp, C.c_float, _i, _i, _i, _i]),
+    "y_colpar_destroy": (None, [_vp]),
+    "y_colpar_forward": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "y_colpar_submit_host": (_i, [_vp, _vp, _vp, _vp]),
+    "y_colpar_drain": (_i, [_vp, _vp]),
+    "y_colpar_synchronize": (_i, [_vp]),
+    "y_colpar_host_bytes_per_step": (_i, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),
     "y_autotune_persist_key": (_vp, [_u32, _u32, _u32, _i, C.c_char_p]),
     "y_autotune_parse_persisted": (_i, [C.c_char_p, _u32p]),
     "y_autotune_set_profile_path": (None, [C.c_char_p]),
@@ -179,7 +186,11 @@ SIGNATURES.update({
 })
 
 for _name, (_res, _args) in SIGNATURES.items():
-    _fn = getattr(lib, _name)
+    try:
+        _fn = getattr(lib, _name)
+    except AttributeError:
+        raise ImportError(f"{LIB_PATH} is older than this package (no symbol {_name}): rebuild it with "
+                          "`python y_b200/build.py`") from None
     _fn.restype = _res
     _fn.argtypes = _args
 

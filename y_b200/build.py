@@ -1,4 +1,8 @@
-"""Builds liby_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU)."""
+"""Builds liby_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
+
+Run it as a script (`python y_b200/build.py [--force] [-v]`): importing the package binds the
+shared library, which a fresh checkout does not have yet.
+"""
 from __future__ import annotations
 
 import os
@@ -8,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liby_b200.so")
-SOURCES = ["core.cu", "quantize.cu", "int4.cu", "gemm_fp8.cu", "gemm_f16.cu", "attention.cu", "autotuner.cu", "c_api.cu", "runtime.cu"]
+SOURCES = ["core.cu", "quantize.cu", "int4.cu", "gemm_fp8.cu", "gemm_f16.cu", "attention.cu", "autotuner.cu", "c_api.cu", "runtime.cu", "colpar.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math=false",

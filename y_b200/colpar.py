@@ -68,25 +68,39 @@ class _RawOut:
 
 class GatheredOutput:
     """The gathered output [world, M, N_s] of a column-parallel GEMM, filled by the GEMM's own
-    epilogue instead of a collective: every rank allocates the whole buffer in memory its
-    peers can map (CUDA IPC through the library), and each rank's GEMM stores its shard into
-    slot `rank` of every rank's buffer with plain NVLink stores. `barrier()` orders the ranks
-    on the current stream; after it every rank may read its `tensor_bytes()`.
+    epilogue instead of a collective: every rank allocates the buffers in memory its peers can
+    map (CUDA IPC through the library), and each rank's GEMM stores its shard into slot `rank`
+    of every rank's current buffer with plain NVLink stores. `barrier()` orders the ranks on
+    the current stream; after it every rank may read its current buffer.
+
+    Reuse. A peer may start the next step's GEMM (and with it the stores into this rank's
+    memory) as soon as its own `barrier()` has completed, which does not wait for this rank's
+    reads. So there are `buffers` (>= 2) buffers used in turn: `advance()` moves every rank to
+    the next one before the next step, and a buffer is written again only `buffers` steps
+    later, i.e. after at least one further `barrier()` that every rank enters only once its
+    reads of that buffer (enqueued on the same stream before the barrier) are done. The rule
+    for the caller: read the current buffer on the stream the step runs on, before the next
+    step's `barrier()` is enqueued there, and call `advance()` on every rank between steps.
+    With `buffers=1` the caller has to put a second `barrier()` after its reads itself.
     """
 
-    def __init__(self, m: int, n_shard: int, dtype=torch.bfloat16, group=None):
+    def __init__(self, m: int, n_shard: int, dtype=torch.bfloat16, group=None, buffers: int = 2):
         import ctypes as C
 
         from ._lib import check, lib
 
+        if buffers < 1:
+            raise ValueError("buffers must be >= 1")
         self._lib, self._check, self._C = lib, check, C
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.m, self.n_shard, self.dtype = m, n_shard, dtype
+        self.buffers, self.current = buffers, 0
         self.slot_bytes = m * n_shard * torch.empty((), dtype=dtype).element_size()
+        self.buffer_bytes = self.slot_bytes * self.world
         base = C.c_void_p()
-        check(lib.y_b200_peer_alloc(self.slot_bytes * self.world, C.byref(base)))
+        check(lib.y_b200_peer_alloc(self.buffer_bytes * buffers, C.byref(base)))
         self.base = base.value
         handle = C.create_string_buffer(64)
         check(lib.y_b200_peer_export(self.base, handle))
@@ -102,23 +116,31 @@ class GatheredOutput:
             self.peer_bases[r] = ptr.value
         self._token = torch.zeros(1, device="cuda")
 
+    def advance(self) -> None:
+        """Switch to the next buffer (every rank, between steps)."""
+        self.current = (self.current + 1) % self.buffers
+
+    def _buffer_offset(self) -> int:
+        return self.current * self.buffer_bytes
+
     def local_slot(self) -> int:
-        """Device address of this rank's slot in its own buffer (the GEMM's `c`)."""
-        return self.base + self.rank * self.slot_bytes
+        """Device address of this rank's slot in its own current buffer (the GEMM's `c`)."""
+        return self.base + self._buffer_offset() + self.rank * self.slot_bytes
 
     def replica_slots(self) -> list[int]:
-        """Device addresses of this rank's slot in every peer's buffer (the GEMM's replicas)."""
-        return [b + self.rank * self.slot_bytes for _, b in sorted(self.peer_bases.items())]
+        """Device addresses of this rank's slot in every peer's current buffer (the GEMM's replicas)."""
+        off = self._buffer_offset() + self.rank * self.slot_bytes
+        return [b + off for _, b in sorted(self.peer_bases.items())]
 
     def barrier(self) -> None:
         if self.world > 1:
             dist.all_reduce(self._token, group=self.group)  # stream-ordered on every rank
 
     def to_host(self) -> torch.Tensor:
-        """Copy of the whole gathered buffer as a CPU tensor [world, M, N_s] (for checks)."""
+        """Copy of the current gathered buffer as a CPU tensor [world, M, N_s] (for checks)."""
         out = torch.empty((self.world, self.m, self.n_shard), dtype=self.dtype)
         torch.cuda.synchronize()
-        self._check(self._lib.y_b200_peer_read(out.data_ptr(), self.base, self.slot_bytes * self.world))
+        self._check(self._lib.y_b200_peer_read(out.data_ptr(), self.base + self._buffer_offset(), self.buffer_bytes))
         return out
 
     def close(self) -> None:
@@ -142,12 +164,14 @@ class ColumnParallelFp8Linear:
     takes pinned host buffers: the host->device copy of step i+1, the kernels of step
     i and the device->host copy of step i-1 run on three streams at the same time, so
     the two directions of the host link and the GPU overlap; `drain` makes the current
-    stream wait for everything submitted. With more than one rank the activations are
-    the same on every rank, so each rank copies only its 1/world of the rows from the
-    host and the ranks all-gather the rest over NVLink (every rank must call
-    `submit_host` the same number of times). Buffers are reused round-robin over `depth`
-    slots; a host output buffer may be read after `drain` (or after the event
-    `submit_host` returns has completed).
+    stream wait for everything submitted. On one rank this is the library's own
+    `y_colpar_submit_host` / `y_colpar_drain` (the C entry a non-Python host binds), and this
+    class only holds the handle. With more than one rank the activations are the same on
+    every rank, so each rank copies only its 1/world of the rows from the host and the ranks
+    all-gather the rest over NVLink on the copy-in stream (every rank must call `submit_host`
+    the same number of times); that exchange is torch.distributed's, so this path keeps its
+    streams here. Buffers are reused round-robin over `depth` slots; a host output buffer may
+    be read after `drain` (or after the event `submit_host` returns has completed).
     """
 
     def __init__(self, bqt: torch.Tensor, scale_b, gamma: torch.Tensor, eps: float, m: int, depth: int = 2,
@@ -169,6 +193,7 @@ class ColumnParallelFp8Linear:
         self._x = self._c = None  # host-path staging, allocated on first use
         self._streams = None
         self._count = 0
+        self._handle = None       # y_colpar handle of the single-rank host path
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, slot: int = 0,
                 gathered: "GatheredOutput | None" = None) -> torch.Tensor:
@@ -182,6 +207,34 @@ class ColumnParallelFp8Linear:
                                 out=_RawOut(gathered.local_slot(), (self.m, self.n_shard), torch.bfloat16, x.device),
                                 replicas=gathered.replica_slots())
 
+    # ---- single rank: the library's pipelined host path -------------------------------------
+    def _c_handle(self):
+        if self._handle is None:
+            q = self._q
+            sb = self.scale_b
+            if not isinstance(sb, torch.Tensor):
+                sb = torch.tensor([float(sb)], dtype=torch.float32, device=self.bqt.device)
+            self._scale_b_dev = sb  # kept alive: the handle holds its address
+            h = q.lib.y_colpar_create(self.bqt.data_ptr(), sb.data_ptr(), self.gamma.data_ptr(), self.eps, self.m, self.k,
+                                      self.n_shard, self.depth)
+            if not h:
+                from ._lib import YB200Error, last_error
+                raise YB200Error(-4, last_error())
+            self._handle = h
+        return self._handle
+
+    def close(self) -> None:
+        if self._handle is not None:
+            self._q.lib.y_colpar_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- several ranks: the same pipeline with the row exchange on the copy-in stream ---------
     def _host_state(self):
         if self._streams is None:
             dev = self.bqt.device
@@ -195,7 +248,19 @@ class ColumnParallelFp8Linear:
                     e.record()
         return self._streams
 
-    def submit_host(self, x_host: torch.Tensor, c_host: torch.Tensor) -> torch.cuda.Event:
+    def _shares_rows(self) -> bool:
+        return self.world > 1 and self.m % self.world == 0
+
+    def submit_host(self, x_host: torch.Tensor, c_host: torch.Tensor):
+        """Enqueues one step with pinned host input and output. Returns an event that completes
+        with the copy-out (several ranks) or None (one rank: use `drain`)."""
+        if not (x_host.is_pinned() and c_host.is_pinned()):
+            raise ValueError("submit_host takes pinned host tensors")
+        if self.world == 1:
+            from ._lib import check
+            check(self._q.lib.y_colpar_submit_host(self._c_handle(), x_host.data_ptr(), c_host.data_ptr(),
+                                                   torch.cuda.current_stream(self.bqt.device).cuda_stream))
+            return None
         s_in, s_cmp, s_out = self._host_state()
         i = self._count % self.depth
         self._count += 1
@@ -205,19 +270,20 @@ class ColumnParallelFp8Linear:
         with torch.cuda.stream(s_in):
             s_in.wait_event(start)
             s_in.wait_event(cmp_done)  # the kernels that last read this slot's x are done
-            if self.world > 1 and self.m % self.world == 0:
+            if self._shares_rows():
                 rows = self.m // self.world
                 mine = slice(self.rank * rows, (self.rank + 1) * rows)
                 self._x[i][mine].copy_(x_host[mine], non_blocking=True)
+                # The exchange of the row blocks rides on the copy-in stream, so it overlaps the
+                # kernels of the step before; in place: this rank's rows already sit where the
+                # gather puts them.
+                dist.all_gather_into_tensor(self._x[i], self._x[i][mine], group=self.group)
             else:
-                mine = None
                 self._x[i].copy_(x_host, non_blocking=True)
             in_done.record()
         with torch.cuda.stream(s_cmp):
             s_cmp.wait_event(in_done)
             s_cmp.wait_event(out_done)  # the copy that last read this slot's c is done
-            if mine is not None:  # in place: this rank's rows are already where the gather puts them
-                dist.all_gather_into_tensor(self._x[i], self._x[i][mine], group=self.group)
             self.forward(self._x[i], out=self._c[i], slot=i)
             cmp_done.record()
         with torch.cuda.stream(s_out):
@@ -226,12 +292,24 @@ class ColumnParallelFp8Linear:
             out_done.record()
         return out_done
 
+    def host_api(self) -> str:
+        """The call a step with host buffers goes through."""
+        if self.world == 1:
+            return "y_colpar_submit_host / y_colpar_drain (C ABI; 3-stream pipeline inside the library)"
+        return ("y_b200.colpar.ColumnParallelFp8Linear.submit_host (3-stream pipeline; rows of X shared by "
+                "torch.distributed all-gather on the copy-in stream)")
+
     def host_bytes_per_step(self) -> tuple[int, int]:
         """(host->device, device->host) bytes this rank moves per `submit_host`."""
-        share = self.world if self.world > 1 and self.m % self.world == 0 else 1
+        share = self.world if self._shares_rows() else 1
         return self.m * self.k * 2 // share, self.m * self.n_shard * 2
 
     def drain(self) -> None:
+        if self.world == 1:
+            if self._handle is not None:
+                from ._lib import check
+                check(self._q.lib.y_colpar_drain(self._handle, torch.cuda.current_stream(self.bqt.device).cuda_stream))
+            return
         if self._streams is None:
             return
         cur = torch.cuda.current_stream(self.bqt.device)

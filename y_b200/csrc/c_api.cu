@@ -251,13 +251,18 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         const bool swiglu = fam == KernelFamily::GemmF16Swiglu;
         const bool decode = fam == KernelFamily::GemmF16 && k.m <= 32 && k.k % 16 == 0 && k.n % 8 == 0;
         if (decode) {
+            // as decode_k_slabs in gemm_f16.cu, for the default profile's 148 SMs
+            const long long blocks = (k.n + 63) / 64;
+            int slabs = 1;
+            for (int sl = 8; sl > 1; sl >>= 1)
+                if ((k.k / 16) % sl == 0 && blocks * sl <= 2 * 148) { slabs = sl; break; }
             snprintf(buf, sizeof buf,
-                     "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %dx32x16 | 8x1 warps | "
-                     "weight streaming, mma.sync.m16n8k16 f16 x f16 -> f32, K split across the warps of a CTA\n"
-                     "// Launch grid required: (%lld, 1, 1) CTAs, block (256,1,1).\n"
+                     "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %dx64x16 | 8x1 warps | "
+                     "weight streaming, mma.sync.m16n8k16 f16 x f16 -> f32, K split over a cluster of %d CTAs and the warps of each\n"
+                     "// Launch grid required: (%lld, 1, 1) CTAs, block (256,1,1), cluster (%d,1,1).\n"
                      "// Dynamic shared memory required: 81920 bytes.\n"
                      "// Workspace required: 0 bytes.\n",
-                     k.m, k.n, k.k, k.m <= 16 ? 16 : 32, (k.n + 31) / 32);
+                     k.m, k.n, k.k, k.m <= 16 ? 16 : 32, slabs, blocks * slabs, slabs);
         } else {
             const long long n_eff = swiglu ? 2 * k.n : k.n;
             Candidate c = autotune((uint32_t)k.m, (uint32_t)n_eff, (uint32_t)(2 * k.k), Precision::Fp8, "NVIDIA B200", 148);

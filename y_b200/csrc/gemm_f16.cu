@@ -68,20 +68,27 @@ int launch_transpose(const void* src, int rows, int cols, void* dst, int dst_mul
 
 // ---- small-M weight-streaming GEMM ---------------------------------------------------------
 // out [M, N] = x [M, K] @ w [K, N], M <= 32. HBM-bound: the K * N * 2 bytes of w are read once.
-// A CTA of 8 warps owns 32 output columns (a 64-byte run of every weight row). K is cut into
-// steps of 16 rows; warp v takes steps v, v + 8, ... so the CTA reads 128 adjacent rows at a
-// time, and streams its steps through a private ring of kStages 1 KB slots filled by per-thread
-// 16-byte cp.async copies (no producer warp, no barrier another agent has to complete). A
-// step is one mma.sync.m16n8k16 per 8 columns and 16 tokens: the tokens are the 16-row operand
-// (fragments straight from global memory, a few KB that stay in L1), the weights the 8-wide
-// one, read from the slot with ldmatrix.trans (w is row-major along N). The 16-byte units of a
-// slot row are XOR-swizzled so the eight row addresses of an ldmatrix phase hit eight
-// different bank groups. The warps' partial sums are added in warp order in shared memory:
-// no atomics, overwrite semantics, run-to-run identical.
+// A CTA of 8 warps owns 64 output columns, i.e. a 128-byte run of every weight row it reads
+// (64-byte runs reached a quarter of the HBM copy rate: too little per DRAM page). K is cut two
+// ways. Across CTAs: a thread-block cluster of S CTAs shares the 64 columns, CTA r taking the
+// r-th contiguous K slab, so that small N still fills the GPU (N = 4096: 64 column blocks x 4);
+// the slabs' partial tiles meet in the first CTA's shared memory over distributed shared memory
+// and are added there in rank order. Inside a CTA: the slab is cut into steps of 16 rows, warp
+// v takes the v-th contiguous eighth of them and streams it through a private ring of 2 KB
+// slots filled by per-thread 16-byte cp.async copies (no producer warp, no barrier another
+// agent has to complete). A step is one mma.sync.m16n8k16 per 8 columns and 16 tokens: the
+// tokens are the 16-row operand, the weights the 8-wide one, read from the slot with
+// ldmatrix.trans (w is row-major along N). The token fragments come straight from global
+// memory, four steps ahead of their use: consecutive steps of a warp share 128-byte lines of x
+// (with steps dealt round-robin to the warps every fragment load went to L2 and the kernel
+// spent its time on the long scoreboard: 7 stall cycles per issue, 12 % L1 hits). The 16-byte
+// units of a slot row are XOR-swizzled with the row index, so the eight row addresses of an
+// ldmatrix phase hit eight different bank groups. All sums are added in a fixed order (warp
+// order, then cluster rank order): no atomics, overwrite semantics, run-to-run identical.
 constexpr int kDecWarps = 8;
-constexpr int kDecCols = 32;
-constexpr int kDecStages = 10;
-constexpr int kDecSlotBytes = 16 * kDecCols * 2;  // 1 KB
+constexpr int kDecCols = 64;
+constexpr int kDecStages = 5;
+constexpr int kDecSlotBytes = 16 * kDecCols * 2;  // 2 KB
 constexpr int kDecSmemBytes = kDecWarps * kDecStages * kDecSlotBytes;  // 80 KB: two CTAs per SM
 
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t dst_smem, const void* src, bool valid) {
@@ -104,6 +111,16 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
 
 template <int MT, typename OutT>
 __global__ void __launch_bounds__(kDecWarps * 32)
@@ -111,26 +128,31 @@ __global__ void __launch_bounds__(kDecWarps * 32)
                       int M, int N, int K) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kDecCols;
-    const int steps = K / 16;
-    const int my_steps = warp < steps ? (steps - warp + kDecWarps - 1) / kDecWarps : 0;
+    const uint32_t rank = cluster_ctarank(), nranks = cluster_nctarank();
+    const int n0 = (int)(blockIdx.x / nranks) * kDecCols;
+    // This CTA's K slab, in steps of 16 rows (the host makes K / 16 a multiple of the cluster size).
+    const int slab_steps = K / 16 / (int)nranks;
+    const int per_warp = (slab_steps + kDecWarps - 1) / kDecWarps;
+    const int my_steps = max(0, min(per_warp, slab_steps - warp * per_warp));
+    const int step0 = (int)rank * slab_steps + warp * per_warp;  // this warp's first step
     const uint32_t ring = smem_u32(smem) + warp * (kDecStages * kDecSlotBytes);
     pdl_launch_dependents();
 
-    // This lane's two 16-byte units of a slot: rows lane / 4 and lane / 4 + 8, unit lane % 4.
-    const int crow = lane >> 2, cunit = lane & 3;
+    // This lane's four 16-byte units of a slot: rows lane / 8 + 4 j, unit lane % 8.
+    const int crow = lane >> 3, cunit = lane & 7;
     const bool col_ok = n0 + cunit * 8 < N;  // N % 8 == 0: a unit is wholly inside or outside
     // columns beyond N are zero-filled without a read; their source address stays inside the matrix
-    const __half* wsrc = w + (size_t)(16 * warp + crow) * N + (col_ok ? n0 + cunit * 8 : 0);
-    const size_t step_stride = (size_t)16 * kDecWarps * N;  // this warp's next step
-    const uint32_t dst0 = crow * 64 + ((cunit ^ ((crow >> 1) & 3)) << 4);
-    const uint32_t dst1 = (crow + 8) * 64 + ((cunit ^ (((crow + 8) >> 1) & 3)) << 4);
+    const __half* wsrc = w + (size_t)(16 * step0 + crow) * N + (col_ok ? n0 + cunit * 8 : 0);
+    const size_t step_stride = (size_t)16 * N;  // this warp's next step
     auto request = [&](int i) {  // step i of this warp into slot i % kDecStages; always commits a group
         if (i < my_steps) {
             const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
             const __half* s = wsrc + (size_t)i * step_stride;
-            cp_async_16_zfill(slot + dst0, s, col_ok);
-            cp_async_16_zfill(slot + dst1, s + (size_t)8 * N, col_ok);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int row = crow + 4 * j;
+                cp_async_16_zfill(slot + row * 128 + ((cunit ^ (row & 7)) << 4), s + (size_t)(4 * j) * N, col_ok);
+            }
         }
         cp_async_commit();
     };
@@ -140,22 +162,20 @@ __global__ void __launch_bounds__(kDecWarps * 32)
     pdl_wait();  // x is the previous kernel's output
 
     const int g = lane >> 2, c = lane & 3;
-    // ldmatrix row address of this lane inside a slot, for the two calls (16-byte units 0,1 / 2,3)
+    // ldmatrix row address of this lane inside a slot; call t reads the 16-byte units 2t and 2t + 1
     const int mrow = (lane & 7) + 8 * ((lane >> 3) & 1), munit = lane >> 4;
-    const uint32_t ld0 = mrow * 64 + ((munit ^ ((mrow >> 1) & 3)) << 4);
-    const uint32_t ld1 = mrow * 64 + (((munit + 2) ^ ((mrow >> 1) & 3)) << 4);
 
-    float acc[MT][4][4];
+    float acc[MT][8][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.0f;
 
     // Token fragments of one step: rows g and g + 8 of each 16-token tile, k = k0 + 2c (+1), k0 + 8 + 2c (+1).
     auto load_a = [&](int i, uint32_t (&a)[MT][4]) {
-        const int k0 = 16 * (warp + kDecWarps * i) + 2 * c;
+        const int k0 = 16 * (step0 + i) + 2 * c;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             const int ra = 16 * mt + g, rb = ra + 8;
@@ -171,54 +191,80 @@ __global__ void __launch_bounds__(kDecWarps * 32)
             }
         }
     };
-    uint32_t a_cur[MT][4], a_nxt[MT][4];
-    load_a(0, a_cur);
+    constexpr int kAhead = 4;  // token fragments are loaded this many steps before their MMAs
+    uint32_t a[kAhead][MT][4];
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) load_a(j, a[j]);
 #pragma unroll 1
-    for (int i = 0; i < my_steps; ++i) {
-        load_a(i + 1, a_nxt);
-        cp_async_wait<kDecStages - 1>();  // all but the newest kDecStages - 1 groups: step i has landed
-        __syncwarp();
-        const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
-        uint32_t b01[4], b23[4];
-        ldmatrix_x4_trans(slot + ld0, b01);
-        ldmatrix_x4_trans(slot + ld1, b23);
-        __syncwarp();  // every lane has read the slot
-        request(i + kDecStages);
+    for (int i0 = 0; i0 < my_steps; i0 += kAhead) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            mma_16816(acc[mt][0], a_cur[mt], b01[0], b01[1]);
-            mma_16816(acc[mt][1], a_cur[mt], b01[2], b01[3]);
-            mma_16816(acc[mt][2], a_cur[mt], b23[0], b23[1]);
-            mma_16816(acc[mt][3], a_cur[mt], b23[2], b23[3]);
+        for (int j = 0; j < kAhead; ++j) {
+            const int i = i0 + j;
+            if (i < my_steps) {  // uniform across the warp
+                cp_async_wait<kDecStages - 1>();  // all but the newest kDecStages - 1 groups: step i has landed
+                __syncwarp();
+                const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
+                uint32_t b[4][4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+                    ldmatrix_x4_trans(slot + mrow * 128 + (((2 * t + munit) ^ (mrow & 7)) << 4), b[t]);
+                __syncwarp();  // every lane has read the slot
+                request(i + kDecStages);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        mma_16816(acc[mt][2 * t], a[j][mt], b[t][0], b[t][1]);
+                        mma_16816(acc[mt][2 * t + 1], a[j][mt], b[t][2], b[t][3]);
+                    }
+                load_a(i + kAhead, a[j]);
+            }
         }
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) a_cur[mt][j] = a_nxt[mt][j];
     }
     cp_async_wait<0>();
     __syncthreads();  // the rings are free: they become the reduction area
     float* red = reinterpret_cast<float*>(smem);
-    constexpr int kPerWarp = MT * 4 * 32 * 4;  // floats a warp contributes
+    constexpr int kPerWarp = MT * 8 * 32 * 4;  // floats a warp contributes (at most 8 KB)
+    float* tile = red + kDecWarps * kPerWarp;   // this CTA's reduced tile, read by the cluster's first CTA
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-            *reinterpret_cast<float4*>(red + warp * kPerWarp + ((mt * 4 + nt) * 32 + lane) * 4) =
+        for (int nt = 0; nt < 8; ++nt)
+            *reinterpret_cast<float4*>(red + warp * kPerWarp + ((mt * 8 + nt) * 32 + lane) * 4) =
                 make_float4(acc[mt][nt][0], acc[mt][nt][1], acc[mt][nt][2], acc[mt][nt][3]);
     __syncthreads();
     for (int e = threadIdx.x; e < kPerWarp; e += kDecWarps * 32) {
         float v = red[e];
 #pragma unroll
         for (int wv = 1; wv < kDecWarps; ++wv) v += red[wv * kPerWarp + e];
-        const int i = e & 3, l = (e >> 2) & 31, nt = (e >> 7) & 3, mt = e >> 9;
-        const int row = 16 * mt + (l >> 2) + 8 * (i >> 1);
-        const int col = n0 + 8 * nt + 2 * (l & 3) + (i & 1);
-        if (row < M && col < N) {
-            if constexpr (sizeof(OutT) == 4) out[(size_t)row * N + col] = v;
-            else out[(size_t)row * N + col] = __float2half_rn(v);
+        tile[e] = v;
+    }
+    if (nranks > 1) cluster_sync_all();  // every CTA's tile is complete and visible across the cluster
+    if (rank == 0) {
+        const uint32_t tile_addr = smem_u32(tile);
+        for (int e = threadIdx.x; e < kPerWarp; e += kDecWarps * 32) {
+            float v = tile[e];
+            for (uint32_t r = 1; r < nranks; ++r) v += ld_shared_cluster_f32(mapa_shared(tile_addr + 4u * (uint32_t)e, r));
+            const int i = e & 3, l = (e >> 2) & 31, nt = (e >> 7) & 7, mt = e >> 10;
+            const int row = 16 * mt + (l >> 2) + 8 * (i >> 1);
+            const int col = n0 + 8 * nt + 2 * (l & 3) + (i & 1);
+            if (row < M && col < N) {
+                if constexpr (sizeof(OutT) == 4) out[(size_t)row * N + col] = v;
+                else out[(size_t)row * N + col] = __float2half_rn(v);
+            }
         }
     }
+    if (nranks > 1) cluster_sync_all();  // no CTA leaves while its tile can still be read
+}
+
+// Cluster size (K slabs per 64-column block): the largest of 8, 4, 2, 1 that divides K / 16 and
+// keeps the grid within two CTAs per SM, so narrow matrices still spread over the whole GPU.
+int decode_k_slabs(int n, int k) {
+    const int blocks = (n + kDecCols - 1) / kDecCols;
+    const int cap = 2 * sm_count();
+    for (int s = 8; s > 1; s >>= 1)
+        if ((k / 16) % s == 0 && blocks * s <= cap) return s;
+    return 1;
 }
 
 template <int MT, typename OutT>
@@ -230,10 +276,24 @@ int launch_f16_decode(const void* x, int ldx, const void* w, void* out, int m, i
         YB_CUDA(cudaFuncSetAttribute(f16_decode_kernel<MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes));
         configured[dev] = true;
     }
-    const unsigned grid = (unsigned)((n + kDecCols - 1) / kDecCols);
-    return check_cuda(launch_pdl(f16_decode_kernel<MT, OutT>, dim3(grid), dim3(kDecWarps * 32), (size_t)kDecSmemBytes, st,
-                                 static_cast<const __half*>(x), ldx, static_cast<const __half*>(w), static_cast<OutT*>(out),
-                                 m, n, k),
+    const int slabs = decode_k_slabs(n, k);
+    const unsigned grid = (unsigned)((n + kDecCols - 1) / kDecCols) * (unsigned)slabs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kDecWarps * 32);
+    cfg.dynamicSmemBytes = kDecSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)slabs;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return check_cuda(cudaLaunchKernelEx(&cfg, f16_decode_kernel<MT, OutT>, static_cast<const __half*>(x), ldx,
+                                         static_cast<const __half*>(w), static_cast<OutT*>(out), m, n, k),
                       "f16_decode_kernel launch");
 }
 
@@ -254,8 +314,9 @@ size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 }  // namespace
 
 // Launch geometry of the weight-streaming kernel for the host launch API.
-void f16_decode_launch_geometry(int n, unsigned* grid, unsigned* block, unsigned* smem, int* stages) {
-    *grid = (unsigned)((n + kDecCols - 1) / kDecCols);
+void f16_decode_launch_geometry(int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster) {
+    *cluster = (unsigned)decode_k_slabs(n, k);
+    *grid = (unsigned)((n + kDecCols - 1) / kDecCols) * *cluster;
     *block = kDecWarps * 32;
     *smem = kDecSmemBytes;
     *stages = kDecStages;

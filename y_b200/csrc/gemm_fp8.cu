@@ -63,7 +63,6 @@ constexpr int kEpiSmemBytes = kBiasBytes + kEpiWarps * kRepStageBytes;
 // chunks per flush instead, so that every store instruction to peer memory writes whole
 // 128-byte lines (64-byte runs reached 0.43 TB/s of NVLink egress with seven peers).
 constexpr int kRepStageBytesWide = 2 * kRepStageBytes;
-constexpr int kSwizzleGroup = 8;  // M-tiles per raster group
 
 struct GemmParams {
     void* c;
@@ -78,6 +77,7 @@ struct GemmParams {
     unsigned int* amax_out;
     DeviceStatus* status;
     int m_tiles, n_tiles;
+    int raster_group;  // M-tiles per raster group (tile_coords)
     void* c_rep[Y_B200_MAX_REPLICAS];  // further destinations of every output element (peer memory)
     int n_rep;
     int full_units;  // CTA-pair kernel: work units below this index are whole 256 x 256 tiles, the rest half tiles
@@ -98,13 +98,21 @@ struct GemmCfg {
     static constexpr int smem_bytes = stages * stage_bytes + bar_bytes + 1024;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& tm, int& tn) {
-    const int per_group = n_tiles * kSwizzleGroup;
+// Grouped raster order (the reference's emit_grid_swizzle_code, src/ptx_emitter.rs:2222-2284,
+// as a persistent scheduler's tile sequence): `group` M-tiles at a time walk all N-tiles,
+// column first, so the CTAs running together share A and B panels through L2. Two changes
+// against the reference's fixed group of 8, both measured on the 8192^3 launch (ncu DRAM
+// bytes, CUDA-event times): the group is sized by bytes (see raster_group_for) and
+// odd groups walk the N-tiles backwards, so the B panels a group ends on are the ones the
+// next group starts with while they are still in L2.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group, int& tm, int& tn) {
+    const int per_group = n_tiles * group;
     const int gid = tile / per_group, off = tile % per_group;
-    const int first_m = gid * kSwizzleGroup;
-    const int gsz = min(kSwizzleGroup, m_tiles - first_m);
+    const int first_m = gid * group;
+    const int gsz = min(group, m_tiles - first_m);
     tm = first_m + off % gsz;
     tn = off / gsz;
+    if (gid & 1) tn = n_tiles - 1 - tn;
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
@@ -357,7 +365,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+                tile_coords(tile, p.m_tiles, p.n_tiles, p.raster_group, tm, tn);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1u, abort_flag)) {
                         report_timeout(p.status, abort_flag, 0x10u, (unsigned)kb);
@@ -434,7 +442,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             int tm, tn;
-            tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+            tile_coords(tile, p.m_tiles, p.n_tiles, p.raster_group, tm, tn);
             const uint32_t as = it & 1, aphase = (it >> 1) & 1;
             const int col_base = tn * BN + half * (BN / 2);
             if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane);
@@ -501,7 +509,7 @@ __device__ __forceinline__ void pair_unit(const GemmParams& p, int u, int& tm, i
         half = (u - p.full_units) & 1;
         bn = 128;
     }
-    tile_coords(tile, p.m_tiles, p.n_tiles, tm, tn);
+    tile_coords(tile, p.m_tiles, p.n_tiles, p.raster_group, tm, tn);
     col0 = tn * 256 + half * 128;
 }
 
@@ -874,6 +882,19 @@ PairUnits pair_units(long long tiles, int pairs) {
     return {(int)tiles, (int)tiles};
 }
 
+// M-tiles per raster group: as many as keep the group's A panel (group x tile_m rows of K bytes)
+// within 32 MiB. The whole B matrix streams past each group once, so fewer, larger groups mean
+// fewer passes over B, until the A panel no longer survives in L2 beside them. Measured on
+// 8192^3 e4m3 (A, B 67 MB each, 256-row tiles): 8 tiles per group (16.8 MB) 342 MB of DRAM
+// reads per launch and 370.5 us; 16 (33.5 MB) with the serpentine order 219 MB and 364.2 us;
+// 32 (all of A, 67 MB) 554 MB and 399.7 us.
+int raster_group_for(int tile_m, int k_bytes, int m_tiles) {
+    long long g = (32LL << 20) / ((long long)tile_m * k_bytes);
+    if (g < 1) g = 1;
+    if (g > m_tiles) g = m_tiles;
+    return (int)g;
+}
+
 // Builds the tensor maps for `tile`, sizes the persistent grid and launches.
 // `p` arrives with everything but m_tiles / n_tiles filled in.
 int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, int epi, int out_kind,
@@ -886,6 +907,7 @@ int launch_tiled(const void* a, const void* bt, GemmParams p, TileShape tile, in
     if ((rc = make_operand_map(&tb, bt, p.n, p.k_bytes, tile.cta_m == 256 ? 128 : tile.cta_n))) return rc;
     p.m_tiles = (p.m + tile.cta_m - 1) / tile.cta_m;
     p.n_tiles = (p.n + tile.cta_n - 1) / tile.cta_n;
+    p.raster_group = raster_group_for(tile.cta_m, p.k_bytes, p.m_tiles);
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles > 0x3fffffffLL) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: too many tiles");
     int cap = max_ctas > 0 ? max_ctas : sm_count();
@@ -1036,7 +1058,7 @@ extern "C" int y_b200_gemm_fp8_f32(const float* a, const float* b, float scale_a
         return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_fp8_f32: a, b need 16-byte and workspace 256-byte alignment");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     char* ws = static_cast<char*>(workspace);
-    const size_t a_bytes = ((size_t)m * k + 255) & ~(size_t)255, b_bytes = ((size_t)n * k + 255) & ~(size_t)255;
+    const size_t a_bytes = ((size_t)m * k + 255) & ~(size_t)255;
     void* aq = ws;
     void* bq = ws + a_bytes;
     int rc = quantize_with_host_scale(a, Y_B200_F32, (size_t)m, (size_t)k, false, scale_a, aq, st);

@@ -41,7 +41,7 @@ struct y_kernel {
 
 namespace yb {
 void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsigned* smem, int* slots, int* unit_k);
-void f16_decode_launch_geometry(int n, unsigned* grid, unsigned* block, unsigned* smem, int* stages);
+void f16_decode_launch_geometry(int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
 }
 using namespace yb;
 
@@ -116,10 +116,10 @@ int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out
     const bool f16 = k->entry == Entry::GemmF16 || k->entry == Entry::GemmF16BiasRelu || k->entry == Entry::GemmF16Swiglu ||
                      k->entry == Entry::TensorCoreGemm || k->entry == Entry::FusedGemmBiasReluFp16;
     if ((k->entry == Entry::GemmF16 || k->entry == Entry::TensorCoreGemm) && uses_decode_kernel(m, n, kk)) {
-        f16_decode_launch_geometry(n, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages);
+        f16_decode_launch_geometry(n, kk, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages, &out->cluster[0]);
         out->grid[1] = out->grid[2] = out->block[1] = out->block[2] = 1;
-        out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
-        out->cta_m = m <= 16 ? 16 : 32; out->cta_n = 32; out->cta_k = 16;
+        out->cluster[1] = out->cluster[2] = 1;
+        out->cta_m = m <= 16 ? 16 : 32; out->cta_n = 64; out->cta_k = 16;
         return 0;
     }
     // An f16 problem runs the byte-tiled kernels on rows of 2 K bytes; SwiGLU on 2 N interleaved columns.
