@@ -343,21 +343,26 @@ def other_config_metrics(peaks):
                                      "bytes": "read and write 23.2 MB each (L2-resident at this size: once per weight matrix, not a hot path)"}
     del wsets, qw, sc, stream
     # F16 family: the reference's decode fixture shape (weights [4096, 4096] f16 streamed once,
-    # 16 rotating buffers = 4 x L2) and the tensor-core GEMM on K-major f16 operands
-    wpool = [(torch.randn(4096, 4096, device="cuda") / 64).to(torch.float16) for _ in range(16)]
-    for mtok in (1, 8, 32):
-        xs = torch.randn(mtok, 4096, device="cuda", dtype=torch.float16)
-        it[0] = 0
+    # 16 rotating buffers = 4 x L2) through the launch API's own timing loop, under the
+    # reference's .cu entry name, and the tensor-core GEMM on K-major f16 operands
+    from y_b200 import runtime as rt
 
-        def f16_dec():
-            q.gemm_f16_decode(xs, wpool[it[0] % 16], out_dtype=torch.float32)
-            it[0] += 1
-
-        us = timeit(f16_dec, iters=64, warm=16)
-        nbytes = 4096 * 4096 * 2 + mtok * 4096 * 2 + mtok * 4096 * 4
-        out[f"f16_decode_m{mtok}_4096x4096"] = {"us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1),
-                                                 "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes}
-    del wpool
+    ctx = rt.CudaContext.new()
+    kern = ctx.load_module(None, "y_tensor_core_gemm")
+    for nn2 in (4096, DECODE_N):
+        wpool = [(torch.randn(4096, nn2, device="cuda") / 64).to(torch.float16) for _ in range(16 if nn2 == 4096 else 8)]
+        for mtok in (1, 8, 32):
+            xs = torch.randn(mtok, 4096, device="cuda", dtype=torch.float16)
+            o16 = torch.empty(mtok, nn2, device="cuda", dtype=torch.float16)
+            sets = [[xs.data_ptr(), wp.data_ptr(), o16.data_ptr(), ("i32", mtok), ("i32", nn2), ("i32", 4096)] for wp in wpool]
+            ctx.time_launches(kern, None, None, 0, sets, len(sets))
+            us = min(ctx.time_launches(kern, None, None, 0, sets, 100) for _ in range(5))
+            nbytes = 4096 * nn2 * 2 + mtok * 4096 * 2 + mtok * nn2 * 2
+            out[f"f16_decode_m{mtok}_4096x{nn2}"] = {"us": round(us, 2), "gb_s": round(nbytes / us / 1e3, 1),
+                                                      "frac_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4), "bytes": nbytes}
+        del wpool
+    kern.free()
+    ctx.close()
     m = n = k = 4096
     sets = [(torch.randn(m, k, device="cuda", dtype=torch.float16), (torch.randn(n, k, device="cuda") / 64).to(torch.float16),
              torch.empty(m, n, device="cuda", dtype=torch.float32)) for _ in range(2)]

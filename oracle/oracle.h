@@ -9,13 +9,18 @@
  * Pinning status (what fixes the results independently of this file):
  *   - f16 decode, input generator, y_block_cdiv, grouped-raster swizzle:
  *     pinned by the reference's own known-answer tests.
- *   - e4m3 encode/decode: the reference holds no golden vector for it
- *     ("parity unpinned" by the reference); pinned here against two
- *     independent implementations (torch CPU float8_e4m3fn and the host
- *     conversion in cuda_fp8.h) over every code and every rounding midpoint.
- *   - INT4 group quantise/pack and all GEMM outputs: parity unpinned by the
- *     reference (it has no INT4 implementation and gates GEMMs on tolerance
- *     against torch on a GPU only).
+ *   - e4m3 encode/decode, the FP8 and F16 GEMMs with their scale, bias+ReLU and
+ *     SwiGLU epilogues, fused add+RMSNorm, RoPE and paged decode attention:
+ *     pinned against the reference's own emitted kernels (its PTX fixtures,
+ *     assembled unchanged for sm_100a by make_ref.py into _ref/) run on a B200
+ *     on the same inputs - bit for bit where the arithmetic is exact (every
+ *     e4m3 code, exact-integer GEMMs, the residual stream), by the reference's
+ *     own gates elsewhere. Outputs of those kernels recorded on a B200 are
+ *     committed with the tests, so the pin also holds without a GPU.
+ *     The e4m3 codec is additionally pinned against torch CPU float8_e4m3fn
+ *     and the host conversion in cuda_fp8.h over every code and midpoint.
+ *   - INT4 group quantise/pack/decode: parity unpinned (the reference has no
+ *     INT4 implementation; the format is defined by this file).
  */
 #ifndef Y_B200_ORACLE_H
 #define Y_B200_ORACLE_H

@@ -149,6 +149,10 @@ def test_argument_errors_are_codes_not_crashes():
     assert lib.y_b200_gemm_f16_rowmajor_workspace_bytes(4096, 4096) == 4096 * 4096 * 2
     assert lib.y_b200_gemm_f16_swiglu_workspace_bytes(11008, 4096) == 2 * 11008 * 4096 * 2
     assert lib.y_b200_gemm_f16(None, None) == _lib.ERR_INVALID
+    assert not lib.y_colpar_create(None, None, None, 1e-6, 8, 16, 8, 2) and "null" in _lib.last_error()
+    assert lib.y_colpar_submit_host(None, None, None, None) == _lib.ERR_INVALID
+    assert lib.y_colpar_drain(None, None) == _lib.ERR_INVALID
+    lib.y_colpar_destroy(None)
     assert lib.y_b200_gemm_f16_decode(None, 0, None, None, 0, 1, 8, 16, None) == _lib.ERR_INVALID
     one = C.c_int(0)
     p = C.addressof(one)

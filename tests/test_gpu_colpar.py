@@ -62,6 +62,32 @@ def test_step_at_the_benchmark_shape(cuda):
         assert torch.equal(layer.forward(x), c)
 
 
+def test_c_abi_handle_forward_and_shape_errors(layer_and_inputs):
+    """y_colpar_forward (the device path behind the C handle) gives the operator's result, and a
+    bad shape or depth is an error code at creation."""
+    from y_b200._lib import check, last_error, lib
+    layer, xs, g, bqt_h, sb, q = layer_and_inputs
+    want = layer.forward(f16_dev(xs[1])).clone()
+    sb_dev = torch.tensor([sb], dtype=torch.float32, device="cuda")
+    h = lib.y_colpar_create(layer.bqt.data_ptr(), sb_dev.data_ptr(), layer.gamma.data_ptr(), 1e-6, layer.m, layer.k,
+                            layer.n_shard, 2)
+    assert h, last_error()
+    x = f16_dev(xs[1])
+    c = torch.empty(layer.m, layer.n_shard, dtype=torch.bfloat16, device="cuda")
+    for slot in (0, 1):
+        c.zero_()
+        check(lib.y_colpar_forward(h, x.data_ptr(), c.data_ptr(), slot, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert torch.equal(c, want)
+    assert lib.y_colpar_forward(h, x.data_ptr(), c.data_ptr(), 2, None) != 0 and "slot" in last_error()
+    lib.y_colpar_destroy(h)
+    assert not lib.y_colpar_create(layer.bqt.data_ptr(), sb_dev.data_ptr(), layer.gamma.data_ptr(), 1e-6, layer.m, 24,
+                                   layer.n_shard, 2)
+    assert not lib.y_colpar_create(layer.bqt.data_ptr(), sb_dev.data_ptr(), layer.gamma.data_ptr(), 1e-6, layer.m, layer.k,
+                                   layer.n_shard, 9)
+    q.device_status()
+
+
 def test_host_pipeline_equals_device_path_step_by_step(layer_and_inputs):
     layer, xs, g, bqt_h, sb, q = layer_and_inputs
     m, k, n = layer.m, layer.k, layer.n_shard

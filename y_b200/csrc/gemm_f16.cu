@@ -191,7 +191,10 @@ __global__ void __launch_bounds__(kDecWarps * 32)
             }
         }
     };
-    constexpr int kAhead = 4;  // token fragments are loaded this many steps before their MMAs
+    // Token fragments are loaded this many steps before their MMAs. With two 16-token tiles the
+    // deeper prefetch costs the registers that let two CTAs share an SM (measured: 22 us against
+    // 14.6 us at 32 tokens, K = N = 4096), so it stays at one step there.
+    constexpr int kAhead = MT == 1 ? 4 : 1;
     uint32_t a[kAhead][MT][4];
 #pragma unroll
     for (int j = 0; j < kAhead; ++j) load_a(j, a[j]);
