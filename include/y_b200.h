@@ -53,7 +53,12 @@ Y_B200_API int y_b200_selftest_bounded_wait(unsigned long long cycles, void* str
 
 /* ---- element kinds ---------------------------------------------------------- */
 enum { Y_B200_F32 = 0, Y_B200_F16 = 1, Y_B200_BF16 = 2, Y_B200_E4M3 = 3 };
-enum { Y_B200_EPI_NONE = 0, Y_B200_EPI_BIAS = 1, Y_B200_EPI_BIAS_RELU = 2, Y_B200_EPI_SWIGLU = 3 };
+/* The reference's activation functor set (src/quantization_pass.rs:667-798: None, ReLU, GELU,
+ * SiLU) plus the gated SwiGLU. GELU is the reference's own tanh form,
+ * 0.5 x (1 + tanh(x (0.79788456 + 0.044715 x^2))); SiLU is x / (1 + exp(-x)). For BIAS_GELU and
+ * BIAS_SILU the bias pointer may be NULL (no bias). */
+enum { Y_B200_EPI_NONE = 0, Y_B200_EPI_BIAS = 1, Y_B200_EPI_BIAS_RELU = 2, Y_B200_EPI_SWIGLU = 3,
+       Y_B200_EPI_BIAS_GELU = 4, Y_B200_EPI_BIAS_SILU = 5 };
 
 /* ---- FP8 quantisation -------------------------------------------------------
  * Replaces the quantise+stage loops fused into the reference's FP8 GEMM

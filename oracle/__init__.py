@@ -15,7 +15,7 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_SWIGLU = 0, 1, 2, 3
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_SWIGLU, EPI_BIAS_GELU, EPI_BIAS_SILU = 0, 1, 2, 3, 4, 5
 OUT_F32, OUT_F16, OUT_BF16 = 0, 1, 2
 BIAS_NONE, BIAS_F16, BIAS_F32 = 0, 1, 2
 

@@ -513,6 +513,17 @@ static float swiglu(float g, float u) {
     return (g * sig) * u;
 }
 
+/* The reference's fused GELU (src/quantization_pass.rs:748-796): 0.5 x (1 + tanh(x * p)) with
+ * p = fma(x^2, 0.044715, 0.79788456) exactly as its emitter writes it (the cubic coefficient
+ * is not multiplied by sqrt(2/pi) there), all f32; the emitted code uses tanh.approx. */
+static float gelu_ref(float x) {
+    float p = fmaf(x * x, 0.044715f, 0.79788456f);
+    return (0.5f * x) * (1.0f + tanhf(x * p));
+}
+
+/* silu(x) = x * 1/(1 + exp(-x)) (src/quantization_pass.rs:716-747). */
+static float silu_ref(float x) { return x * (1.0f / (1.0f + expf(-x))); }
+
 static void epilogue_row(const float* acc, size_t N, float scale, const void* bias,
                          int bias_kind, int epilogue, int out_kind, void* out, size_t out_row) {
     if (epilogue == ORC_EPI_SWIGLU) {
@@ -527,9 +538,12 @@ static void epilogue_row(const float* acc, size_t N, float scale, const void* bi
         /* C = acc * (sa*sb): the scale product is formed once and applied
          * after the sum (src/ptx_emitter.rs:3532-3566). */
         float v = acc[c] * scale;
-        if (epilogue == ORC_EPI_BIAS || epilogue == ORC_EPI_BIAS_RELU)
+        if (epilogue == ORC_EPI_BIAS || epilogue == ORC_EPI_BIAS_RELU ||
+            ((epilogue == ORC_EPI_BIAS_GELU || epilogue == ORC_EPI_BIAS_SILU) && bias != NULL))
             v = v + bias_at(bias, bias_kind, c);                 /* :4804-4806 */
         if (epilogue == ORC_EPI_BIAS_RELU) v = v > 0.0f ? v : 0.0f; /* :4807-4808 */
+        if (epilogue == ORC_EPI_BIAS_GELU) v = gelu_ref(v);
+        if (epilogue == ORC_EPI_BIAS_SILU) v = silu_ref(v);
         store_out(out, out_kind, out_row * N + c, v);
     }
 }

@@ -89,7 +89,8 @@ void  orc_rmsnorm_quantize_fp8(const uint16_t* x, const uint16_t* gamma,
                                uint8_t* q, float* scale_out);
 
 /* ---- FP8 GEMM + epilogues ---------------------------------------------- */
-enum { ORC_EPI_NONE = 0, ORC_EPI_BIAS = 1, ORC_EPI_BIAS_RELU = 2, ORC_EPI_SWIGLU = 3 };
+enum { ORC_EPI_NONE = 0, ORC_EPI_BIAS = 1, ORC_EPI_BIAS_RELU = 2, ORC_EPI_SWIGLU = 3,
+       ORC_EPI_BIAS_GELU = 4, ORC_EPI_BIAS_SILU = 5 };  /* bias may be absent for 4 and 5 */
 enum { ORC_OUT_F32 = 0, ORC_OUT_F16 = 1, ORC_OUT_BF16 = 2 };
 enum { ORC_BIAS_NONE = 0, ORC_BIAS_F16 = 1, ORC_BIAS_F32 = 2 };
 

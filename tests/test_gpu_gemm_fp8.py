@@ -121,6 +121,28 @@ def test_bias_relu_epilogue(q, m, n, k, bias_dtype, cta_m):
             assert got.min() >= 0.0
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (130, 72, 192)])
+@pytest.mark.parametrize("cta_m", [128, 256])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_gelu_and_silu_epilogues(q, m, n, k, cta_m, with_bias):
+    """The rest of the reference's activation functor set (src/quantization_pass.rs:716-796):
+    its tanh-form GELU (with the coefficients exactly as its emitter writes them) and SiLU, fused
+    after the optional bias add; the device uses tanh.approx / ex2.approx as the emitted code does,
+    the oracle libm, so the comparison is by the GEMM tolerance."""
+    _, _, sa, sb, aq, bqt = quantised_operands(m, n, k)
+    sa, sb = sa / 8, sb / 8          # keep the pre-activations in the curved part of both functions
+    bias = oracle.fill_normal_f16(n, oracle.SEED_B + 1, 0.5)
+    for epi, oepi in ((q.EPI_BIAS_GELU, oracle.EPI_BIAS_GELU), (q.EPI_BIAS_SILU, oracle.EPI_BIAS_SILU)):
+        c = q.gemm_fp8_codes(dev(aq), dev(bqt), sa, sb, bias=f16_dev(bias) if with_bias else None, epilogue=epi,
+                             out_dtype=torch.float32, cta_m=cta_m)
+        q.device_status()
+        ref = oracle.gemm_fp8(aq, bqt, sa, sb, bias=bias if with_bias else None, epilogue=oepi)
+        pre = oracle.gemm_fp8(aq, bqt, sa, sb, bias=bias if with_bias else None,
+                              epilogue=oracle.EPI_BIAS if with_bias else oracle.EPI_NONE)
+        assert np.abs(ref - pre).max() > 0.05        # the activation did something
+        assert_gemm_close(c.cpu().numpy(), ref, f"epilogue {epi}, bias {with_bias}")
+
+
 @pytest.mark.parametrize("m,n,k", [(256, 512, 256), (100, 88, 128), (2048, 2560, 128)])
 @pytest.mark.parametrize("cta_m", [128, 256])
 def test_swiglu_requant(q, m, n, k, cta_m):

@@ -194,6 +194,16 @@ def test_gemm_oracle_matches_float64_matmul_and_epilogues():
     assert np.abs(h - refh).max() <= 1e-5 * np.abs(refh).max() + 1e-6
     part = oracle.gemm_fp8(aq, bqt, sa, sb, row_begin=5, row_count=4)
     assert np.array_equal(part, c[5:9])
+    # the reference's GELU (its coefficients as emitted, src/quantization_pass.rs:748-796) and SiLU
+    x = ref / 64 + bias.view(np.float16).astype(np.float64)
+    cg = oracle.gemm_fp8(aq, bqt, sa / 8, sb / 8, bias=bias, epilogue=oracle.EPI_BIAS_GELU)
+    refg = 0.5 * x * (1 + np.tanh(x * (0.79788456 + 0.044715 * x * x)))
+    assert np.abs(cg - refg).max() <= 1e-5 * np.abs(refg).max() + 1e-6
+    cs = oracle.gemm_fp8(aq, bqt, sa / 8, sb / 8, bias=bias, epilogue=oracle.EPI_BIAS_SILU)
+    assert np.abs(cs - x / (1 + np.exp(-x))).max() <= 1e-5 * np.abs(x).max() + 1e-6
+    x0 = ref / 64
+    c0 = oracle.gemm_fp8(aq, bqt, sa / 8, sb / 8, epilogue=oracle.EPI_BIAS_SILU)      # no bias given
+    assert np.abs(c0 - x0 / (1 + np.exp(-x0))).max() <= 1e-5 * np.abs(x0).max() + 1e-6
 
 
 def test_rmsnorm_oracle():

@@ -16,7 +16,7 @@ OK = 0
 ERR_INVALID, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_WORKSPACE, ERR_DEVICE, ERR_UNSUPPORTED = (
     -1, -2, -3, -4, -5, -6, -7)
 F32, F16, BF16, E4M3 = 0, 1, 2, 3
-EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_SWIGLU = 0, 1, 2, 3
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_SWIGLU, EPI_BIAS_GELU, EPI_BIAS_SILU = 0, 1, 2, 3, 4, 5
 
 
 class YB200Error(RuntimeError):

@@ -121,6 +121,24 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return __fdividef(g, 1.0f + e) * u;
 }
 
+// The reference's fused GELU and SiLU (src/quantization_pass.rs:716-796), with tanh and exp
+// through the fast hardware forms as its emitted code does.
+__device__ __forceinline__ float gelu_ref(float x) {
+    const float p = fmaf(x * x, 0.044715f, 0.79788456f);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x * p));
+    return (0.5f * x) * (1.0f + t);
+}
+__device__ __forceinline__ float silu_ref(float x) {
+    const float e = exp2f(-x * 1.4426950408889634f);
+    return __fdividef(x, 1.0f + e);
+}
+
+template <int EPI>
+__host__ __device__ constexpr bool epi_has_bias() {
+    return EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU || EPI == Y_B200_EPI_BIAS_GELU || EPI == Y_B200_EPI_BIAS_SILU;
+}
+
 template <int OUT>
 struct OutT;
 template <>
@@ -176,7 +194,7 @@ __device__ __forceinline__ void stage_bias(const GemmParams& p, float* bias_s, i
     for (int i = lane; i < count; i += 32) {
         const int col = col_base + i;
         float b = 0.0f;
-        if (col < p.n)
+        if (col < p.n && p.bias != nullptr)
             b = p.bias_kind == Y_B200_F16 ? __half2float(__ldg(static_cast<const __half*>(p.bias) + col))
                                           : __ldg(static_cast<const float*>(p.bias) + col);
         bias_s[i] = b;
@@ -205,7 +223,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * scale;
 
-        if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) {
+        if (epi_has_bias<EPI>()) {
             const float4* b4 = reinterpret_cast<const float4*>(bias_s + ch * 32);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -215,6 +233,14 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
             if (EPI == Y_B200_EPI_BIAS_RELU) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+            }
+            if (EPI == Y_B200_EPI_BIAS_GELU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = gelu_ref(v[j]);
+            }
+            if (EPI == Y_B200_EPI_BIAS_SILU) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = silu_ref(v[j]);
             }
         }
 
@@ -445,7 +471,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tile_coords(tile, p.m_tiles, p.n_tiles, p.raster_group, tm, tn);
             const uint32_t as = it & 1, aphase = (it >> 1) & 1;
             const int col_base = tn * BN + half * (BN / 2);
-            if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane);
+            if (epi_has_bias<EPI>()) stage_bias<BN>(p, bias_s, col_base, lane);
             if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
                 report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
                 dead = true;
@@ -657,7 +683,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             pair_unit(p, u, tm, tn, bn, col0);
             const uint32_t as = it & 1, aphase = (it >> 1) & 1;
             const int col_base = col0 + half * (bn / 2);
-            if (EPI == Y_B200_EPI_BIAS || EPI == Y_B200_EPI_BIAS_RELU) stage_bias<BN>(p, bias_s, col_base, lane, bn / 2);
+            if (epi_has_bias<EPI>()) stage_bias<BN>(p, bias_s, col_base, lane, bn / 2);
             if (!dead && !mbar_wait(tfull0 + 8 * as, aphase, abort_flag)) {
                 report_timeout(p.status, abort_flag, 0x30u + warp, (unsigned)it);
                 dead = true;
@@ -785,6 +811,8 @@ int launch_epi(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
         case Y_B200_EPI_NONE: return launch_out<BN, Y_B200_EPI_NONE>(ta, tb, p, out_kind, grid, st);
         case Y_B200_EPI_BIAS: return launch_out<BN, Y_B200_EPI_BIAS>(ta, tb, p, out_kind, grid, st);
         case Y_B200_EPI_BIAS_RELU: return launch_out<BN, Y_B200_EPI_BIAS_RELU>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_GELU: return launch_out<BN, Y_B200_EPI_BIAS_GELU>(ta, tb, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_SILU: return launch_out<BN, Y_B200_EPI_BIAS_SILU>(ta, tb, p, out_kind, grid, st);
         case Y_B200_EPI_SWIGLU:
             if (out_kind == Y_B200_F32) return launch_one<BN, Y_B200_EPI_SWIGLU, Y_B200_F32>(ta, tb, p, grid, st);
             if (out_kind != Y_B200_BF16)
@@ -827,6 +855,8 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
         case Y_B200_EPI_NONE: return launch_pair_out<Y_B200_EPI_NONE>(ta, tb, tbh, p, out_kind, grid, st);
         case Y_B200_EPI_BIAS: return launch_pair_out<Y_B200_EPI_BIAS>(ta, tb, tbh, p, out_kind, grid, st);
         case Y_B200_EPI_BIAS_RELU: return launch_pair_out<Y_B200_EPI_BIAS_RELU>(ta, tb, tbh, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_GELU: return launch_pair_out<Y_B200_EPI_BIAS_GELU>(ta, tb, tbh, p, out_kind, grid, st);
+        case Y_B200_EPI_BIAS_SILU: return launch_pair_out<Y_B200_EPI_BIAS_SILU>(ta, tb, tbh, p, out_kind, grid, st);
         case Y_B200_EPI_SWIGLU:
             if (out_kind == Y_B200_F32) return launch_pair_one<Y_B200_EPI_SWIGLU, Y_B200_F32>(ta, tb, tbh, p, grid, st);
             if (out_kind != Y_B200_BF16)
@@ -850,6 +880,9 @@ int validate(const y_b200_gemm_fp8_args* a) {
         if (a->bias_kind != Y_B200_F16 && a->bias_kind != Y_B200_F32)
             return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bias_kind must be F16 or F32");
     }
+    if ((a->epilogue == Y_B200_EPI_BIAS_GELU || a->epilogue == Y_B200_EPI_BIAS_SILU) && a->bias &&
+        a->bias_kind != Y_B200_F16 && a->bias_kind != Y_B200_F32)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_fp8: bias_kind must be F16 or F32");
     if (a->epilogue == Y_B200_EPI_SWIGLU && a->n % 2 != 0)
         return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_fp8: SwiGLU needs an even N (gate|up pairs), got %d", a->n);
     if (a->cta_n != 0 && a->cta_n != 64 && a->cta_n != 128 && a->cta_n != 256)
@@ -985,6 +1018,9 @@ extern "C" int y_b200_gemm_f16(const y_b200_gemm_f16_args* a, void* stream) {
         if (a->bias_kind != Y_B200_F16 && a->bias_kind != Y_B200_F32)
             return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: bias_kind must be F16 or F32");
     }
+    if ((a->epilogue == Y_B200_EPI_BIAS_GELU || a->epilogue == Y_B200_EPI_BIAS_SILU) && a->bias &&
+        a->bias_kind != Y_B200_F16 && a->bias_kind != Y_B200_F32)
+        return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16: bias_kind must be F16 or F32");
     if (a->epilogue == Y_B200_EPI_SWIGLU && a->n % 2 != 0)
         return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16: SwiGLU needs an even N (gate|up pairs), got %d", a->n);
     if (a->cta_n != 0 && a->cta_n != 64 && a->cta_n != 128 && a->cta_n != 256)

@@ -14,7 +14,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import (BF16, E4M3, EPI_BIAS, EPI_BIAS_RELU, EPI_NONE, EPI_SWIGLU, F16, F32,
+from ._lib import (BF16, E4M3, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RELU, EPI_BIAS_SILU, EPI_NONE, EPI_SWIGLU, F16, F32,
                    GemmF16Args, GemmFp8Args, LaunchInfo, check, lib)
 
 _KIND = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
