@@ -415,18 +415,40 @@ def decode_metrics(peaks, iters=200, n=None, tokens=(1, 4, 8, 32)):
         gbs = nbytes / best / 1e3
         out.append({"m": m, "us": round(best, 3), "gb_s": round(gbs, 1), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
                     "bytes": nbytes})
+    # what a launch that only reads the same bytes costs in the same kind of chain
+    # (programmatic dependent launches over the same rotating buffers)
+    floor_us = q.probe_chain_read(pool, stream_bytes, launches=iters, reps=7)
+    for e in out:
+        e["frac_of_bare_read"] = round(floor_us / e["us"], 4)
     q.device_status()
     kern.free()
     ctx.close()
     return {"workload": f"int4_decode_K{DECODE_K}_N{DECODE_N}_g128", "weight_buffers": nbuf,
-            "l2_bytes": l2, "peak_gb_s": peaks["hbm_gbs"], "peak_source": peaks["source"], "by_m": out}
+            "l2_bytes": l2, "peak_gb_s": peaks["hbm_gbs"], "peak_source": peaks["source"], "by_m": out,
+            "bare_read_same_chain": {"us": round(floor_us, 3), "gb_s": round(stream_bytes / floor_us / 1e3, 1),
+                                     "frac_hbm": round(stream_bytes / floor_us / 1e3 / peaks["hbm_gbs"], 4),
+                                     "what": "a kernel that only reads one weight buffer per launch, 148 CTAs x 512 "
+                                             "threads, 128 KB per CTA requested before griddepcontrol.wait, launched "
+                                             "as the same chain of programmatic dependent launches"}}
 
 
 def bind_near_gpu(uuid: str, index: int):
-    """Runs this process on the CPUs NVML lists as local to its GPU, so that the pinned host
-    buffers it allocates afterwards land in that socket's memory (first touch): with eight
-    ranks copying 134 MB per step each, buffers that all sit on one socket halve what the
-    host can take in. Returns the number of CPUs bound, or None if NVML has no answer."""
+    """Runs this process on the CPUs NVML lists as local to its GPU and asks the kernel to
+    prefer that GPU's NUMA node for this process's pages, so that the pinned host buffers it
+    allocates afterwards land in the memory next to the GPU's PCIe root: with eight ranks
+    copying 134 MB per step each, buffers that all sit on one socket cross the socket link.
+    Returns what was possible here: {"cpus": CPUs bound or None, "gpu_node": the GPU's NUMA
+    node or None, "mems_allowed": the nodes this process may allocate on, "prefer_node": whether
+    the memory policy call succeeded}. Every step is best-effort; none changes a GPU setting."""
+    import ctypes
+
+    info = {"cpus": None, "gpu_node": None, "mems_allowed": None, "prefer_node": False}
+    try:
+        for line in open("/proc/self/status"):
+            if line.startswith("Mems_allowed_list:"):
+                info["mems_allowed"] = line.split(":", 1)[1].strip()
+    except OSError:
+        pass
     try:
         import pynvml as nv
 
@@ -439,12 +461,30 @@ def bind_near_gpu(uuid: str, index: int):
         mask = nv.nvmlDeviceGetCpuAffinity(h, words)
         cpus = {64 * w + b for w, bits in enumerate(mask) for b in range(64) if (int(bits) >> b) & 1}
         cpus &= os.sched_getaffinity(0)
-        if not cpus:
-            return None
-        os.sched_setaffinity(0, cpus)
-        return len(cpus)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info["cpus"] = len(cpus)
+        bus = nv.nvmlDeviceGetPciInfo(h).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        for cand in (bus, bus[-12:]):  # NVML prints an 8-digit domain, sysfs a 4-digit one
+            path = f"/sys/bus/pci/devices/{cand}/numa_node"
+            if os.path.exists(path):
+                node = int(open(path).read().strip())
+                info["gpu_node"] = node if node >= 0 else None
+                break
     except Exception:
-        return None
+        pass
+    if info["gpu_node"] is not None:
+        try:
+            libc = ctypes.CDLL(None, use_errno=True)
+            MPOL_PREFERRED, SYS_set_mempolicy = 1, 238  # x86-64
+            nodemask = (ctypes.c_ulong * 16)()
+            nodemask[info["gpu_node"] // 64] = 1 << (info["gpu_node"] % 64)
+            rc = libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, nodemask, ctypes.c_ulong(16 * 64))
+            info["prefer_node"] = rc == 0
+        except Exception:
+            pass
+    return info
 
 
 def run_ours(args):
@@ -456,7 +496,7 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     _uuid = str(torch.cuda.get_device_properties(local).uuid)
-    cpus_bound = bind_near_gpu(("" if _uuid.startswith("GPU-") else "GPU-") + _uuid, local)
+    placement = bind_near_gpu(("" if _uuid.startswith("GPU-") else "GPU-") + _uuid, local)
 
     from y_b200 import colpar
     from y_b200 import quant as q
@@ -504,6 +544,14 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def gather_objects(obj):
+        """[obj of rank 0, obj of rank 1, ...] on every rank."""
+        if world == 1:
+            return [obj]
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
 
     def timed(fn, steps):
         barrier()
@@ -672,7 +720,7 @@ def run_ours(args):
     host_link = {"d2h_gb_s_all_ranks": link_gbs(c_host[0], c), "h2d_gb_s_all_ranks": link_gbs(x, x_host),
                  "what": f"10 pinned {M * N_SHARD * 2 >> 20} MiB copies per rank, all {world} rank(s) at once, one direction at a time",
                  "e2e_bytes_gb_s_all_ranks": world * sum(layer.host_bytes_per_step()) / (e2e_ms * 1e-3) / 1e9,
-                 "cpus_bound_near_gpu_rank0": cpus_bound}
+                 "placement_per_rank": gather_objects(placement)}
 
     # ---- the exchange step, reported separately: the same step followed by NCCL's all-gather,
     # and the step whose GEMM epilogue stores its shard straight into every peer's gathered

@@ -291,6 +291,16 @@ Y_B200_API int y_b200_int4_repack(const uint32_t* qweight, const void* scales_f1
 Y_B200_API int y_b200_gemm_int4_decode(const void* x_f16, const void* wstream, void* out_f16, int m, int n,
                             int k, void* stream);
 
+/* Measurement aid with no counterpart in the reference: the time per launch, in
+ * microseconds, of a kernel that only reads `bytes` (a multiple of 16) from bufs[i % nbufs]
+ * in a chain of `launches` programmatic dependent launches, each reading one word the launch
+ * before it wrote: the floor for any weight-streaming launch of that size in such a chain
+ * (a chain of short launches cannot reach the bandwidth of one long copy). One warm-up chain,
+ * then the median of `reps` (<= 64) timed chains is written to *us_per_launch.
+ * scratch_256: 256 bytes of device memory. Synchronises the stream. */
+Y_B200_API int y_b200_probe_chain_read(const void* const* bufs, int nbufs, size_t bytes, int launches, int reps,
+                                       void* scratch_256, float* us_per_launch, void* stream);
+
 /* ---- fused add + RMSNorm with the residual stream ------------------------------
  * Replaces rmsnorm_residual_<H> (src/ptx_emitter.rs:5773-6015; parameters X,
  * Residual, Weight, Out, NewResidual, all f16; one CTA of 256 threads per row):

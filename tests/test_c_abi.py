@@ -153,6 +153,13 @@ def test_argument_errors_are_codes_not_crashes():
     assert lib.y_colpar_submit_host(None, None, None, None) == _lib.ERR_INVALID
     assert lib.y_colpar_drain(None, None) == _lib.ERR_INVALID
     lib.y_colpar_destroy(None)
+    us = C.c_float(0.0)
+    assert lib.y_b200_probe_chain_read(None, 0, 16, 1, 1, None, C.byref(us), None) == _lib.ERR_INVALID
+    one = (C.c_void_p * 1)(64)
+    assert lib.y_b200_probe_chain_read(one, 1, 24, 1, 1, 64, C.byref(us), None) == _lib.ERR_SHAPE
+    assert lib.y_b200_probe_chain_read(one, 1, 32, 1, 65, 64, C.byref(us), None) == _lib.ERR_SHAPE
+    odd = (C.c_void_p * 1)(72)
+    assert lib.y_b200_probe_chain_read(odd, 1, 32, 1, 1, 64, C.byref(us), None) == _lib.ERR_ALIGN
     assert lib.y_b200_gemm_f16_decode(None, 0, None, None, 0, 1, 8, 16, None) == _lib.ERR_INVALID
     one = C.c_int(0)
     p = C.addressof(one)

@@ -125,3 +125,12 @@ def test_decode_both_paths_on_mixed_shares(q, tiles):
     q.device_status()
     ref = oracle.gemm_int4_decode(x[:8], rq, rs)
     assert_gemm_close(to_f64(host_bits(out), oracle.OUT_F16), to_f64(ref, oracle.OUT_F16))
+
+
+def test_chain_read_probe_reports_a_launch_time(q):
+    # the measurement aid bench.py holds the decode kernel against: a plain reader in a chain of
+    # programmatic dependent launches; the time must be positive and below a millisecond here
+    bufs = [torch.full((1 << 22,), i + 1, dtype=torch.uint8, device="cuda") for i in range(4)]
+    us = q.probe_chain_read(bufs, 1 << 22, launches=20, reps=3)
+    q.device_status()
+    assert 0.5 < us < 1000.0

@@ -107,6 +107,7 @@ SIGNATURES = {
     "y_b200_int4_stream_bytes": (_sz, [_sz, _sz]),
     "y_b200_int4_repack": (_i, [_vp, _vp, _sz, _sz, _vp, _vp]),
     "y_b200_gemm_int4_decode": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "y_b200_probe_chain_read": (_i, [C.POINTER(_vp), _i, _sz, _i, _i, _vp, C.POINTER(C.c_float), _vp]),
     "y_b200_rmsnorm_residual": (_i, [_vp, _vp, _vp, _sz, _sz, C.c_float, _vp, _vp, _vp]),
     "y_b200_rope": (_i, [_vp, _vp, _vp, _sz, _i, C.c_float, _vp]),
     "y_b200_paged_decode_attention_workspace_bytes": (_sz, [_i, _i, _i, _i]),

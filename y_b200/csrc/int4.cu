@@ -19,6 +19,8 @@
 
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace yb {
 namespace {
 
@@ -161,6 +163,23 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// d = a * b + c with c and d in different registers: the first MMA of a chain reads its start
+// value where it lies (no copy into the accumulator first).
+__device__ __forceinline__ void mma_16816_from(float (&d)[4], const float (&c)[4], uint32_t a0, uint32_t a1,
+                                               uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %11, %12, %13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+// d = a * b.
+__device__ __forceinline__ void mma_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                uint32_t a3, uint32_t b0, uint32_t b1) {
+    const float zero[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    mma_16816_from(d, zero, a0, a1, a2, a3, b0, b1);
 }
 
 // Dequantisation costs one logic instruction per f16 pair. With u = q + 8 the
@@ -319,14 +338,17 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
 #pragma unroll
             for (int t = 0; t < kRoundTiles; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
             auto group_offsets = [&]() {
-                float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                // four chains of two MMAs, not one of eight: every warp of the CTA runs this pass
+                // at the same moment (right after the activations arrive), so nothing hides a
+                // long chain's latency
+                float o[4][4];
 #pragma unroll
                 for (int pp = 0; pp < 4; ++pp) {
-                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[pp].x, xf[pp].y);
-                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[pp].z, xf[pp].w);
+                    mma_16816_first(o[pp], kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[pp].x, xf[pp].y);
+                    mma_16816(o[pp], kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[pp].z, xf[pp].w);
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) neg_off[i] = -o[i];
+                for (int i = 0; i < 4; ++i) neg_off[i] = -((o[0][i] + o[1][i]) + (o[2][i] + o[3][i]));
             };
             // One 16 x 128 block against the group's activations, added into `a`. `done_reading`
             // runs as soon as the block's bytes are in registers (it frees the ring slot).
@@ -339,7 +361,9 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
                 done_reading();
                 const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
                 const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
-                float tmp[4] = {neg_off[0], neg_off[1], neg_off[2], neg_off[3]};
+                // two independent chains of four MMAs (even and odd 16-wide K slices); the first
+                // starts from the negated offsets, the second from zero
+                float t0[4], t1[4];
 #pragma unroll
                 for (int pp = 0; pp < 4; ++pp) {
                     const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
@@ -347,19 +371,26 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
                     const uint32_t a2 = and_or(wA[pp], dq.mask_hi, dq.exp_hi), a3 = and_or(wB[pp], dq.mask_hi, dq.exp_hi);
                     const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
                     const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
-                    mma_16816(tmp, a0, a1, a2, a3, xf[pp].x, xf[pp].y);
-                    mma_16816(tmp, e0, e1, e2, e3, xf[pp].z, xf[pp].w);
+                    if (pp == 0) {
+                        mma_16816_from(t0, neg_off, a0, a1, a2, a3, xf[pp].x, xf[pp].y);
+                        mma_16816_first(t1, e0, e1, e2, e3, xf[pp].z, xf[pp].w);
+                    } else {
+                        mma_16816(t0, a0, a1, a2, a3, xf[pp].x, xf[pp].y);
+                        mma_16816(t1, e0, e1, e2, e3, xf[pp].z, xf[pp].w);
+                    }
                 }
-                a[0] = fmaf(s_lo, tmp[0], a[0]);
-                a[1] = fmaf(s_lo, tmp[1], a[1]);
-                a[2] = fmaf(s_hi, tmp[2], a[2]);
-                a[3] = fmaf(s_hi, tmp[3], a[3]);
+                a[0] = fmaf(s_lo, t1[0], fmaf(s_lo, t0[0], a[0]));
+                a[1] = fmaf(s_lo, t1[1], fmaf(s_lo, t0[1], a[1]));
+                a[2] = fmaf(s_hi, t1[2], fmaf(s_hi, t0[2], a[2]));
+                a[3] = fmaf(s_hi, t1[3], fmaf(s_hi, t0[3], a[3]));
             };
             float* const mine = red + (size_t)warp * (kRoundTiles * 128);
             auto straight_line = [&](auto rt_const) {
                 constexpr int RT = decltype(rt_const)::value;
                 static_assert(RT >= kDepth, "the second group's activations must land before its first block");
-                const uint8_t* const s0 = wmine + (size_t)t_begin * tile_stride + lane * 16;
+                // K is known on this path, so every source of the warp is s0 plus a constant
+                constexpr size_t kTileStride = (size_t)2 * kWarps * kBlkBytes;
+                const uint8_t* const s0 = wmine + (size_t)t_begin * kTileStride + lane * 16;
                 const uint8_t* const s1 = s0 + (size_t)kWarps * kBlkBytes;
                 const uint32_t d0 = stage0 + lane * 16;
                 // First group's activations straight into registers.
@@ -394,13 +425,13 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
                                    __syncwarp();
                                    constexpr int nb = b + kDepth;
                                    if constexpr (nb < 2 * RT) {
-                                       const uint8_t* src = (nb < RT ? s0 : s1) + (size_t)(nb % RT) * tile_stride;
+                                       const uint8_t* src = (nb < RT ? s0 : s1) + (size_t)(nb % RT) * kTileStride;
                                        const uint32_t dst = d0 + (nb % kDepth) * kBlkBytes;
                                        cp_async_16(dst, src);
                                        cp_async_16(dst + 512, src + 512);
                                        if (lane < 2) cp_async_16(dst + 1024, src + 1024);
                                    }
-                                   cp_async_commit();
+                                   cp_async_commit();  // one group per block, empty or not
                                },
                                acc[b % RT]);
                 });
@@ -415,14 +446,31 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
             for (int t = 0; t < kRoundTiles; ++t)
                 *reinterpret_cast<float4*>(mine + t * 128 + lane * 4) = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
             __syncthreads();
-            for (int e = threadIdx.x; e < share * 128; e += kWarps * 32) {
-                float v = red[e];
+            // One pass: thread e4 sums the 16 warps' copies of one lane's four accumulators of
+            // one tile (sixteen 16-byte reads issued together, then four chains of adds in
+            // warp order). With one float per thread the 640 sums of a five-tile share took
+            // two dependent rounds on the first four warps, 0.5 us at the end of every launch.
+            if ((int)threadIdx.x < share * 32) {
+                const int e4 = threadIdx.x;
+                float4 p[kWarps];
 #pragma unroll
-                for (int w = 1; w < kWarps; ++w) v += red[w * (kRoundTiles * 128) + e];
-                const int t = e / 128, l = (e % 128) / 4, i = e % 4;
-                const int col = (t_begin + t) * 16 + (l >> 2) + 8 * (i >> 1);
-                const int tok = 2 * (l & 3) + (i & 1);
-                if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
+                for (int w = 0; w < kWarps; ++w)
+                    p[w] = *reinterpret_cast<const float4*>(red + w * (kRoundTiles * 128) + e4 * 4);
+                float v[4] = {p[0].x, p[0].y, p[0].z, p[0].w};
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) {
+                    v[0] += p[w].x;
+                    v[1] += p[w].y;
+                    v[2] += p[w].z;
+                    v[3] += p[w].w;
+                }
+                const int t = e4 >> 5, l = e4 & 31;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int col = (t_begin + t) * 16 + (l >> 2) + 8 * (i >> 1);
+                    const int tok = 2 * (l & 3) + (i & 1);
+                    if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v[i]);
+                }
             }
             return;
         }
@@ -457,14 +505,14 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
             float neg_off[NT][4];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                float o[4][4];  // the same four chains and the same sum as the straight-line path
 #pragma unroll
                 for (int pp = 0; pp < 4; ++pp) {
-                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].x, xf[j][pp].y);
-                    mma_16816(o, kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].z, xf[j][pp].w);
+                    mma_16816_first(o[pp], kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].x, xf[j][pp].y);
+                    mma_16816(o[pp], kOffsetLo, kOffsetLo, kOffsetHi, kOffsetHi, xf[j][pp].z, xf[j][pp].w);
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) neg_off[j][i] = -o[i];
+                for (int i = 0; i < 4; ++i) neg_off[j][i] = -((o[0][i] + o[1][i]) + (o[2][i] + o[3][i]));
             }
             auto tile_step = [&](const int t) {
                 const uint8_t* blk = acquire();
@@ -476,30 +524,48 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
                 release();
                 const uint32_t wA[4] = {u0.x, u0.z, u1.x, u1.z};  // column gq
                 const uint32_t wB[4] = {u0.y, u0.w, u1.y, u1.w};  // column gq + 8
-                float tmp[NT][4];
-#pragma unroll
-                for (int j = 0; j < NT; ++j)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) tmp[j][i] = neg_off[j][i];
+                // The two chains of the straight-line path, one after the other (a thread of this path
+                // has no registers for both at once): the same operations in the same order per
+                // output, so a token's result does not depend on which path computed it.
+                float ch[NT][4];
 #pragma unroll
                 for (int pp = 0; pp < 4; ++pp) {
-                    const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
                     const uint32_t a0 = and_or(wA[pp], dq.mask_lo, dq.exp_lo), a1 = and_or(wB[pp], dq.mask_lo, dq.exp_lo);
                     const uint32_t a2 = and_or(wA[pp], dq.mask_hi, dq.exp_hi), a3 = and_or(wB[pp], dq.mask_hi, dq.exp_hi);
-                    const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
-                    const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
-                        mma_16816(tmp[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
-                        mma_16816(tmp[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
+                        if (pp == 0)
+                            mma_16816_from(ch[j], neg_off[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
+                        else
+                            mma_16816(ch[j], a0, a1, a2, a3, xf[j][pp].x, xf[j][pp].y);
                     }
                 }
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    acc[t][j][0] = fmaf(s_lo, tmp[j][0], acc[t][j][0]);
-                    acc[t][j][1] = fmaf(s_lo, tmp[j][1], acc[t][j][1]);
-                    acc[t][j][2] = fmaf(s_hi, tmp[j][2], acc[t][j][2]);
-                    acc[t][j][3] = fmaf(s_hi, tmp[j][3], acc[t][j][3]);
+                    acc[t][j][0] = fmaf(s_lo, ch[j][0], acc[t][j][0]);
+                    acc[t][j][1] = fmaf(s_lo, ch[j][1], acc[t][j][1]);
+                    acc[t][j][2] = fmaf(s_hi, ch[j][2], acc[t][j][2]);
+                    acc[t][j][3] = fmaf(s_hi, ch[j][3], acc[t][j][3]);
+                }
+#pragma unroll
+                for (int pp = 0; pp < 4; ++pp) {
+                    const uint32_t hA = wA[pp] >> 8, hB = wB[pp] >> 8;
+                    const uint32_t e0 = and_or(hA, dq.mask_lo, dq.exp_lo), e1 = and_or(hB, dq.mask_lo, dq.exp_lo);
+                    const uint32_t e2 = and_or(hA, dq.mask_hi, dq.exp_hi), e3 = and_or(hB, dq.mask_hi, dq.exp_hi);
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        if (pp == 0)
+                            mma_16816_first(ch[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
+                        else
+                            mma_16816(ch[j], e0, e1, e2, e3, xf[j][pp].z, xf[j][pp].w);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    acc[t][j][0] = fmaf(s_lo, ch[j][0], acc[t][j][0]);
+                    acc[t][j][1] = fmaf(s_lo, ch[j][1], acc[t][j][1]);
+                    acc[t][j][2] = fmaf(s_hi, ch[j][2], acc[t][j][2]);
+                    acc[t][j][3] = fmaf(s_hi, ch[j][3], acc[t][j][3]);
                 }
             };
             if (rt == kRoundTiles) {
@@ -520,15 +586,29 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
                 *reinterpret_cast<float4*>(mine + (t * NT + j) * 128 + lane * 4) =
                     make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
         __syncthreads();
-        const int nout = rt * NT * 128;
-        for (int e = threadIdx.x; e < nout; e += kWarps * 32) {
-            float v = red[e];
+        // thread e4 sums the warps' copies of one lane's four accumulators of one (tile, token
+        // tile): all reads issued together, then four chains of adds in warp order
+        const int nout4 = rt * NT * 32;
+        for (int e4 = threadIdx.x; e4 < nout4; e4 += kWarps * 32) {
+            float4 p[kWarps];
 #pragma unroll
-            for (int w = 1; w < kWarps; ++w) v += red[w * (kRoundTiles * NT * 128) + e];
-            const int t = e / (NT * 128), j = (e / 128) % NT, l = (e % 128) / 4, i = e % 4;
-            const int col = (r0 + t) * 16 + (l >> 2) + 8 * (i >> 1);
-            const int tok = 8 * j + 2 * (l & 3) + (i & 1);
-            if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v);
+            for (int w = 0; w < kWarps; ++w)
+                p[w] = *reinterpret_cast<const float4*>(red + w * (kRoundTiles * NT * 128) + e4 * 4);
+            float v[4] = {p[0].x, p[0].y, p[0].z, p[0].w};
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) {
+                v[0] += p[w].x;
+                v[1] += p[w].y;
+                v[2] += p[w].z;
+                v[3] += p[w].w;
+            }
+            const int t = e4 / (NT * 32), j = (e4 / 32) % NT, l = e4 & 31;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int col = (r0 + t) * 16 + (l >> 2) + 8 * (i >> 1);
+                const int tok = 8 * j + 2 * (l & 3) + (i & 1);
+                if (tok < M) out[(size_t)tok * N + col] = __float2half_rn(v[i]);
+            }
         }
         __syncthreads();
     }
@@ -556,6 +636,44 @@ int launch_decode(const void* x, const void* wstream, void* out, int m, int n, i
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// A measurement aid, not part of the path: what a launch that does nothing but read `n16`
+// 16-byte units costs in the same kind of dependent chain as the decode GEMM (programmatic
+// dependent launch, one CTA of 512 threads per multiprocessor, the first 128 KB per CTA
+// requested before griddepcontrol.wait, one word that the launch before wrote read after
+// it). The decode kernel's launch time is held against this as well as against the copy
+// bandwidth: a chain of 23 MB launches cannot run at the bandwidth of a long copy.
+constexpr int kProbeUnroll = 16;
+__global__ void __launch_bounds__(512, 1)
+    chain_read_probe_kernel(const uint4* __restrict__ w, size_t n16, uint32_t* __restrict__ link) {
+    pdl_launch_dependents();
+    const size_t per = (n16 + gridDim.x - 1) / gridDim.x;
+    const size_t b0 = (size_t)blockIdx.x * per, b1 = b0 + per < n16 ? b0 + per : n16;
+    uint32_t acc = 0;
+    size_t i = b0 + threadIdx.x;
+    uint4 v[kProbeUnroll];
+#pragma unroll
+    for (int u = 0; u < kProbeUnroll; ++u) {
+        const size_t j = i + (size_t)u * 512;
+        v[u] = j < b1 ? __ldcs(w + j) : make_uint4(0, 0, 0, 0);
+    }
+    pdl_wait();
+    const uint32_t dep = link[threadIdx.x & 31];  // written by the launch before this one
+    for (;;) {
+#pragma unroll
+        for (int u = 0; u < kProbeUnroll; ++u) acc ^= v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+        i += (size_t)kProbeUnroll * 512;
+        if (i >= b1) break;
+#pragma unroll
+        for (int u = 0; u < kProbeUnroll; ++u) {
+            const size_t j = i + (size_t)u * 512;
+            v[u] = j < b1 ? __ldcs(w + j) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    // every CTA's sum feeds the word the next launch reads, so no load can be dropped
+    if (threadIdx.x == 0 && blockIdx.x < 32) link[blockIdx.x] = (acc ^ dep) | 1u;
+    else if (acc == 0x9e3779b9u) link[32 + (threadIdx.x & 31)] = acc;
+}
 
 }  // namespace
 
@@ -604,6 +722,43 @@ extern "C" int y_b200_int4_repack(const uint32_t* qweight, const void* scales_f1
         qweight, static_cast<const uint16_t*>(scales_f16), k / 128, n, words,
         static_cast<uint32_t*>(wstream));
     return check_cuda(cudaGetLastError(), "int4_repack_kernel launch");
+}
+
+extern "C" int y_b200_probe_chain_read(const void* const* bufs, int nbufs, size_t bytes, int launches,
+                                       int reps, void* scratch_256, float* us_per_launch, void* stream) {
+    if (!bufs || nbufs < 1 || !scratch_256 || !us_per_launch)
+        return fail(Y_B200_ERR_INVALID, "y_b200_probe_chain_read: null pointer or no buffers");
+    if (bytes < 16 || bytes % 16 != 0 || launches < 1 || reps < 1 || reps > 64)
+        return fail(Y_B200_ERR_SHAPE, "y_b200_probe_chain_read: bytes %% 16 == 0, launches >= 1, 1 <= reps <= 64");
+    for (int i = 0; i < nbufs; ++i)
+        if (!bufs[i] || !aligned16(bufs[i])) return fail(Y_B200_ERR_ALIGN, "y_b200_probe_chain_read: buffer %d null or not 16-byte aligned", i);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint32_t* link = static_cast<uint32_t*>(scratch_256);
+    YB_CUDA(cudaMemsetAsync(link, 0, 256, st));
+    cudaEvent_t e0, e1;
+    YB_CUDA(cudaEventCreate(&e0));
+    YB_CUDA(cudaEventCreate(&e1));
+    float sorted[64];
+    cudaError_t err = cudaSuccess;
+    for (int r = -1; r < reps && err == cudaSuccess; ++r) {  // r = -1: warm-up
+        if (r >= 0) err = cudaEventRecord(e0, st);
+        for (int i = 0; i < launches && err == cudaSuccess; ++i)
+            err = launch_pdl(chain_read_probe_kernel, (unsigned)sm_count(), 512u, 0, st,
+                             static_cast<const uint4*>(bufs[i % nbufs]), bytes / 16, link);
+        if (r >= 0 && err == cudaSuccess) {
+            err = cudaEventRecord(e1, st);
+            if (err == cudaSuccess) err = cudaEventSynchronize(e1);
+            float ms = 0.0f;
+            if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
+            sorted[r] = ms * 1000.0f / (float)launches;
+        }
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (err != cudaSuccess) return check_cuda(err, "y_b200_probe_chain_read");
+    std::sort(sorted, sorted + reps);
+    *us_per_launch = sorted[reps / 2];
+    return Y_B200_OK;
 }
 
 extern "C" int y_b200_gemm_int4_decode(const void* x_f16, const void* wstream, void* out_f16, int m,

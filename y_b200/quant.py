@@ -403,6 +403,22 @@ def gemm_int4_decode(x: torch.Tensor, wstream: torch.Tensor, n: int,
     return o
 
 
+def probe_chain_read(buffers, nbytes: int, launches: int = 200, reps: int = 7) -> float:
+    """Microseconds per launch of a kernel that only reads `nbytes` from each of `buffers` in turn,
+    in a chain of programmatic dependent launches (see y_b200_probe_chain_read): the floor a
+    weight-streaming launch of that size is held against."""
+    import ctypes as C
+
+    for b in buffers:
+        _dev(b, "buffer")
+    ptrs = (C.c_void_p * len(buffers))(*[b.data_ptr() for b in buffers])
+    scratch = torch.zeros(64, dtype=torch.int32, device=buffers[0].device)
+    us = C.c_float(0.0)
+    check(lib.y_b200_probe_chain_read(ptrs, len(buffers), nbytes, launches, reps, scratch.data_ptr(),
+                                      C.byref(us), _stream()))
+    return float(us.value)
+
+
 def int4_weight_only_gemm(x: torch.Tensor, w_q4: torch.Tensor, scales: torch.Tensor, zeros=None):
     """The reference's documented W4A16 operator. `w_q4` is either the canonical
     [K/8, N] int32 packing (repacked on the fly) or a streaming buffer from
