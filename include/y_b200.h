@@ -181,8 +181,9 @@ Y_B200_API int y_b200_gemm_f16_swiglu(const void* x_f16, const void* wgate_f16, 
 /* Small-M F16 GEMM with the weights streamed once from HBM, row-major [K, N] as the
  * reference's gemm_f16_decode_m<M> entries take them (tests/gemm_f16_decode_m1.ptx:6-9):
  *   out [M, N] (F32 or F16) = x [M, K] f16 (row stride ldx elements) @ w [K, N] f16.
- * 1 <= M <= 32, K % 16 == 0, N % 8 == 0, ldx % 2 == 0; no workspace, no atomics (K is split
- * across the warps of a CTA and reduced in a fixed order). */
+ * 1 <= M <= 32, K % 16 == 0, N % 8 == 0, ldx % 8 == 0, x and w 16-byte aligned; no workspace,
+ * no atomics (K is split across the warps of a CTA and the CTAs of a cluster and reduced in a
+ * fixed order). */
 Y_B200_API int y_b200_gemm_f16_decode(const void* x_f16, int ldx, const void* w_f16, void* out, int out_kind,
                                       int m, int n, int k, void* stream);
 /* The reference's split-K pair for decode shapes (tests/y_tensor_core_gemm.cu:4732-4738,

@@ -71,25 +71,40 @@ int launch_transpose(const void* src, int rows, int cols, void* dst, int dst_mul
 // A CTA of 8 warps owns 64 output columns, i.e. a 128-byte run of every weight row it reads
 // (64-byte runs reached a quarter of the HBM copy rate: too little per DRAM page). K is cut two
 // ways. Across CTAs: a thread-block cluster of S CTAs shares the 64 columns, CTA r taking the
-// r-th contiguous K slab, so that small N still fills the GPU (N = 4096: 64 column blocks x 4);
-// the slabs' partial tiles meet in the first CTA's shared memory over distributed shared memory
-// and are added there in rank order. Inside a CTA: the slab is cut into steps of 16 rows, warp
-// v takes the v-th contiguous eighth of them and streams it through a private ring of 2 KB
-// slots filled by per-thread 16-byte cp.async copies (no producer warp, no barrier another
-// agent has to complete). A step is one mma.sync.m16n8k16 per 8 columns and 16 tokens: the
-// tokens are the 16-row operand, the weights the 8-wide one, read from the slot with
-// ldmatrix.trans (w is row-major along N). The token fragments come straight from global
-// memory, four steps ahead of their use: consecutive steps of a warp share 128-byte lines of x
-// (with steps dealt round-robin to the warps every fragment load went to L2 and the kernel
-// spent its time on the long scoreboard: 7 stall cycles per issue, 12 % L1 hits). The 16-byte
-// units of a slot row are XOR-swizzled with the row index, so the eight row addresses of an
-// ldmatrix phase hit eight different bank groups. All sums are added in a fixed order (warp
-// order, then cluster rank order): no atomics, overwrite semantics, run-to-run identical.
+// r-th contiguous K slab, so that small N still fills the GPU (N = 4096: 64 column blocks x 4).
+// Inside a CTA: the slab is cut into steps of 32 rows, warp v takes the v-th contiguous eighth
+// of them and streams it through a private ring of 4 KB slots filled by per-thread 16-byte
+// cp.async copies (no producer warp, no barrier another agent has to complete). A step is two
+// mma.sync.m16n8k16 per 16 columns and 8 tokens: the weights are the 16-row operand, read from
+// the slot with ldmatrix.trans (w is row-major along N), the tokens the 8-wide one, so up to 8
+// tokens cost one MMA per 256 weights. (With the tokens as the 16-row operand it was one per
+// 128 weights whatever the token count, and at K = N = 4096 the steps of a CTA took as long as
+// the tensor pipe needs for them: mma.sync issues one m16n8k16 every 16 cycles per scheduler.)
+//
+// The 32 rows of a step are dealt to the two MMAs so that a thread's token fragments are
+// contiguous in memory: thread (g, c) of a warp holds token g (and g + 8, ... for more than 8
+// tokens) at k = 8c .. 8c + 7 of the step (one 16-byte load per token and step), the first MMA
+// takes k = 8c .. 8c + 3 as its slots (2c, 2c + 1, 2c + 8, 2c + 9) and the second
+// k = 8c + 4 .. 8c + 7. ldmatrix takes a row address per lane, so reading the weight rows in
+// that order costs nothing. (With the natural order a thread's fragments are 4-byte pieces;
+// those loads, four per 16 rows, held the kernel at 0.58 of the copy rate at K = N = 4096 and
+// 0.69 at N = 11008.) The 16-byte units of a slot row are XOR-swizzled with the row index,
+// so the eight row addresses of an ldmatrix phase hit eight different bank groups.
+//
+// The partial tiles of a cluster meet without anyone waiting twice: after its cross-warp sum
+// every CTA stores each 1/S of its tile into the shared memory of the CTA that owns that part
+// (distributed shared memory, a region the rings never touch), one cluster barrier follows, and
+// every CTA adds the S parts it received in rank order and writes its share of the output.
+// All sums are added in a fixed order (warp order, then cluster rank order): no atomics,
+// overwrite semantics, run-to-run identical.
 constexpr int kDecWarps = 8;
 constexpr int kDecCols = 64;
-constexpr int kDecStages = 5;
-constexpr int kDecSlotBytes = 16 * kDecCols * 2;  // 2 KB
-constexpr int kDecSmemBytes = kDecWarps * kDecStages * kDecSlotBytes;  // 80 KB: two CTAs per SM
+constexpr int kDecStepRows = 32;
+constexpr int kDecStages = 3;
+constexpr int kDecSlotBytes = kDecStepRows * kDecCols * 2;  // 4 KB
+constexpr int kDecRingBytes = kDecWarps * kDecStages * kDecSlotBytes;  // 96 KB
+constexpr int kDecRecvBytes = 2 * 8 * 32 * 16;  // one reduced tile of up to 32 tokens x 64 columns, f32: 8 KB
+constexpr int kDecSmemBytes = kDecRingBytes + kDecRecvBytes;  // 104 KB: two CTAs per SM
 
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t dst_smem, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;
@@ -116,42 +131,50 @@ __device__ __forceinline__ uint32_t cluster_nctarank() {
     asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
     return r;
 }
-__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
-    return v;
+__device__ __forceinline__ void st_shared_cluster_f32x4(uint32_t cluster_addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// XOR key of a slot row's 16-byte units. The eight rows one ldmatrix phase reads are
+// 8c' + j + const (c' = 0..3, j = 0, 1): their keys are the eight values 2c' + j.
+__device__ __forceinline__ int swizzle_key(int row) { return ((row >> 3) << 1) | (row & 1); }
 
-template <int MT, typename OutT>
-__global__ void __launch_bounds__(kDecWarps * 32)
+template <int NT, typename OutT>
+__global__ void __launch_bounds__(kDecWarps * 32, 2)
     f16_decode_kernel(const __half* __restrict__ x, int ldx, const __half* __restrict__ w, OutT* __restrict__ out,
                       int M, int N, int K) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank(), nranks = cluster_nctarank();
+    // First phase of the cluster barrier: "this CTA runs" (nobody waits for it before the tail).
+    if (nranks > 1) cluster_arrive_relaxed();
     const int n0 = (int)(blockIdx.x / nranks) * kDecCols;
-    // This CTA's K slab, in steps of 16 rows (the host makes K / 16 a multiple of the cluster size).
-    const int slab_steps = K / 16 / (int)nranks;
+    // This CTA's K slab, in steps of 32 rows (the host makes the step count a multiple of the
+    // cluster size; the last step of the matrix may hold 16 rows of zeros).
+    const int slab_steps = (K + kDecStepRows - 1) / kDecStepRows / (int)nranks;
     const int per_warp = (slab_steps + kDecWarps - 1) / kDecWarps;
     const int my_steps = max(0, min(per_warp, slab_steps - warp * per_warp));
     const int step0 = (int)rank * slab_steps + warp * per_warp;  // this warp's first step
     const uint32_t ring = smem_u32(smem) + warp * (kDecStages * kDecSlotBytes);
     pdl_launch_dependents();
 
-    // This lane's four 16-byte units of a slot: rows lane / 8 + 4 j, unit lane % 8.
+    // This lane's eight 16-byte units of a slot: rows lane / 8 + 4 j, unit lane % 8.
     const int crow = lane >> 3, cunit = lane & 7;
     const bool col_ok = n0 + cunit * 8 < N;  // N % 8 == 0: a unit is wholly inside or outside
-    // columns beyond N are zero-filled without a read; their source address stays inside the matrix
-    const __half* wsrc = w + (size_t)(16 * step0 + crow) * N + (col_ok ? n0 + cunit * 8 : 0);
-    const size_t step_stride = (size_t)16 * N;  // this warp's next step
+    const int krow0 = kDecStepRows * step0 + crow;
+    // columns beyond N and rows beyond K are zero-filled without a read from a valid address
+    const __half* wsrc = w + (col_ok ? n0 + cunit * 8 : 0);
     auto request = [&](int i) {  // step i of this warp into slot i % kDecStages; always commits a group
         if (i < my_steps) {
             const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
-            const __half* s = wsrc + (size_t)i * step_stride;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int row = crow + 4 * j;
-                cp_async_16_zfill(slot + row * 128 + ((cunit ^ (row & 7)) << 4), s + (size_t)(4 * j) * N, col_ok);
+            for (int j = 0; j < 8; ++j) {
+                const int row = crow + 4 * j, k = krow0 + kDecStepRows * i + 4 * j;
+                const bool ok = col_ok && k < K;
+                cp_async_16_zfill(slot + row * 128 + ((cunit ^ swizzle_key(row)) << 4), wsrc + (size_t)(ok ? k : 0) * N, ok);
             }
         }
         cp_async_commit();
@@ -162,40 +185,36 @@ __global__ void __launch_bounds__(kDecWarps * 32)
     pdl_wait();  // x is the previous kernel's output
 
     const int g = lane >> 2, c = lane & 3;
-    // ldmatrix row address of this lane inside a slot; call t reads the 16-byte units 2t and 2t + 1
-    const int mrow = (lane & 7) + 8 * ((lane >> 3) & 1), munit = lane >> 4;
+    // ldmatrix row of this lane: matrices 0 and 2 of an x4 call are the MMA's K slots 0..7,
+    // matrices 1 and 3 its slots 8..15; slot 2c' + j (+ 8) of MMA e is row 8c' + 4e + j (+ 2)
+    // of the step. Call t reads the 16-byte units 2t and 2t + 1.
+    const int khalf = (lane >> 3) & 1, munit = lane >> 4;
+    const int mrow0 = 8 * ((lane & 7) >> 1) + 2 * khalf + (lane & 1);  // MMA 0; MMA 1 is 4 rows further
 
-    float acc[MT][8][4];
+    // acc[t][j]: weight columns 16t + g (+ 8) of the CTA's 64, tokens 8j + 2c (+ 1)
+    float acc[4][NT][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int t = 0; t < 4; ++t)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int j = 0; j < NT; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.0f;
+            for (int i = 0; i < 4; ++i) acc[t][j][i] = 0.0f;
 
-    // Token fragments of one step: rows g and g + 8 of each 16-token tile, k = k0 + 2c (+1), k0 + 8 + 2c (+1).
-    auto load_a = [&](int i, uint32_t (&a)[MT][4]) {
-        const int k0 = 16 * (step0 + i) + 2 * c;
+    // Token fragments of one step: token 8j + g, k = 32 (step0 + i) + 8c + (0..7).
+    auto load_a = [&](int i, uint4 (&a)[NT]) {
+        const int k0 = kDecStepRows * (step0 + i) + 8 * c;
+        const bool live = i < my_steps && k0 < K;  // K % 8 == 0
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            const int ra = 16 * mt + g, rb = ra + 8;
-            const bool live = i < my_steps;
-            a[mt][0] = a[mt][2] = a[mt][1] = a[mt][3] = 0u;
-            if (live && ra < M) {
-                a[mt][0] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)ra * ldx + k0));
-                a[mt][2] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)ra * ldx + k0 + 8));
-            }
-            if (live && rb < M) {
-                a[mt][1] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)rb * ldx + k0));
-                a[mt][3] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)rb * ldx + k0 + 8));
-            }
+        for (int j = 0; j < NT; ++j) {
+            const int tok = 8 * j + g;
+            a[j] = make_uint4(0u, 0u, 0u, 0u);
+            if (live && tok < M) a[j] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)tok * ldx + k0));
         }
     };
-    // Token fragments are loaded this many steps before their MMAs. With two 16-token tiles the
-    // deeper prefetch costs the registers that let two CTAs share an SM (measured: 22 us against
-    // 14.6 us at 32 tokens, K = N = 4096), so it stays at one step there.
-    constexpr int kAhead = MT == 1 ? 4 : 1;
-    uint32_t a[kAhead][MT][4];
+    // Token fragments are loaded this many steps before their MMAs. With four token tiles a
+    // deeper prefetch costs the registers that let two CTAs share an SM.
+    constexpr int kAhead = NT == 1 ? 4 : 2;
+    uint4 a[kAhead][NT];
 #pragma unroll
     for (int j = 0; j < kAhead; ++j) load_a(j, a[j]);
 #pragma unroll 1
@@ -207,19 +226,45 @@ __global__ void __launch_bounds__(kDecWarps * 32)
                 cp_async_wait<kDecStages - 1>();  // all but the newest kDecStages - 1 groups: step i has landed
                 __syncwarp();
                 const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
-                uint32_t b[4][4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-                    ldmatrix_x4_trans(slot + mrow * 128 + (((2 * t + munit) ^ (mrow & 7)) << 4), b[t]);
-                __syncwarp();  // every lane has read the slot
-                request(i + kDecStages);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
+                // The weights are the 16-row operand (16 columns x 16 K slots per MMA, so up to 8
+                // tokens cost one MMA per 256 weights), the tokens the 8-wide one. ldmatrix call t
+                // returns (K slots 0..7, columns 16t..16t+7), (slots 8..15, same columns), and
+                // the same two for columns 16t+8..16t+15: fragment registers 0, 2, 1, 3. With
+                // more than 16 tokens the two MMAs' weight fragments are read one after the other
+                // (16 registers instead of 32, which a token prefetch two steps deep needs:
+                // 11.0 against 11.3 us at 32 tokens, K = N = 4096; at 16 tokens it costs 4 %).
+                auto mmas = [&](int e, const uint32_t (&b)[4][4]) {
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
-                        mma_16816(acc[mt][2 * t], a[j][mt], b[t][0], b[t][1]);
-                        mma_16816(acc[mt][2 * t + 1], a[j][mt], b[t][2], b[t][3]);
+                        const uint32_t wf[4] = {b[t][0], b[t][2], b[t][1], b[t][3]};
+#pragma unroll
+                        for (int jt = 0; jt < NT; ++jt)
+                            mma_16816(acc[t][jt], wf, e == 0 ? a[j][jt].x : a[j][jt].z, e == 0 ? a[j][jt].y : a[j][jt].w);
                     }
+                };
+                auto read_weights = [&](int e, uint32_t (&b)[4][4]) {
+                    const int r = mrow0 + 4 * e;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t)
+                        ldmatrix_x4_trans(slot + r * 128 + (((2 * t + munit) ^ swizzle_key(r)) << 4), b[t]);
+                };
+                if constexpr (NT <= 2) {
+                    uint32_t b0[4][4], b1[4][4];
+                    read_weights(0, b0);
+                    read_weights(1, b1);
+                    __syncwarp();  // every lane has read the slot
+                    request(i + kDecStages);
+                    mmas(0, b0);
+                    mmas(1, b1);
+                } else {
+                    uint32_t b[4][4];
+                    read_weights(0, b);
+                    mmas(0, b);
+                    read_weights(1, b);
+                    __syncwarp();  // every lane has read the slot
+                    request(i + kDecStages);
+                    mmas(1, b);
+                }
                 load_a(i + kAhead, a[j]);
             }
         }
@@ -227,56 +272,93 @@ __global__ void __launch_bounds__(kDecWarps * 32)
     cp_async_wait<0>();
     __syncthreads();  // the rings are free: they become the reduction area
     float* red = reinterpret_cast<float*>(smem);
-    constexpr int kPerWarp = MT * 8 * 32 * 4;  // floats a warp contributes (at most 8 KB)
-    float* tile = red + kDecWarps * kPerWarp;   // this CTA's reduced tile, read by the cluster's first CTA
+    constexpr int kPerWarp = 4 * NT * 32 * 4;  // floats a warp contributes (at most 8 KB)
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int t = 0; t < 4; ++t)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-            *reinterpret_cast<float4*>(red + warp * kPerWarp + ((mt * 8 + nt) * 32 + lane) * 4) =
-                make_float4(acc[mt][nt][0], acc[mt][nt][1], acc[mt][nt][2], acc[mt][nt][3]);
+        for (int j = 0; j < NT; ++j)
+            *reinterpret_cast<float4*>(red + warp * kPerWarp + ((t * NT + j) * 32 + lane) * 4) =
+                make_float4(acc[t][j][0], acc[t][j][1], acc[t][j][2], acc[t][j][3]);
     __syncthreads();
-    for (int e = threadIdx.x; e < kPerWarp; e += kDecWarps * 32) {
-        float v = red[e];
+    // Cross-warp sum in warp order: thread e4 adds the warps' copies of one lane's four
+    // accumulators of one (token tile, column tile), all reads issued together, and hands the
+    // result to the CTA that owns that part of the tile (part r of rank r's region there).
+    constexpr int kPerWarp4 = kPerWarp / 4;
+    const int chunk = kPerWarp4 / (int)nranks;  // nranks is 1, 2, 4 or 8
+    const uint32_t recv = smem_u32(smem) + kDecRingBytes;  // [nranks][chunk] float4, written by the cluster
+    if (nranks > 1) cluster_wait_acquire();  // every CTA of the cluster runs: its shared memory may be written
+    for (int e4 = threadIdx.x; e4 < kPerWarp4; e4 += kDecWarps * 32) {
+        float4 p[kDecWarps];
 #pragma unroll
-        for (int wv = 1; wv < kDecWarps; ++wv) v += red[wv * kPerWarp + e];
-        tile[e] = v;
+        for (int wv = 0; wv < kDecWarps; ++wv) p[wv] = *reinterpret_cast<const float4*>(red + wv * kPerWarp + e4 * 4);
+        float4 v = p[0];
+#pragma unroll
+        for (int wv = 1; wv < kDecWarps; ++wv) {
+            v.x += p[wv].x;
+            v.y += p[wv].y;
+            v.z += p[wv].z;
+            v.w += p[wv].w;
+        }
+        const int owner = e4 / chunk, idx = e4 - owner * chunk;
+        st_shared_cluster_f32x4(mapa_shared(recv + 16u * (uint32_t)((int)rank * chunk + idx), (uint32_t)owner), v);
     }
-    if (nranks > 1) cluster_sync_all();  // every CTA's tile is complete and visible across the cluster
-    if (rank == 0) {
-        const uint32_t tile_addr = smem_u32(tile);
-        for (int e = threadIdx.x; e < kPerWarp; e += kDecWarps * 32) {
-            float v = tile[e];
-            for (uint32_t r = 1; r < nranks; ++r) v += ld_shared_cluster_f32(mapa_shared(tile_addr + 4u * (uint32_t)e, r));
-            const int i = e & 3, l = (e >> 2) & 31, nt = (e >> 7) & 7, mt = e >> 10;
-            const int row = 16 * mt + (l >> 2) + 8 * (i >> 1);
-            const int col = n0 + 8 * nt + 2 * (l & 3) + (i & 1);
-            if (row < M && col < N) {
-                if constexpr (sizeof(OutT) == 4) out[(size_t)row * N + col] = v;
-                else out[(size_t)row * N + col] = __float2half_rn(v);
+    // Second phase: every part has been stored (release) and is visible here (acquire). After it
+    // nobody touches another CTA's shared memory, so a CTA may leave as soon as it has written.
+    if (nranks > 1) {
+        cluster_arrive_release();
+        cluster_wait_acquire();
+    } else {
+        __syncthreads();
+    }
+    for (int idx = threadIdx.x; idx < chunk; idx += kDecWarps * 32) {
+        const float4* part = reinterpret_cast<const float4*>(smem + kDecRingBytes) + idx;
+        float4 p[8];
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r)
+            if (r < nranks) p[r] = part[(int)r * chunk];
+        float4 v = p[0];
+#pragma unroll
+        for (uint32_t r = 1; r < 8; ++r)
+            if (r < nranks) {
+                v.x += p[r].x;
+                v.y += p[r].y;
+                v.z += p[r].z;
+                v.w += p[r].w;
+            }
+        const int e4 = (int)rank * chunk + idx;
+        const int l = e4 & 31, tj = e4 >> 5;
+        const int col = n0 + 16 * (tj / NT) + (l >> 2), tok = 8 * (tj % NT) + 2 * (l & 3);
+        const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int cc = col + 8 * (i >> 1), tt = tok + (i & 1);  // N % 8 == 0: cc < N whenever col < N
+            if (cc < N && tt < M) {
+                if constexpr (sizeof(OutT) == 4) out[(size_t)tt * N + cc] = vv[i];
+                else out[(size_t)tt * N + cc] = __float2half_rn(vv[i]);
             }
         }
     }
-    if (nranks > 1) cluster_sync_all();  // no CTA leaves while its tile can still be read
 }
 
-// Cluster size (K slabs per 64-column block): the largest of 8, 4, 2, 1 that divides K / 16 and
-// keeps the grid within two CTAs per SM, so narrow matrices still spread over the whole GPU.
+// Cluster size (K slabs per 64-column block): the largest of 8, 4, 2, 1 that divides the number
+// of 32-row steps and keeps the grid within two CTAs per SM, so narrow matrices still spread
+// over the whole GPU.
 int decode_k_slabs(int n, int k) {
     const int blocks = (n + kDecCols - 1) / kDecCols;
+    const int steps = (k + kDecStepRows - 1) / kDecStepRows;
     const int cap = 2 * sm_count();
     for (int s = 8; s > 1; s >>= 1)
-        if ((k / 16) % s == 0 && blocks * s <= cap) return s;
+        if (steps % s == 0 && blocks * s <= cap) return s;
     return 1;
 }
 
-template <int MT, typename OutT>
+template <int NT, typename OutT>
 int launch_f16_decode(const void* x, int ldx, const void* w, void* out, int m, int n, int k, cudaStream_t st) {
     static bool configured[64] = {};
     int dev = 0;
     YB_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        YB_CUDA(cudaFuncSetAttribute(f16_decode_kernel<MT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes));
+        YB_CUDA(cudaFuncSetAttribute(f16_decode_kernel<NT, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmemBytes));
         configured[dev] = true;
     }
     const int slabs = decode_k_slabs(n, k);
@@ -295,7 +377,7 @@ int launch_f16_decode(const void* x, int ldx, const void* w, void* out, int m, i
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return check_cuda(cudaLaunchKernelEx(&cfg, f16_decode_kernel<MT, OutT>, static_cast<const __half*>(x), ldx,
+    return check_cuda(cudaLaunchKernelEx(&cfg, f16_decode_kernel<NT, OutT>, static_cast<const __half*>(x), ldx,
                                          static_cast<const __half*>(w), static_cast<OutT*>(out), m, n, k),
                       "f16_decode_kernel launch");
 }
@@ -335,17 +417,19 @@ extern "C" int y_b200_gemm_f16_decode(const void* x_f16, int ldx, const void* w_
     if (m < 1 || m > 32) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16_decode: M=%d outside 1..32", m);
     if (k < 16 || k % 16 != 0 || n < 8 || n % 8 != 0)
         return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16_decode: need K %% 16 == 0 and N %% 8 == 0 (K=%d N=%d)", k, n);
-    if (ldx < k || ldx % 2 != 0) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16_decode: ldx=%d must be even and >= K", ldx);
+    if (ldx < k || ldx % 8 != 0) return fail(Y_B200_ERR_SHAPE, "y_b200_gemm_f16_decode: ldx=%d must be a multiple of 8 and >= K", ldx);
     if (out_kind != Y_B200_F32 && out_kind != Y_B200_F16)
         return fail(Y_B200_ERR_INVALID, "y_b200_gemm_f16_decode: out_kind must be F32 or F16");
-    if ((reinterpret_cast<uintptr_t>(w_f16) & 15u) || (reinterpret_cast<uintptr_t>(x_f16) & 3u))
-        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_f16_decode: w must be 16-byte and x 4-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(w_f16) & 15u) || (reinterpret_cast<uintptr_t>(x_f16) & 15u))
+        return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_f16_decode: w and x must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (out_kind == Y_B200_F32)
-        return m <= 16 ? launch_f16_decode<1, float>(x_f16, ldx, w_f16, out, m, n, k, st)
-                       : launch_f16_decode<2, float>(x_f16, ldx, w_f16, out, m, n, k, st);
-    return m <= 16 ? launch_f16_decode<1, __half>(x_f16, ldx, w_f16, out, m, n, k, st)
-                   : launch_f16_decode<2, __half>(x_f16, ldx, w_f16, out, m, n, k, st);
+        return m <= 8    ? launch_f16_decode<1, float>(x_f16, ldx, w_f16, out, m, n, k, st)
+               : m <= 16 ? launch_f16_decode<2, float>(x_f16, ldx, w_f16, out, m, n, k, st)
+                         : launch_f16_decode<4, float>(x_f16, ldx, w_f16, out, m, n, k, st);
+    return m <= 8    ? launch_f16_decode<1, __half>(x_f16, ldx, w_f16, out, m, n, k, st)
+           : m <= 16 ? launch_f16_decode<2, __half>(x_f16, ldx, w_f16, out, m, n, k, st)
+                     : launch_f16_decode<4, __half>(x_f16, ldx, w_f16, out, m, n, k, st);
 }
 
 extern "C" int y_b200_gemm_f16_splitk_workspace(const void* a_f16, const void* b_f16, float* workspace, int m, int n, int k,
