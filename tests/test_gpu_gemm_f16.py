@@ -87,7 +87,9 @@ def test_swiglu_two_weight_drop_in(q, m, n, k):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 32])
-@pytest.mark.parametrize("n,k", [(8, 16), (40, 144), (4096, 4096), (11008, 4096), (264, 2048)])
+# (72, 112): four 32-row steps, the last one half zeros, split over a cluster of four;
+# (264, 2048): a cluster of eight; (40, 144): five steps, no cluster
+@pytest.mark.parametrize("n,k", [(8, 16), (40, 144), (72, 112), (4096, 4096), (11008, 4096), (264, 2048)])
 def test_decode_weight_streaming(q, m, n, k):
     x, w = ints_f16((m, k), 41, -2, 3), ints_f16((k, n), 42, -2, 3)
     want = oracle.gemm_f16(x, np.ascontiguousarray(w.T))
