@@ -717,7 +717,34 @@ def run_ours(args):
             dist.all_reduce(ms_, op=dist.ReduceOp.MAX)
         return world * 10 * src.numel() * src.element_size() / (ms_.item() * 1e-3) / 1e9
 
+    def link_both_ms():
+        """One step's output going out and one step's input coming in at the same time, on two
+        streams, ten times: the milliseconds per pair, which is what the pipelined step can at
+        best take per step when both directions of the link are busy."""
+        s_out, s_in = torch.cuda.Stream(), torch.cuda.Stream()
+        h2d_src = x_host if world == 1 else x_host[: x_host.shape[0] // world]
+        h2d_dst = x if world == 1 else x[: x.shape[0] // world]
+        barrier()
+        t0, t1, t2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        t0.record()
+        s_out.wait_event(t0), s_in.wait_event(t0)
+        with torch.cuda.stream(s_out):
+            for _ in range(10):
+                c_host[0].copy_(c, non_blocking=True)
+            t1.record()
+        with torch.cuda.stream(s_in):
+            for _ in range(10):
+                h2d_dst.copy_(h2d_src, non_blocking=True)
+            t2.record()
+        barrier()
+        ms_ = torch.tensor([max(t0.elapsed_time(t1), t0.elapsed_time(t2)) / 10], device=dev)
+        if world > 1:
+            dist.all_reduce(ms_, op=dist.ReduceOp.MAX)
+        return ms_.item()
+
+    both_ms = link_both_ms()
     host_link = {"d2h_gb_s_all_ranks": link_gbs(c_host[0], c), "h2d_gb_s_all_ranks": link_gbs(x, x_host),
+                 "both_directions_ms_per_step": both_ms, "e2e_ms_over_both_directions_ms": e2e_ms / both_ms,
                  "what": f"10 pinned {M * N_SHARD * 2 >> 20} MiB copies per rank, all {world} rank(s) at once, one direction at a time",
                  "e2e_bytes_gb_s_all_ranks": world * sum(layer.host_bytes_per_step()) / (e2e_ms * 1e-3) / 1e9,
                  "placement_per_rank": gather_objects(placement)}

@@ -615,6 +615,20 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::threads, 1)
     cp_async_wait<0>();  // only empty groups can be left; nothing may be pending at exit
 }
 
+// CTAs of a launch: one per SM (fewer for fewer column tiles than SMs). The straight-line path
+// (up to 8 tokens, K = 4096) wants four or five column tiles per CTA; a matrix too wide for
+// that in one wave runs as whole waves of such CTAs when the tile count allows it (N = 22016:
+// 296 CTAs instead of 148 with nine or ten tiles each on the loop path). A CTA of a later wave
+// starts when one of an earlier wave exits and finds the launch before long complete.
+int decode_grid(int nt, int n, int k) {
+    const int tiles = n / 16, sms = sm_count();
+    if (nt == 1 && k == 2 * DecodeCfg<1>::unit_k && tiles > 5 * sms) {
+        const int g = (tiles + 5 * sms - 1) / (5 * sms) * sms;
+        if (tiles / g >= 4 && (tiles + g - 1) / g <= 5) return g;
+    }
+    return tiles < sms ? tiles : sms;
+}
+
 template <int NT>
 int launch_decode(const void* x, const void* wstream, void* out, int m, int n, int k,
                   cudaStream_t st) {
@@ -628,7 +642,7 @@ int launch_decode(const void* x, const void* wstream, void* out, int m, int n, i
         configured[dev] = true;
     }
     const int tiles = n / 16;
-    const int grid = tiles < sm_count() ? tiles : sm_count();
+    const int grid = decode_grid(NT, n, k);
     return check_cuda(launch_pdl(int4_decode_kernel<NT>, (unsigned)grid, (unsigned)Cfg::threads, Cfg::smem_bytes, st,
                                  static_cast<const __half*>(x), static_cast<const uint8_t*>(wstream),
                                  static_cast<__half*>(out), m, n, k, tiles / grid, tiles % grid),
@@ -678,10 +692,9 @@ __global__ void __launch_bounds__(512, 1)
 }  // namespace
 
 // Launch geometry of the decode kernel for the host launch API.
-void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsigned* smem, int* slots,
+void decode_launch_geometry(int m, int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* slots,
                             int* unit_k) {
-    const int tiles = n > 0 ? n / 16 : 0;
-    *grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
+    *grid = n > 0 ? (unsigned)decode_grid(m <= 8 ? 1 : (m <= 16 ? 2 : 4), n, k) : 0u;
     if (m <= 8) { *block = DecodeCfg<1>::threads; *smem = DecodeCfg<1>::smem_bytes; *slots = DecodeCfg<1>::depth; *unit_k = DecodeCfg<1>::unit_k; }
     else if (m <= 16) { *block = DecodeCfg<2>::threads; *smem = DecodeCfg<2>::smem_bytes; *slots = DecodeCfg<2>::depth; *unit_k = DecodeCfg<2>::unit_k; }
     else { *block = DecodeCfg<4>::threads; *smem = DecodeCfg<4>::smem_bytes; *slots = DecodeCfg<4>::depth; *unit_k = DecodeCfg<4>::unit_k; }

@@ -40,7 +40,7 @@ struct y_kernel {
 };
 
 namespace yb {
-void decode_launch_geometry(int m, int n, unsigned* grid, unsigned* block, unsigned* smem, int* slots, int* unit_k);
+void decode_launch_geometry(int m, int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* slots, int* unit_k);
 void f16_decode_launch_geometry(int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
 }
 using namespace yb;
@@ -106,7 +106,7 @@ int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out
     memset(out, 0, sizeof *out);
     if (k->entry == Entry::Int4Decode) {
         int slots = 0, unit_k = 0;
-        decode_launch_geometry(m, n, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &slots, &unit_k);
+        decode_launch_geometry(m, n, kk, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &slots, &unit_k);
         out->grid[1] = out->grid[2] = 1;
         out->block[1] = out->block[2] = 1;
         out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
@@ -119,7 +119,7 @@ int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out
         f16_decode_launch_geometry(n, kk, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages, &out->cluster[0]);
         out->grid[1] = out->grid[2] = out->block[1] = out->block[2] = 1;
         out->cluster[1] = out->cluster[2] = 1;
-        out->cta_m = m <= 16 ? 16 : 32; out->cta_n = 64; out->cta_k = 16;
+        out->cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32); out->cta_n = 64; out->cta_k = 32;
         return 0;
     }
     // An f16 problem runs the byte-tiled kernels on rows of 2 K bytes; SwiGLU on 2 N interleaved columns.
