@@ -108,10 +108,11 @@ def test_decode_preconditions(q):
         q.gemm_int4_decode(x[:4, :100].contiguous(), s, 16)
 
 
-@pytest.mark.parametrize("tiles", [592, 740, 800, 149])
+@pytest.mark.parametrize("tiles", [592, 740, 800, 149, 1376])
 def test_decode_both_paths_on_mixed_shares(q, tiles):
     # K = 4096 with 592 / 740 column tiles: every CTA owns 4 / 5 tiles (straight-line path);
-    # 800: shares of 5 and 6 (both paths in one launch); 149: shares of 1 and 2 (loop only)
+    # 800: shares of 5 and 6 (both paths in one launch); 149: shares of 1 and 2 (loop only);
+    # 1376 (N = 22016): up to 8 tokens run as two waves of CTAs with 4 or 5 tiles each
     k, n = 4096, 16 * tiles
     w = oracle.fill_normal_f16(k * n, oracle.SEED_B + 11, 1.0 / 64.0).reshape(k, n)
     rq, rs = oracle.int4_quantize(w)
