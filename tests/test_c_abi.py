@@ -127,8 +127,13 @@ def test_other_reference_shapes_are_classified():
     assert "weight streaming" in dec and "Workspace required: 0 bytes" in dec and "tcgen05" not in dec
     out = (C.c_uint32 * 4)()
     assert lib.y_parse_launch_config(dec.encode(), 8, 4096, out) == 0
-    assert (out[0], out[1], out[2], out[3]) == (64, 1, 256, 81920)   # 64-column blocks (the parser knows no clusters)
+    assert (out[0], out[1], out[2], out[3]) == (64, 1, 256, 106496)   # 64-column blocks (the parser knows no clusters)
     assert "Launch grid required: (256, 1, 1) CTAs, block (256,1,1), cluster (4,1,1)" in dec
+    # 17..32 tokens run on tcgen05 with the weights as the MN-major operand: still no workspace
+    dec32 = runtime.compile_to_ptx("@tile(32, 4096, 4096)\nkernel gemm_f16_decode_m32(A: GlobalMemory<F16>, "
+                                   "B: GlobalMemory<F16>, C: GlobalMemory<F32>) {\n}\n")
+    assert "weight streaming, tcgen05.mma.cta_group::1.kind::f16" in dec32 and "Workspace required: 0 bytes" in dec32
+    assert "block (128,1,1), cluster (4,1,1)" in dec32
     rms = ("kernel rmsnorm_residual_4096(X: GlobalMemory<F16>, Residual: GlobalMemory<F16>, "
            "Weight: GlobalMemory<F16>, Out: GlobalMemory<F16>, NewResidual: GlobalMemory<F16>) {\n}\n")
     assert "family=rmsnorm_residual" in runtime.compile_to_ptx(rms)

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liby_b200.so")
-SOURCES = ["core.cu", "quantize.cu", "int4.cu", "gemm_fp8.cu", "gemm_f16.cu", "attention.cu", "autotuner.cu", "c_api.cu", "runtime.cu", "colpar.cu"]
+SOURCES = ["core.cu", "quantize.cu", "int4.cu", "gemm_fp8.cu", "gemm_f16.cu", "decode_umma.cu", "attention.cu", "autotuner.cu", "c_api.cu", "runtime.cu", "colpar.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--use_fast_math=false",

@@ -19,6 +19,9 @@
 #include "frontend.h"
 
 namespace yb {
+void f16_decode_launch_geometry(int n, int k, int sms, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
+void umma_decode_launch_geometry(int n, int k, int sms, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
+bool umma_decode_applies(int m, int n, int k);
 
 namespace {
 
@@ -251,18 +254,21 @@ std::string describe_kernel(const KernelDecl& k, KernelFamily fam, const std::st
         const bool swiglu = fam == KernelFamily::GemmF16Swiglu;
         const bool decode = fam == KernelFamily::GemmF16 && k.m <= 32 && k.k % 16 == 0 && k.n % 8 == 0;
         if (decode) {
-            // as decode_k_slabs in gemm_f16.cu, for the default profile's 148 SMs
-            const long long blocks = (k.n + 63) / 64;
-            int slabs = 1;
-            for (int sl = 8; sl > 1; sl >>= 1)
-                if ((k.k / 16) % sl == 0 && blocks * sl <= 2 * 148) { slabs = sl; break; }
+            // the geometry of the launch, for the default profile's 148 SMs
+            const bool umma = umma_decode_applies((int)k.m, (int)k.n, (int)k.k);
+            unsigned grid = 0, block = 0, smem = 0, cluster = 1;
+            int stages = 0;
+            if (umma) umma_decode_launch_geometry((int)k.n, (int)k.k, 148, &grid, &block, &smem, &stages, &cluster);
+            else f16_decode_launch_geometry((int)k.n, (int)k.k, 148, &grid, &block, &smem, &stages, &cluster);
             snprintf(buf, sizeof buf,
-                     "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %dx64x16 | 8x1 warps | "
-                     "weight streaming, mma.sync.m16n8k16 f16 x f16 -> f32, K split over a cluster of %d CTAs and the warps of each\n"
-                     "// Launch grid required: (%lld, 1, 1) CTAs, block (256,1,1), cluster (%d,1,1).\n"
-                     "// Dynamic shared memory required: 81920 bytes.\n"
+                     "// [Y TENSOR CORE GEMM] M=%lld N=%lld K=%lld | CTA %dx64x%d | %ux1 warps | "
+                     "weight streaming, %s f16 x f16 -> f32, K split over a cluster of %u CTAs%s\n"
+                     "// Launch grid required: (%u, 1, 1) CTAs, block (%u,1,1), cluster (%u,1,1).\n"
+                     "// Dynamic shared memory required: %u bytes.\n"
                      "// Workspace required: 0 bytes.\n",
-                     k.m, k.n, k.k, k.m <= 16 ? 16 : 32, slabs, blocks * slabs, slabs);
+                     k.m, k.n, k.k, k.m <= 8 ? 8 : (k.m <= 16 ? 16 : 32), umma ? 64 : 32, block / 32,
+                     umma ? "tcgen05.mma.cta_group::1.kind::f16 (weights MN-major from TMA, TMEM accumulator)" : "mma.sync.m16n8k16",
+                     cluster, umma ? "" : " and the warps of each", grid, block, cluster, smem);
         } else {
             const long long n_eff = swiglu ? 2 * k.n : k.n;
             Candidate c = autotune((uint32_t)k.m, (uint32_t)n_eff, (uint32_t)(2 * k.k), Precision::Fp8, "NVIDIA B200", 148);

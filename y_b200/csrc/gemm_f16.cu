@@ -343,10 +343,10 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
 // Cluster size (K slabs per 64-column block): the largest of 8, 4, 2, 1 that divides the number
 // of 32-row steps and keeps the grid within two CTAs per SM, so narrow matrices still spread
 // over the whole GPU.
-int decode_k_slabs(int n, int k) {
+int decode_k_slabs(int n, int k, int sms = 0) {
     const int blocks = (n + kDecCols - 1) / kDecCols;
     const int steps = (k + kDecStepRows - 1) / kDecStepRows;
-    const int cap = 2 * sm_count();
+    const int cap = 2 * (sms > 0 ? sms : sm_count());
     for (int s = 8; s > 1; s >>= 1)
         if (steps % s == 0 && blocks * s <= cap) return s;
     return 1;
@@ -399,14 +399,21 @@ size_t round256(size_t v) { return (v + 255) & ~(size_t)255; }
 }  // namespace
 
 // Launch geometry of the weight-streaming kernel for the host launch API.
-void f16_decode_launch_geometry(int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster) {
-    *cluster = (unsigned)decode_k_slabs(n, k);
+// `sms` > 0: for a GPU with that many multiprocessors (no device needed); 0: the current device.
+void f16_decode_launch_geometry(int n, int k, int sms, unsigned* grid, unsigned* block, unsigned* smem, int* stages,
+                                unsigned* cluster) {
+    *cluster = (unsigned)decode_k_slabs(n, k, sms);
     *grid = (unsigned)((n + kDecCols - 1) / kDecCols) * *cluster;
     *block = kDecWarps * 32;
     *smem = kDecSmemBytes;
     *stages = kDecStages;
 }
 
+}  // namespace yb
+
+namespace yb {
+bool umma_decode_applies(int m, int n, int k);
+int launch_umma_decode(const void* x, int ldx, const void* w, void* out, bool out_f32, int m, int n, int k, cudaStream_t st);
 }  // namespace yb
 
 using namespace yb;
@@ -423,6 +430,9 @@ extern "C" int y_b200_gemm_f16_decode(const void* x_f16, int ldx, const void* w_
     if ((reinterpret_cast<uintptr_t>(w_f16) & 15u) || (reinterpret_cast<uintptr_t>(x_f16) & 15u))
         return fail(Y_B200_ERR_ALIGN, "y_b200_gemm_f16_decode: w and x must be 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // 17..32 tokens: the tcgen05 kernel (decode_umma.cu) where its shape rules hold; mma.sync
+    // issues too slowly for four token tiles per weight fragment.
+    if (umma_decode_applies(m, n, k) && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) return launch_umma_decode(x_f16, ldx, w_f16, out, out_kind == Y_B200_F32, m, n, k, st);
     if (out_kind == Y_B200_F32)
         return m <= 8    ? launch_f16_decode<1, float>(x_f16, ldx, w_f16, out, m, n, k, st)
                : m <= 16 ? launch_f16_decode<2, float>(x_f16, ldx, w_f16, out, m, n, k, st)

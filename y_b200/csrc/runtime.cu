@@ -41,7 +41,9 @@ struct y_kernel {
 
 namespace yb {
 void decode_launch_geometry(int m, int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* slots, int* unit_k);
-void f16_decode_launch_geometry(int n, int k, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
+void f16_decode_launch_geometry(int n, int k, int sms, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
+void umma_decode_launch_geometry(int n, int k, int sms, unsigned* grid, unsigned* block, unsigned* smem, int* stages, unsigned* cluster);
+bool umma_decode_applies(int m, int n, int k);
 }
 using namespace yb;
 
@@ -116,10 +118,12 @@ int kernel_info(const y_kernel* k, int m, int n, int kk, y_b200_launch_info* out
     const bool f16 = k->entry == Entry::GemmF16 || k->entry == Entry::GemmF16BiasRelu || k->entry == Entry::GemmF16Swiglu ||
                      k->entry == Entry::TensorCoreGemm || k->entry == Entry::FusedGemmBiasReluFp16;
     if ((k->entry == Entry::GemmF16 || k->entry == Entry::TensorCoreGemm) && uses_decode_kernel(m, n, kk)) {
-        f16_decode_launch_geometry(n, kk, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages, &out->cluster[0]);
+        const bool umma = umma_decode_applies(m, n, kk);  // 17..32 tokens: the tcgen05 kernel
+        if (umma) umma_decode_launch_geometry(n, kk, 0, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages, &out->cluster[0]);
+        else f16_decode_launch_geometry(n, kk, 0, &out->grid[0], &out->block[0], &out->dyn_smem_bytes, &out->stages, &out->cluster[0]);
         out->grid[1] = out->grid[2] = out->block[1] = out->block[2] = 1;
         out->cluster[1] = out->cluster[2] = 1;
-        out->cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32); out->cta_n = 64; out->cta_k = 32;
+        out->cta_m = m <= 8 ? 8 : (m <= 16 ? 16 : 32); out->cta_n = 64; out->cta_k = umma ? 64 : 32;
         return 0;
     }
     // An f16 problem runs the byte-tiled kernels on rows of 2 K bytes; SwiGLU on 2 N interleaved columns.
