@@ -88,9 +88,10 @@ def test_swiglu_two_weight_drop_in(q, m, n, k):
 
 @pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 32])
 # (72, 112): four 32-row steps, the last one half zeros, split over a cluster of four;
-# (264, 2048): a cluster of eight; (40, 144): five steps, no cluster. From 17 tokens on, shapes with
-# K % 64 == 0 run on the tcgen05 kernel: (64, 64) one K block, (72, 128) a cluster of two with a
-# column block that is mostly outside the matrix, (264, 2048) a cluster of eight
+# (264, 2048): a cluster of eight; (40, 144): five steps, no cluster. From 17 tokens on all of them
+# run on the tcgen05 kernel: (64, 64) one K block, (72, 128) a cluster of two with a column block
+# that is mostly outside the matrix, (264, 2048) a cluster of eight, (72, 112) and (40, 144) a
+# last K block that reaches beyond K (zero-filled by TMA), (8, 16) a single block of 16 rows
 @pytest.mark.parametrize("n,k", [(8, 16), (40, 144), (72, 112), (64, 64), (72, 128), (4096, 4096), (11008, 4096), (264, 2048)])
 def test_decode_weight_streaming(q, m, n, k):
     x, w = ints_f16((m, k), 41, -2, 3), ints_f16((k, n), 42, -2, 3)

@@ -104,7 +104,9 @@ __global__ void __launch_bounds__(kUdThreads, 2)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank(), nranks = cluster_size();
     const int n0 = (int)(blockIdx.x / nranks) * kUdCols;
-    const int slab_kb = p.K / kUdKB / (int)nranks;  // the host makes K / 64 a multiple of the cluster size
+    // K blocks of 64 rows; the host makes their number a multiple of the cluster size. The last
+    // block of the matrix may reach beyond K: TMA zero-fills those rows of both operands.
+    const int slab_kb = (p.K + kUdKB - 1) / kUdKB / (int)nranks;
     const int kb0 = (int)rank * slab_kb;
 
     if (threadIdx.x == 0) {
@@ -338,17 +340,17 @@ int ud_make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, 
 
 }  // namespace
 
-// Cluster size for the tcgen05 decode kernel: the largest of 8, 4, 2, 1 that divides K / 64 and
+// Cluster size for the tcgen05 decode kernel: the largest of 8, 4, 2, 1 that divides the number of K blocks and
 // keeps the grid within two CTAs per SM.
 int umma_decode_slabs(int n, int k, int sms = 0) {
-    const int blocks = (n + kUdCols - 1) / kUdCols, kbs = k / kUdKB;
+    const int blocks = (n + kUdCols - 1) / kUdCols, kbs = (k + kUdKB - 1) / kUdKB;
     const int cap = 2 * (sms > 0 ? sms : sm_count());
     for (int s = 8; s > 1; s >>= 1)
         if (kbs % s == 0 && blocks * s <= cap) return s;
     return 1;
 }
 
-bool umma_decode_applies(int m, int n, int k) { return m > 16 && m <= 32 && k >= kUdKB && k % kUdKB == 0 && n % 8 == 0; }
+bool umma_decode_applies(int m, int n, int k) { return m > 16 && m <= 32 && k >= 16 && k % 16 == 0 && n % 8 == 0; }
 
 // `sms` > 0: for a GPU with that many multiprocessors (no device needed); 0: the current device.
 void umma_decode_launch_geometry(int n, int k, int sms, unsigned* grid, unsigned* block, unsigned* smem, int* stages,
