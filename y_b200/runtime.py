@@ -31,7 +31,10 @@ class DeviceBuffer:
             self._h = None
 
     def __del__(self):
-        self.free()
+        try:
+            self.free()
+        except Exception:  # at interpreter exit the library binding may be gone already
+            pass
 
 
 class KernelModule:
@@ -52,7 +55,10 @@ class KernelModule:
             self._h = None
 
     def __del__(self):
-        self.free()
+        try:
+            self.free()
+        except Exception:  # at interpreter exit the library binding may be gone already
+            pass
 
 
 def _args(values) -> C.Array:
