@@ -100,7 +100,7 @@ int launch_transpose(const void* src, int rows, int cols, void* dst, int dst_mul
 constexpr int kDecWarps = 8;
 constexpr int kDecCols = 64;
 constexpr int kDecStepRows = 32;
-constexpr int kDecStages = 3;
+constexpr int kDecStages = 3;  // slots of a warp's ring (two are used with 9 to 16 tokens, see the kernel)
 constexpr int kDecSlotBytes = kDecStepRows * kDecCols * 2;  // 4 KB
 constexpr int kDecRingBytes = kDecWarps * kDecStages * kDecSlotBytes;  // 96 KB
 constexpr int kDecRecvBytes = 2 * 8 * 32 * 16;  // one reduced tile of up to 32 tokens x 64 columns, f32: 8 KB
@@ -158,6 +158,10 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
     const int per_warp = (slab_steps + kDecWarps - 1) / kDecWarps;
     const int my_steps = max(0, min(per_warp, slab_steps - warp * per_warp));
     const int step0 = (int)rank * slab_steps + warp * per_warp;  // this warp's first step
+    // Steps in flight per warp. With two token tiles two are faster than three (7.7 against
+    // 7.9 us at 16 tokens, K = N = 4096; 17.0 against 17.8 at N = 11008); with one tile the third
+    // pays (6.5 against 6.7 us at up to 8 tokens).
+    constexpr int kStages = NT == 2 ? 2 : kDecStages;
     const uint32_t ring = smem_u32(smem) + warp * (kDecStages * kDecSlotBytes);
     pdl_launch_dependents();
 
@@ -167,9 +171,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
     const int krow0 = kDecStepRows * step0 + crow;
     // columns beyond N and rows beyond K are zero-filled without a read from a valid address
     const __half* wsrc = w + (col_ok ? n0 + cunit * 8 : 0);
-    auto request = [&](int i) {  // step i of this warp into slot i % kDecStages; always commits a group
+    auto request = [&](int i) {  // step i of this warp into slot i % kStages; always commits a group
         if (i < my_steps) {
-            const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
+            const uint32_t slot = ring + (i % kStages) * kDecSlotBytes;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int row = crow + 4 * j, k = krow0 + kDecStepRows * i + 4 * j;
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
     };
     // The weights do not depend on the kernel before this one: the ring fills before the wait.
 #pragma unroll 1
-    for (int i = 0; i < kDecStages; ++i) request(i);
+    for (int i = 0; i < kStages; ++i) request(i);
     pdl_wait();  // x is the previous kernel's output
 
     const int g = lane >> 2, c = lane & 3;
@@ -223,9 +227,9 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
         for (int j = 0; j < kAhead; ++j) {
             const int i = i0 + j;
             if (i < my_steps) {  // uniform across the warp
-                cp_async_wait<kDecStages - 1>();  // all but the newest kDecStages - 1 groups: step i has landed
+                cp_async_wait<kStages - 1>();  // all but the newest kStages - 1 groups: step i has landed
                 __syncwarp();
-                const uint32_t slot = ring + (i % kDecStages) * kDecSlotBytes;
+                const uint32_t slot = ring + (i % kStages) * kDecSlotBytes;
                 // The weights are the 16-row operand (16 columns x 16 K slots per MMA, so up to 8
                 // tokens cost one MMA per 256 weights), the tokens the 8-wide one. ldmatrix call t
                 // returns (K slots 0..7, columns 16t..16t+7), (slots 8..15, same columns), and
@@ -253,7 +257,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
                     read_weights(0, b0);
                     read_weights(1, b1);
                     __syncwarp();  // every lane has read the slot
-                    request(i + kDecStages);
+                    request(i + kStages);
                     mmas(0, b0);
                     mmas(1, b1);
                 } else {
@@ -262,7 +266,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
                     mmas(0, b);
                     read_weights(1, b);
                     __syncwarp();  // every lane has read the slot
-                    request(i + kDecStages);
+                    request(i + kStages);
                     mmas(1, b);
                 }
                 load_a(i + kAhead, a[j]);
