@@ -186,3 +186,18 @@ def test_launch_api_entries(q):
     kern.free()
     q.device_status()
     ctx.close()
+
+
+def test_decode_tcgen05_tensor_map_cache_wraps(q):
+    # the 17..32-token kernel keeps the tensor maps of a host thread's last 64 operands: more
+    # distinct weight matrices than that, twice over, must keep giving exact results
+    m, n, k = 24, 72, 128
+    x = ints_f16((m, k), 51, -2, 3)
+    xd = f16_dev(x)
+    ws = [ints_f16((k, n), 100 + i, -2, 3) for i in range(70)]
+    wd = [f16_dev(w) for w in ws]
+    for _ in range(2):
+        for w, d in zip(ws, wd):
+            want = oracle.gemm_f16(x, np.ascontiguousarray(w.T))
+            assert np.array_equal(q.gemm_f16_decode(xd, d).cpu().numpy(), want)
+    q.device_status()
