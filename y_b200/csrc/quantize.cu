@@ -141,8 +141,11 @@ __global__ void __launch_bounds__(kThreads)
     if (SCALE_IS_AMAX && scale_out != nullptr && blockIdx.x == 0 && threadIdx.x == 0)
         scale_out[0] = scale;
     const size_t n16 = n / 16;
-    for (size_t v = (size_t)blockIdx.x * kThreads + threadIdx.x; v < n16;
-         v += (size_t)gridDim.x * kThreads) {
+    for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < n16;
+         i += (size_t)gridDim.x * kThreads) {
+        // After an amax pass over the same tensor (first to last) the end of it is what L2 still
+        // holds: walk it last to first.
+        const size_t v = SCALE_IS_AMAX ? n16 - 1 - i : i;
         float a[8], b[8];
         Elem<KIND>::load8(x, v * 16, a);
         Elem<KIND>::load8(x, v * 16 + 8, b);
@@ -248,7 +251,9 @@ __global__ void __launch_bounds__(kThreads)
         scale_out[0] = scale;
     const size_t c0 = (size_t)blockIdx.x * kTC;
     const int row_tiles = (int)(rows / kTR);
-    const int rt0 = blockIdx.y * tiles_per_cta, rt1 = min(rt0 + tiles_per_cta, row_tiles);
+    // after an amax pass the last rows are what L2 still holds: the strips that start first take those
+    const int strip = SCALE_IS_AMAX ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
+    const int rt0 = strip * tiles_per_cta, rt1 = min(rt0 + tiles_per_cta, row_tiles);
     const int rq = threadIdx.x / 8, cv = threadIdx.x % 8;
     const uint16_t* xin = x + c0 + (size_t)cv * 8 + (size_t)rq * 4 * cols;  // row rq*4 of tile 0
     const int oc0 = threadIdx.x / 8, orv = threadIdx.x % 8;                // write-out slots
