@@ -18,7 +18,7 @@ def q(cuda):
     return quant
 
 
-@pytest.mark.parametrize("k,n", [(128, 16), (256, 32), (1024, 176), (4096, 1376)])
+@pytest.mark.parametrize("k,n", [(128, 16), (256, 32), (1024, 176), (4096, 1376), (4096, 11008)])
 def test_quantise_and_repack_bit_exact(q, k, n):
     w = oracle.fill_normal_f16(k * n, oracle.SEED_B + 3, 1.0 / 16.0).reshape(k, n)
     if k >= 256:
@@ -29,6 +29,32 @@ def test_quantise_and_repack_bit_exact(q, k, n):
     assert np.array_equal(host_bits(sc), rs)
     stream = q.int4_repack(qw, sc)
     assert np.array_equal(stream.cpu().numpy(), oracle.int4_repack(rq, rs))
+
+
+def test_quantise_ties_and_near_ties_bit_exact(q):
+    # The kernel replaces the per-element division by a multiplication with 1 / s and takes the
+    # division only near half-integers. Columns whose quotients are EXACT half-integers (ties go
+    # to even), columns of every f16 value of a binade against an awkward scale, subnormal
+    # weights and a subnormal scale must still give the oracle's codes.
+    k, n = 256, 64
+    w = np.zeros((k, n), np.float32)
+    rng = np.random.default_rng(17)
+    for c in range(n):
+        s0 = 2.0 ** -(c % 12)                     # group amax = 7 s0 -> scale exactly s0
+        half = (rng.integers(-7, 7, size=k) + 0.5) * s0     # -6.5 .. 6.5 times s0
+        w[:, c] = half
+        w[0, c] = 7.0 * s0
+        w[128, c] = -7.0 * s0
+    wh = w.astype(np.float16)
+    # awkward scales: amax values whose seventh is not a power of two; all f16 values of [1, 2)
+    wh[:128, 40:48] = np.arange(0x3C00, 0x3C00 + 128 * 8, dtype=np.uint16).view(np.float16).reshape(128, 8)
+    wh[128:, 40:48] = (np.arange(0x3C00 + 1024 - 128 * 8, 0x3C00 + 1024, dtype=np.uint16).view(np.float16).reshape(128, 8) * np.float16(-1))
+    wh[:128, 48:52] = np.arange(1, 1 + 128 * 4, dtype=np.uint16).view(np.float16).reshape(128, 4)   # subnormals only: subnormal scale
+    bits = wh.view(np.uint16)
+    qw, sc = q.int4_quantize(f16_dev(bits))
+    rq, rs = oracle.int4_quantize(bits)
+    assert np.array_equal(host_bits(sc), rs)
+    assert np.array_equal(qw.cpu().numpy().view(np.uint32), rq)
 
 
 @pytest.mark.parametrize("m", [1, 2, 4, 7, 8, 9, 16, 17, 32])

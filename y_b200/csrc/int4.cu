@@ -31,12 +31,35 @@ namespace {
 // a half warp. The weights are read once and stay in registers between the column amax
 // (partial maxima per row block through shared memory) and the packing: a packed word holds
 // eight K-consecutive weights of one column, exactly the thread's eight rows, so every
-// thread writes 32 contiguous bytes of qweight and a half warp 512.
-__global__ void __launch_bounds__(256)
+// thread writes 32 contiguous bytes of qweight and a half warp 512. The kernel is one
+// load-reduce-pack round per CTA, so what it needs is bytes in flight per SM: four CTAs per SM
+// (64 registers) run 39 us at 4096 x 11008 against 43 with three; four rows per thread in CTAs
+// of 512 (40 registers, three CTAs, halves of a word swapped by shuffle) were 43 us again.
+//
+// The code of a weight is clamp(rint(v / s), -8, 7) with an IEEE division and ties to even. The
+// division is not paid per element: v and s are f16 values, so the exact quotient is a ratio of
+// two integers below 2048 times a power of two, and such a ratio is either exactly a half-integer
+// or at least 1 / 4094 away from every half-integer. t = v * (1 / s) carries an error below
+// 1e-6 for |t| < 16, so rint(t) is the code unless t sits within 1e-4 of a half-integer (then the
+// quotient IS that half-integer; the division below settles the tie). Rounding is done by adding
+// and subtracting 1.5 * 2^23 (no conversion instructions); anything outside |t| < 16, NaN
+// included, takes the division as well, so every input gives the same code as before.
+__device__ __forceinline__ int int4_code(float v, float s, float rcp_s) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: v + kMagic has v's nearest integer in its low mantissa bits
+    const float t = __fmul_rn(v, rcp_s);
+    const float y = __fadd_rn(t, kMagic);
+    const float d = fabsf(__fsub_rn(t, __fsub_rn(y, kMagic)));
+    int q = __float_as_int(y) - 0x4B400000;
+    if (!(fabsf(t) < 16.0f) || d > 0.4999f) q = s > 0.0f ? __float2int_rn(__fdiv_rn(v, s)) : 0;
+    return max(-8, min(7, q));
+}
+
+__global__ void __launch_bounds__(256, 4)
     int4_quantize_kernel(const __half* __restrict__ w, size_t K, size_t N,
                          uint32_t* __restrict__ qweight, __half* __restrict__ scales) {
     __shared__ float part[16][128];
     __shared__ float col_scale[128];
+    __shared__ float col_rcp[128];
     const int cv = threadIdx.x & 15, rg = threadIdx.x >> 4;
     const size_t g = blockIdx.y;
     const size_t col = (size_t)blockIdx.x * 128 + (size_t)cv * 8;
@@ -67,6 +90,7 @@ __global__ void __launch_bounds__(256)
         for (int r = 1; r < 16; ++r) a = fmaxf(a, part[r][threadIdx.x]);
         const __half h = __float2half_rn(__fdiv_rn(a, 7.0f));
         col_scale[threadIdx.x] = __half2float(h);
+        col_rcp[threadIdx.x] = __half2float(h) > 0.0f ? __frcp_rn(__half2float(h)) : 0.0f;
         const size_t c = (size_t)blockIdx.x * 128 + threadIdx.x;
         if (c < N) scales[g * N + c] = h;
     }
@@ -79,10 +103,8 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __half22float2(h[j]);
-            const float s0 = col_scale[cv * 8 + 2 * j], s1 = col_scale[cv * 8 + 2 * j + 1];
-            int q0 = 0, q1 = 0;
-            if (s0 > 0.0f) q0 = max(-8, min(7, __float2int_rn(__fdiv_rn(f.x, s0))));
-            if (s1 > 0.0f) q1 = max(-8, min(7, __float2int_rn(__fdiv_rn(f.y, s1))));
+            const int q0 = int4_code(f.x, col_scale[cv * 8 + 2 * j], col_rcp[cv * 8 + 2 * j]);
+            const int q1 = int4_code(f.y, col_scale[cv * 8 + 2 * j + 1], col_rcp[cv * 8 + 2 * j + 1]);
             words[2 * j] |= ((uint32_t)q0 & 0xfu) << (4 * r);
             words[2 * j + 1] |= ((uint32_t)q1 & 0xfu) << (4 * r);
         }
