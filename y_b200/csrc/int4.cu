@@ -126,31 +126,44 @@ constexpr int kBlkWords = kBlkBytes / 4;  // 264
 
 __global__ void __launch_bounds__(256)
     int4_repack_kernel(const uint32_t* __restrict__ qweight, const uint16_t* __restrict__ scales,
-                       size_t ngroups, size_t N, size_t total_words,
+                       size_t ngroups, size_t N, size_t total_blocks,
                        uint32_t* __restrict__ stream) {
-    for (size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x; idx < total_words;
-         idx += (size_t)gridDim.x * 256) {
-        const size_t blk = idx / kBlkWords;
-        const int wi = (int)(idx % kBlkWords);
-        const size_t t = blk / ngroups, g = blk % ngroups;
-        uint32_t outw;
-        if (wi < 256) {
-            const int h = wi / 128, lane = (wi % 128) / 4, i = wi % 4;
-            const int gq = lane / 4, c = lane % 4;
-            const size_t kw = g * 16 + (size_t)(4 * (2 * h + i / 2) + c);
-            const size_t col = t * 16 + (size_t)(gq + 8 * (i % 2));
-            const uint32_t src = qweight[kw * N + col] ^ 0x88888888u;
-            // nibble positions 0,4,1,5,2,6,3,7 for logical elements 0..7
-            outw = (src & 0xfu) | ((src >> 4) & 0xfu) << 16 | ((src >> 8) & 0xfu) << 4 |
-                   ((src >> 12) & 0xfu) << 20 | ((src >> 16) & 0xfu) << 8 |
-                   ((src >> 20) & 0xfu) << 24 | ((src >> 24) & 0xfu) << 12 |
-                   ((src >> 28) & 0xfu) << 28;
-        } else {
-            const int sp = wi - 256;  // scale pair 0..7
-            const uint16_t* s = scales + g * N + t * 16 + 2 * sp;
-            outw = (uint32_t)s[0] | ((uint32_t)s[1] << 16);
+    // One warp per 1056-byte block. Its 256 source words are 16 packed rows of 16 adjacent
+    // columns: a half warp reads one 64-byte row segment per load (eight loads per lane), the
+    // words change places in shared memory (row pitch 17 words: both sides conflict-free) and
+    // every lane writes its two 16-byte units of the block; lanes 0..7 copy the scale pairs. (One
+    // output word per thread gathered its source with a stride of N words: 8x read
+    // amplification, 27 us for 4096 x 11008 against 2 x 23 MB of traffic.)
+    __shared__ uint32_t tile[8][16][17];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t(*t)[17] = tile[warp];
+    const int rsel = lane >> 4, csel = lane & 15;
+    const int gq = lane >> 2, c = lane & 3;
+    for (size_t blk = (size_t)blockIdx.x * 8 + warp; blk < total_blocks; blk += (size_t)gridDim.x * 8) {
+        const size_t tl = blk / ngroups, g = blk % ngroups;
+        const uint32_t* src = qweight + (g * 16 + (size_t)rsel) * N + tl * 16 + csel;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t[2 * r + rsel][csel] = src[(size_t)(2 * r) * N];
+        __syncwarp();
+        uint32_t* dst = stream + blk * kBlkWords;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t v = t[4 * (2 * h + i / 2) + c][gq + 8 * (i % 2)] ^ 0x88888888u;
+                // nibble positions 0,4,1,5,2,6,3,7 for logical elements 0..7
+                o[i] = (v & 0xfu) | ((v >> 4) & 0xfu) << 16 | ((v >> 8) & 0xfu) << 4 | ((v >> 12) & 0xfu) << 20 |
+                       ((v >> 16) & 0xfu) << 8 | ((v >> 20) & 0xfu) << 24 | ((v >> 24) & 0xfu) << 12 |
+                       ((v >> 28) & 0xfu) << 28;
+            }
+            *reinterpret_cast<uint4*>(dst + h * 128 + lane * 4) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        stream[idx] = outw;
+        if (lane < 8) {
+            const uint16_t* sp = scales + g * N + tl * 16 + 2 * lane;
+            dst[256 + lane] = (uint32_t)sp[0] | ((uint32_t)sp[1] << 16);
+        }
+        __syncwarp();  // the tile is reused by the warp's next block
     }
 }
 
@@ -749,12 +762,12 @@ extern "C" int y_b200_int4_repack(const uint32_t* qweight, const void* scales_f1
     if (k == 0 || k % 128 != 0 || n == 0 || n % 16 != 0)
         return fail(Y_B200_ERR_SHAPE, "y_b200_int4_repack: need K %% 128 == 0 and N %% 16 == 0 (K=%zu N=%zu)", k, n);
     if (!aligned16(wstream)) return fail(Y_B200_ERR_ALIGN, "y_b200_int4_repack: wstream must be 16-byte aligned");
-    const size_t words = y_b200_int4_stream_bytes(k, n) / 4;
-    size_t blocks = (words + 255) / 256;
+    const size_t total_blocks = (n / 16) * (k / 128);  // 1056-byte blocks, one warp each
+    size_t ctas = (total_blocks + 7) / 8;
     const size_t cap = (size_t)sm_count() * 16;
-    if (blocks > cap) blocks = cap;
-    int4_repack_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        qweight, static_cast<const uint16_t*>(scales_f16), k / 128, n, words,
+    if (ctas > cap) ctas = cap;
+    int4_repack_kernel<<<(unsigned)ctas, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        qweight, static_cast<const uint16_t*>(scales_f16), k / 128, n, total_blocks,
         static_cast<uint32_t*>(wstream));
     return check_cuda(cudaGetLastError(), "int4_repack_kernel launch");
 }
