@@ -31,10 +31,11 @@ namespace {
 // a half warp. The weights are read once and stay in registers between the column amax
 // (partial maxima per row block through shared memory) and the packing: a packed word holds
 // eight K-consecutive weights of one column, exactly the thread's eight rows, so every
-// thread writes 32 contiguous bytes of qweight and a half warp 512. The kernel is one
-// load-reduce-pack round per CTA, so what it needs is bytes in flight per SM: four CTAs per SM
-// (64 registers) run 39 us at 4096 x 11008 against 43 with three; four rows per thread in CTAs
-// of 512 (40 registers, three CTAs, halves of a word swapped by shuffle) were 43 us again.
+// thread writes 32 contiguous bytes of qweight and a half warp 512. Measured at 4096 x 11008:
+// rows held in registers, three CTAs per SM 43 us, four (64 registers) 39 us; four rows per
+// thread in CTAs of 512 (halves of a word swapped by shuffle) 43 us; the tile staged in shared
+// memory by cp.async (below: 47 registers, five CTAs per SM) 37.5 us. About 15 instructions per
+// weight remain (conversion, amax, code, packing): 19 us of issue time per SM.
 //
 // The code of a weight is clamp(rint(v / s), -8, 7) with an IEEE division and ties to even. The
 // division is not paid per element: v and s are f16 values, so the exact quotient is a ratio of
@@ -44,6 +45,11 @@ namespace {
 // quotient IS that half-integer; the division below settles the tie). Rounding is done by adding
 // and subtracting 1.5 * 2^23 (no conversion instructions); anything outside |t| < 16, NaN
 // included, takes the division as well, so every input gives the same code as before.
+// 16-byte asynchronous copy that writes zeros and reads nothing when `valid` is false.
+__device__ __forceinline__ void cp_async_16_zfill_q(uint32_t dst_smem, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ int int4_code(float v, float s, float rcp_s) {
     constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: v + kMagic has v's nearest integer in its low mantissa bits
     const float t = __fmul_rn(v, rcp_s);
@@ -54,9 +60,13 @@ __device__ __forceinline__ int int4_code(float v, float s, float rcp_s) {
     return max(-8, min(7, q));
 }
 
-__global__ void __launch_bounds__(256, 4)
+__global__ void __launch_bounds__(256, 5)
     int4_quantize_kernel(const __half* __restrict__ w, size_t K, size_t N,
                          uint32_t* __restrict__ qweight, __half* __restrict__ scales) {
+    // The CTA's 128 x 128 tile waits in shared memory, not in registers: a thread copies its
+    // eight 16-byte units there asynchronously and reads them back twice (amax, packing), so
+    // five CTAs fit an SM and 160 KB per SM are in flight.
+    __shared__ __align__(16) uint8_t tile[128][256];
     __shared__ float part[16][128];
     __shared__ float col_scale[128];
     __shared__ float col_rcp[128];
@@ -64,21 +74,23 @@ __global__ void __launch_bounds__(256, 4)
     const size_t g = blockIdx.y;
     const size_t col = (size_t)blockIdx.x * 128 + (size_t)cv * 8;
     const bool live = col < N;  // N % 8 == 0: a column vector is wholly inside or outside
-    uint4 rows[8];
+    {
+        const __half* base = w + (g * 128 + (size_t)rg * 8) * N + (live ? col : 0);
+        const uint32_t dst = smem_u32(&tile[rg * 8][cv * 16]);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) cp_async_16_zfill_q(dst + r * 256, base + (size_t)r * N, live);
+        asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+    }
     float amax[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-    if (live) {
-        const __half* base = w + (g * 128 + (size_t)rg * 8) * N + col;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) rows[r] = *reinterpret_cast<const uint4*>(base + (size_t)r * N);
+    for (int r = 0; r < 8; ++r) {
+        const uint4 row = *reinterpret_cast<const uint4*>(&tile[rg * 8 + r][cv * 16]);  // this thread's own copy
+        const __half2* h = reinterpret_cast<const __half2*>(&row);
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const __half2* h = reinterpret_cast<const __half2*>(&rows[r]);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h[j]);
-                amax[2 * j] = fmaxf(amax[2 * j], fabsf(f.x));
-                amax[2 * j + 1] = fmaxf(amax[2 * j + 1], fabsf(f.y));
-            }
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            amax[2 * j] = fmaxf(amax[2 * j], fabsf(f.x));
+            amax[2 * j + 1] = fmaxf(amax[2 * j + 1], fabsf(f.y));
         }
     }
 #pragma unroll
@@ -99,7 +111,8 @@ __global__ void __launch_bounds__(256, 4)
     uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-        const __half2* h = reinterpret_cast<const __half2*>(&rows[r]);
+        const uint4 row = *reinterpret_cast<const uint4*>(&tile[rg * 8 + r][cv * 16]);
+        const __half2* h = reinterpret_cast<const __half2*>(&row);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __half22float2(h[j]);
