@@ -249,6 +249,36 @@ def other_config_metrics(peaks):
     us = timeit(bias_relu, iters=30)
     tf = 2.0 * m * n * k / us / 1e6
     out["fp8_gemm_4096_bias_relu_bf16"] = {"us": round(us, 2), "tflops": round(tf, 1), "frac_of_2x_bf16_peak": round(tf / fp8_peak, 4)}
+    # The plain GEMM of the same operands against cuBLASLt's (torch._scaled_mm), in interleaved
+    # bursts like the step's comparator: a yardstick, nothing of the product path goes through it.
+    try:
+        cmp_out = [torch.empty(m, n, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+
+        def ours_plain():
+            aq, bqt, sa, sb, c = sets[it[0] % 3]
+            it[0] += 1
+            q.gemm_fp8_codes(aq, bqt, sa, sb, out_dtype=torch.bfloat16, out=c)
+
+        def lib_plain():
+            aq, bqt, sa, sb, _ = sets[it[0] % 3]
+            c2 = cmp_out[it[0] % 3]
+            it[0] += 1
+            torch._scaled_mm(aq.view(torch.float8_e4m3fn), bqt.view(torch.float8_e4m3fn).t(), scale_a=sa.reshape(()),
+                             scale_b=sb.reshape(()), out_dtype=torch.bfloat16, out=c2)
+
+        lib_plain()
+        ours_us, lib_us = [], []
+        for i in range(6):
+            for fn, acc in ((ours_plain, ours_us), (lib_plain, lib_us)) if i % 2 == 0 else ((lib_plain, lib_us), (ours_plain, ours_us)):
+                acc.append(timeit(fn, iters=12, warm=1))
+        ours_us.sort(), lib_us.sort()
+        mo, ml = 0.5 * (ours_us[2] + ours_us[3]), 0.5 * (lib_us[2] + lib_us[3])
+        out["fp8_gemm_4096_bias_relu_bf16"]["plain_gemm_vs_cublaslt"] = {
+            "ours_us": round(mo, 2), "library_us": round(ml, 2), "ours_over_library": round(ml / mo, 4),
+            "what": "e4m3 x e4m3 -> bf16 without the epilogue, torch._scaled_mm on the same operands, 6 interleaved bursts of 12"}
+        del cmp_out
+    except Exception as e:
+        out["fp8_gemm_4096_bias_relu_bf16"]["plain_gemm_vs_cublaslt"] = {"unavailable": str(e)[:200]}
     del sets
     # SwiGLU GEMM + re-quantisation, M = K = 4096, N = 2 x 11008 (gate|up interleaved)
     m, k, n = 4096, 4096, 22016
@@ -378,6 +408,32 @@ def other_config_metrics(peaks):
     out["f16_gemm_4096_kmajor_f32_out"] = {"us": round(us, 2), "tflops": round(tf, 1),
                                            "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
                                            "note": "tcgen05 kind::f16; two rotating operand sets (2 x 134 MB)"}
+    # the same product with f16 output against cuBLAS (torch.matmul), interleaved bursts
+    try:
+        c16 = [torch.empty(m, n, device="cuda", dtype=torch.float16) for _ in range(4)]
+
+        def ours_f16():
+            a, bt, _ = sets[it[0] % 2]
+            it[0] += 1
+            q.gemm_f16_kmajor(a, bt, out_dtype=torch.float16, out=c16[it[0] % 2])
+
+        def lib_f16():
+            a, bt, _ = sets[it[0] % 2]
+            it[0] += 1
+            torch.matmul(a, bt.t(), out=c16[2 + it[0] % 2])
+
+        lib_f16()
+        ours_us, lib_us = [], []
+        for i in range(6):
+            for fn, acc in ((ours_f16, ours_us), (lib_f16, lib_us)) if i % 2 == 0 else ((lib_f16, lib_us), (ours_f16, ours_us)):
+                acc.append(timeit(fn, iters=12, warm=1))
+        ours_us.sort(), lib_us.sort()
+        mo, ml = 0.5 * (ours_us[2] + ours_us[3]), 0.5 * (lib_us[2] + lib_us[3])
+        out["f16_gemm_4096_kmajor_f32_out"]["f16_out_vs_cublas"] = {
+            "ours_us": round(mo, 2), "library_us": round(ml, 2), "ours_over_library": round(ml / mo, 4),
+            "what": "f16 x f16 -> f16, torch.matmul on the same operands, 6 interleaved bursts of 12"}
+    except Exception as e:
+        out["f16_gemm_4096_kmajor_f32_out"]["f16_out_vs_cublas"] = {"unavailable": str(e)[:200]}
     q.device_status()
     return out
 
