@@ -20,6 +20,7 @@ on the device):
   --only decode    [--tokens 8] [--iters 48]                   INT4 decode GEMM, K=4096, N=11008
   --only f16_decode [--tokens 8] [--iters 48]                  F16 weight streaming, K=N=4096
   --only quantize  [--m 8192 --k 8192]                         dynamic e4m3 quantisation, both layouts
+  --only int4_quantize [--iters 6]                             INT4 group quantise + repack, 4096 x 11008
   --only layer_ops [--m 8192 --k 8192]                         fused add+RMSNorm, RoPE
   --only attention [--seqs 16 --seq-len 4096]                  paged decode attention
 """
@@ -957,6 +958,11 @@ def run_only(a):
         for _ in range(a.iters):
             q.quantize_fp8_dynamic(x)
             q.quantize_fp8_dynamic(x, transpose=True)
+    elif a.only == "int4_quantize":
+        ws = [(torch.randn(4096, DECODE_N, device=dev) / 64).to(torch.float16) for _ in range(3)]  # 3 x 90 MB
+        for i in range(a.iters):
+            qw, sc = q.int4_quantize(ws[i % 3])
+            q.int4_repack(qw, sc)
     elif a.only in ("step", "gemm"):
         w = torch.randn(a.k, a.n, device=dev, dtype=torch.float16)
         bqt, sb = q.quantize_fp8_dynamic(w, transpose=True)
@@ -999,7 +1005,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained leg (0 = skip)")
-    ap.add_argument("--only", default=None, choices=["step", "gemm", "decode", "f16_decode", "quantize", "layer_ops", "attention"],
+    ap.add_argument("--only", default=None, choices=["step", "gemm", "decode", "f16_decode", "quantize", "int4_quantize", "layer_ops", "attention"],
                     help="run a few launches of one kernel family (for a profiler capture) and print ok")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)

@@ -34,29 +34,32 @@ namespace {
 // thread writes 32 contiguous bytes of qweight and a half warp 512. Measured at 4096 x 11008:
 // rows held in registers, three CTAs per SM 43 us, four (64 registers) 39 us; four rows per
 // thread in CTAs of 512 (halves of a word swapped by shuffle) 43 us; the tile staged in shared
-// memory by cp.async (below: 47 registers, five CTAs per SM) 37.5 us. About 15 instructions per
-// weight remain (conversion, amax, code, packing): 19 us of issue time per SM.
+// memory by cp.async (below: five CTAs per SM) 37.5 us with about 15 instructions per weight
+// (conversion, amax, code with two range tests, clamp, bit-field packing: 19 us of issue time
+// per SM); the code path described next needs about 9.
 //
 // The code of a weight is clamp(rint(v / s), -8, 7) with an IEEE division and ties to even. The
 // division is not paid per element: v and s are f16 values, so the exact quotient is a ratio of
 // two integers below 2048 times a power of two, and such a ratio is either exactly a half-integer
-// or at least 1 / 4094 away from every half-integer. t = v * (1 / s) carries an error below
-// 1e-6 for |t| < 16, so rint(t) is the code unless t sits within 1e-4 of a half-integer (then the
-// quotient IS that half-integer; the division below settles the tie). Rounding is done by adding
-// and subtracting 1.5 * 2^23 (no conversion instructions); anything outside |t| < 16, NaN
-// included, takes the division as well, so every input gives the same code as before.
+// or at least 1 / 4094 away from every half-integer. t = v * (1 / s) + 8 carries an error below
+// 1e-6 for |v / s| < 7.4, so rint(t) - 8 is the code unless t sits within 1e-4 of a half-integer
+// (then the quotient may BE that half-integer and the division settles the tie). The common path
+// stays on the floating-point pipe and has no conversion, clamp or bit-field instruction:
+//   y = t + 1.5 * 2^23 (y - 1.5 * 2^23 = rint(t), ties to even), d = t - rint(t),
+//   word halves as floats, acc = acc * 16 + rint(t) over four rows (below 2^16: exact),
+// and a word's eight rows are checked together afterwards: max |d| <= 0.4999 and no NaN in the
+// accumulators. A column whose |amax / s| is not below 7.4 (a scale that rounded to a subnormal,
+// an infinite weight) gets NaN for 1 / s, which sends its words down the same exact path; so
+// every input gives the same code as the division. Stored nibbles are two's complement: the
+// offset-binary digits rint(t) = q + 8 are flipped by one XOR per word.
 // 16-byte asynchronous copy that writes zeros and reads nothing when `valid` is false.
 __device__ __forceinline__ void cp_async_16_zfill_q(uint32_t dst_smem, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ int int4_code(float v, float s, float rcp_s) {
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: v + kMagic has v's nearest integer in its low mantissa bits
-    const float t = __fmul_rn(v, rcp_s);
-    const float y = __fadd_rn(t, kMagic);
-    const float d = fabsf(__fsub_rn(t, __fsub_rn(y, kMagic)));
-    int q = __float_as_int(y) - 0x4B400000;
-    if (!(fabsf(t) < 16.0f) || d > 0.4999f) q = s > 0.0f ? __float2int_rn(__fdiv_rn(v, s)) : 0;
+// The definition, for the words the common path hands back.
+__device__ __forceinline__ int int4_code_exact(float v, float s) {
+    const int q = s > 0.0f ? __float2int_rn(__fdiv_rn(v, s)) : 0;
     return max(-8, min(7, q));
 }
 
@@ -68,8 +71,8 @@ __global__ void __launch_bounds__(256, 5)
     // five CTAs fit an SM and 160 KB per SM are in flight.
     __shared__ __align__(16) uint8_t tile[128][256];
     __shared__ float part[16][128];
-    __shared__ float col_scale[128];
-    __shared__ float col_rcp[128];
+    __shared__ __align__(16) float col_scale[128];
+    __shared__ __align__(16) float col_rcp[128];
     const int cv = threadIdx.x & 15, rg = threadIdx.x >> 4;
     const size_t g = blockIdx.y;
     const size_t col = (size_t)blockIdx.x * 128 + (size_t)cv * 8;
@@ -81,45 +84,87 @@ __global__ void __launch_bounds__(256, 5)
         for (int r = 0; r < 8; ++r) cp_async_16_zfill_q(dst + r * 256, base + (size_t)r * N, live);
         asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     }
-    float amax[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    const uint8_t* mine = &tile[rg * 8][cv * 16];  // this thread's own copies
+    // Column maxima of |v| on f16 pairs (a NaN never wins a maximum, as with fmaxf).
+    {
+        __half2 m2[4];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const uint4 row = *reinterpret_cast<const uint4*>(&tile[rg * 8 + r][cv * 16]);  // this thread's own copy
-        const __half2* h = reinterpret_cast<const __half2*>(&row);
+        for (int j = 0; j < 4; ++j) m2[j] = __float2half2_rn(0.0f);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const uint4 row = *reinterpret_cast<const uint4*>(mine + r * 256);
+            const __half2* h = reinterpret_cast<const __half2*>(&row);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m2[j] = __hmax2(m2[j], __habs2(h[j]));
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float2 f = __half22float2(h[j]);
-            amax[2 * j] = fmaxf(amax[2 * j], fabsf(f.x));
-            amax[2 * j + 1] = fmaxf(amax[2 * j + 1], fabsf(f.y));
+            const float2 f = __half22float2(m2[j]);
+            part[rg][cv * 8 + 2 * j] = f.x;
+            part[rg][cv * 8 + 2 * j + 1] = f.y;
         }
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) part[rg][cv * 8 + j] = amax[j];
     __syncthreads();
     if (threadIdx.x < 128) {
         float a = part[0][threadIdx.x];
 #pragma unroll
         for (int r = 1; r < 16; ++r) a = fmaxf(a, part[r][threadIdx.x]);
         const __half h = __float2half_rn(__fdiv_rn(a, 7.0f));
-        col_scale[threadIdx.x] = __half2float(h);
-        col_rcp[threadIdx.x] = __half2float(h) > 0.0f ? __frcp_rn(__half2float(h)) : 0.0f;
+        const float sc = __half2float(h);
+        const float rcp = sc > 0.0f ? __frcp_rn(sc) : 0.0f;
+        col_scale[threadIdx.x] = sc;
+        // NaN for a column the common path must not touch (see above)
+        col_rcp[threadIdx.x] = __fmul_rn(a, rcp) < 7.4f ? rcp : __int_as_float(0x7fc00000);
         const size_t c = (size_t)blockIdx.x * 128 + threadIdx.x;
         if (c < N) scales[g * N + c] = h;
     }
     __syncthreads();
     if (!live) return;
-    uint32_t words[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: t + kMagic has rint(t) in its low mantissa bits
+    float rcp[8];
+    {
+        const float4 r0 = *reinterpret_cast<const float4*>(&col_rcp[cv * 8]);
+        const float4 r1 = *reinterpret_cast<const float4*>(&col_rcp[cv * 8 + 4]);
+        rcp[0] = r0.x; rcp[1] = r0.y; rcp[2] = r0.z; rcp[3] = r0.w;
+        rcp[4] = r1.x; rcp[5] = r1.y; rcp[6] = r1.z; rcp[7] = r1.w;
+    }
+    float acc[8][2], dmax[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const uint4 row = *reinterpret_cast<const uint4*>(&tile[rg * 8 + r][cv * 16]);
+    for (int c = 0; c < 8; ++c) acc[c][0] = acc[c][1] = dmax[c] = 0.0f;
+#pragma unroll
+    for (int r = 7; r >= 0; --r) {  // the highest nibble of each half word first
+        const uint4 row = *reinterpret_cast<const uint4*>(mine + r * 256);
         const __half2* h = reinterpret_cast<const __half2*>(&row);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __half22float2(h[j]);
-            const int q0 = int4_code(f.x, col_scale[cv * 8 + 2 * j], col_rcp[cv * 8 + 2 * j]);
-            const int q1 = int4_code(f.y, col_scale[cv * 8 + 2 * j + 1], col_rcp[cv * 8 + 2 * j + 1]);
-            words[2 * j] |= ((uint32_t)q0 & 0xfu) << (4 * r);
-            words[2 * j + 1] |= ((uint32_t)q1 & 0xfu) << (4 * r);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = 2 * j + e;
+                const float tq = __fmaf_rn(e == 0 ? f.x : f.y, rcp[c], 8.0f);
+                const float rt = __fsub_rn(__fadd_rn(tq, kMagic), kMagic);  // rint(tq)
+                dmax[c] = fmaxf(dmax[c], fabsf(__fsub_rn(tq, rt)));
+                acc[c][r >> 2] = __fmaf_rn(acc[c][r >> 2], 16.0f, rt);
+            }
+        }
+    }
+    uint32_t words[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        // 2^23 + n has the integer n < 2^16 in its low mantissa bits
+        const uint32_t lo = __float_as_uint(__fadd_rn(acc[c][0], 8388608.0f));
+        const uint32_t hi = __float_as_uint(__fadd_rn(acc[c][1], 8388608.0f));
+        words[c] = __byte_perm(lo, hi, 0x5410) ^ 0x88888888u;
+        const float chk = __fadd_rn(acc[c][0], acc[c][1]);
+        if (!(dmax[c] <= 0.4999f) || !(chk == chk)) {  // a possible tie, a NaN, or a column off the common path
+            const float sc = col_scale[cv * 8 + c];
+            uint32_t wd = 0u;
+#pragma unroll 1
+            for (int r = 0; r < 8; ++r) {
+                const float v = __half2float(*reinterpret_cast<const __half*>(mine + r * 256 + 2 * c));
+                wd |= ((uint32_t)int4_code_exact(v, sc) & 0xfu) << (4 * r);
+            }
+            words[c] = wd;
         }
     }
     uint4* dst = reinterpret_cast<uint4*>(qweight + (g * 16 + (size_t)rg) * N + col);
